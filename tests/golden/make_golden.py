@@ -1,0 +1,196 @@
+"""Regenerates tests/golden/*.npz from the CUDALM reference itself.
+
+Run where the reference tree is mounted (it is not present on GPU boxes):
+
+    python tests/golden/make_golden.py [--ref /root/reference]
+
+What is recorded, and which reference code produced it:
+
+* quantize.npz   inputs (bf16 bits) and the outputs of the reference's Python
+                 quantizer ``quantize_w4a16`` (tools/common/w4a16_quant.py:25-60),
+                 imported from the reference tree and run under torch CPU.
+* gemv.npz       inputs and the outputs of the reference's CPU GEMV
+                 ``ref_gemv_bf16`` (tests/cuda/test_int4_gemv_bf16.cpp:54-69),
+                 called through oracle/_ref/libcudalm_ref.so, which oracle/Makefile
+                 compiles from the reference's own sources.
+* pick.npz       bf16 logit rows with the reference's ``argmax_bf16``
+                 (include/cudalm/greedy.h:28-39) result and the keep-set of its
+                 top-k filter (include/cudalm/sampling.h:152-166).
+
+All inputs are seeded; the files are a few hundred KB in total.
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+
+from oracle import cpu_oracle as orc  # noqa: E402
+
+BASE_SEED = 20250922
+
+
+def bf16_bits(t: torch.Tensor) -> np.ndarray:
+    return t.to(torch.bfloat16).contiguous().view(torch.int16).numpy().view(np.uint16).copy()
+
+
+def f16_bits(t: torch.Tensor) -> np.ndarray:
+    return t.to(torch.float16).contiguous().view(torch.int16).numpy().view(np.uint16).copy()
+
+
+def quant_cases(quantize_w4a16):
+    g = torch.Generator().manual_seed(BASE_SEED + 4)
+    cases = {}
+
+    def add(name, W):
+        W = W.to(torch.bfloat16).contiguous()
+        packed, scale16, q, scale32 = quantize_w4a16(W)
+        cases[f"{name}.w"] = bf16_bits(W)
+        cases[f"{name}.packed"] = packed.numpy().copy()
+        cases[f"{name}.scale"] = f16_bits(scale16)
+
+    # the benchmark's distribution: N(0, 0.02)
+    add("normal_16x1024", torch.randn(16, 1024, generator=g) * 0.02)
+    add("normal_5x256", torch.randn(5, 256, generator=g) * 0.02)
+    add("normal_3x3584", torch.randn(3, 3584, generator=g) * 0.02)
+    # wide dynamic range between groups
+    W = torch.randn(8, 512, generator=g)
+    W = W * torch.logspace(-6, 3, 8).view(8, 1)
+    add("logrange_8x512", W)
+    # an all-zero group, an all-zero row, and a group with a single non-zero
+    W = torch.randn(6, 384, generator=g) * 0.02
+    W[0, 0:128] = 0
+    W[2, :] = 0
+    W[4, 128:256] = 0
+    W[4, 200] = 0.3
+    add("zero_groups_6x384", W)
+    # scale underflows fp16 (amax/7 < 2^-25) while the fp32 scale is non-zero:
+    # the stored scale is 0 but q keeps its non-zero values
+    W = torch.randn(4, 256, generator=g) * 1e-9
+    add("fp16_underflow_4x256", W)
+    # fp16-subnormal scales
+    W = torch.randn(4, 256, generator=g) * 3e-6
+    add("fp16_subnormal_4x256", W)
+    # exact .5 ties: amax = 7 so the scale is 1 and w = k + 0.5 are ties
+    W = torch.zeros(2, 128)
+    W[0, :15] = torch.arange(-7, 8).float()
+    W[0, 15:29] = torch.arange(-7, 7).float() + 0.5
+    W[0, 29] = 7.0
+    W[1, :] = torch.linspace(-7, 7, 128)
+    add("ties_2x128", W)
+    # values large enough that the scale is large; negative extreme only
+    W = -torch.rand(3, 128, generator=g) * 1000.0
+    add("negative_large_3x128", W)
+    # every group the same magnitude element (max|q| must be 7 everywhere)
+    W = torch.full((2, 256), 0.0123)
+    W[1] = -W[1]
+    add("constant_2x256", W)
+    return cases
+
+
+def gemv_cases():
+    cases = {}
+    rng = np.random.default_rng(BASE_SEED)
+
+    def add(name, W, S, x):
+        y = orc.ref_gemv_bf16(W, S, x)
+        cases[f"{name}.W"] = W
+        cases[f"{name}.S"] = S
+        cases[f"{name}.x"] = x
+        cases[f"{name}.y"] = y
+
+    def rand_scales(shape):
+        return f16_bits(torch.from_numpy(
+            (0.001 + 0.02 * rng.random(shape)).astype(np.float32)))
+
+    def rand_x(K, scale=1.0):
+        return orc.f32_to_bf16_bits((rng.standard_normal(K) * scale).astype(np.float32))
+
+    # full nibble domain (0x8 = -8 included), positive scales
+    for N, K in ((3, 128), (5, 256), (16, 1024), (9, 1024), (8, 2048), (4, 3584)):
+        W = rng.integers(0, 256, size=(N, K // 2), dtype=np.uint8)
+        add(f"random_{N}x{K}", W, rand_scales((N, K // 128)), rand_x(K))
+    # all-zero weights and scales -> exact zeros
+    add("zero_8x256", np.zeros((8, 128), np.uint8), np.zeros((8, 2), np.uint16),
+        rand_x(256))
+    # all-zero activations
+    W = rng.integers(0, 256, size=(6, 512), dtype=np.uint8)
+    add("zero_x_6x1024", W, rand_scales((6, 8)), np.zeros(1024, np.uint16))
+    # boundary nibbles with one scale in five set to zero
+    nib = np.array([0x7, 0x9, 0x8, 0x0, 0xF, 0x7, 0x8, 0xF], np.uint8)
+    lo = nib[rng.integers(0, 8, size=(12, 512))]
+    hi = nib[rng.integers(0, 8, size=(12, 512))]
+    W = (lo | (hi << 4)).astype(np.uint8)
+    S = rand_scales((12, 8))
+    S[rng.random((12, 8)) < 0.2] = 0
+    add("boundary_12x1024", W, S, rand_x(1024))
+    # tiny activations, mixed signs
+    W = rng.integers(0, 256, size=(7, 512), dtype=np.uint8)
+    add("small_x_7x1024", W, rand_scales((7, 8)), rand_x(1024, 0.005))
+    # activation outliers (1% x20), as the batched-decode configuration uses
+    x = (rng.standard_normal(1024)).astype(np.float32)
+    x[rng.random(1024) < 0.01] *= 20.0
+    W = rng.integers(0, 256, size=(10, 512), dtype=np.uint8)
+    add("outlier_x_10x1024", W, rand_scales((10, 8)), orc.f32_to_bf16_bits(x))
+    return cases
+
+
+def pick_cases():
+    cases = {}
+    rng = np.random.default_rng(BASE_SEED + 3)
+
+    def add(name, logits_bits, k):
+        cases[f"{name}.logits"] = logits_bits
+        cases[f"{name}.argmax"] = np.array([orc.ref_argmax_bf16(logits_bits)], np.int32)
+        cases[f"{name}.k"] = np.array([k], np.int32)
+        cases[f"{name}.keep"] = orc.ref_topk_keep(logits_bits, k)
+
+    add("normal_4096_k50", orc.f32_to_bf16_bits(
+        (rng.standard_normal(4096) * 3).astype(np.float32)), 50)
+    # heavy ties: few distinct bf16 values
+    add("ties_2048_k50", orc.f32_to_bf16_bits(
+        rng.integers(-3, 4, size=2048).astype(np.float32) * 0.5), 50)
+    # all equal
+    add("flat_300_k50", orc.f32_to_bf16_bits(np.full(300, 1.25, np.float32)), 50)
+    # all negative
+    add("negative_1000_k7", orc.f32_to_bf16_bits(
+        (-np.abs(rng.standard_normal(1000)) - 0.5).astype(np.float32)), 7)
+    # k larger than n
+    add("short_20_k50", orc.f32_to_bf16_bits(
+        rng.standard_normal(20).astype(np.float32)), 50)
+    # +0 and -0 compare equal
+    z = np.zeros(64, np.float32)
+    z[::2] = -0.0
+    z[10] = -1.0
+    add("signed_zero_64_k5", orc.f32_to_bf16_bits(z), 5)
+    # single element
+    add("single_1_k1", orc.f32_to_bf16_bits(np.array([-7.5], np.float32)), 1)
+    return cases
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--ref", default="/root/reference")
+    args = ap.parse_args()
+    sys.path.insert(0, os.path.join(args.ref, "tools"))
+    from common.w4a16_quant import quantize_w4a16  # the reference's quantizer
+
+    orc.build(force=True)
+    if not orc.have_ref():
+        raise SystemExit("oracle/_ref/libcudalm_ref.so was not built")
+    np.savez_compressed(os.path.join(HERE, "quantize.npz"), **quant_cases(quantize_w4a16))
+    np.savez_compressed(os.path.join(HERE, "gemv.npz"), **gemv_cases())
+    np.savez_compressed(os.path.join(HERE, "pick.npz"), **pick_cases())
+    for f in ("quantize.npz", "gemv.npz", "pick.npz"):
+        print(f, os.path.getsize(os.path.join(HERE, f)), "bytes")
+
+
+if __name__ == "__main__":
+    main()
