@@ -1,0 +1,447 @@
+#!/usr/bin/env python
+"""Benchmark of the W4A16 projection path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (``config.workload``): the full M=1 projection set of the 24-layer
+hybrid stack -- 132 projections, 237,981,696 algorithmic bytes per pass -- with
+seeded synthetic weights (bf16 ~N(0, 0.02), quantized by this library's GPU
+quantizer) and activations (bf16 ~N(0, 1)).  One step = one pass over the set.
+Several distinct copies of the weights are rotated so that every step reads
+weights that left L2 long ago (the set is 238 MB, L2 is 126 MB).
+
+Printed: ONE JSON line.  ``value`` is algorithmic GB/s with all inputs resident
+in HBM (one grouped launch per step); ``e2e`` is the same metric through the
+host-buffer call (activations copied in from pinned host memory and outputs
+copied back inside the timed region, synchronised every step); ``roofline``
+relates the grouped kernel to the measured HBM copy bandwidth; ``cpu_baseline``
+is the reference's CPU GEMV on this box's cores; ``lm_head`` reports the
+vocabulary projection (rows/s), vocabulary-parallel when N > 1.
+
+With ``--gpus N`` (N > 1, under torchrun) every rank runs its own replica of the
+projection set (the set does not shard: replicas only, no collective), and the
+248320-row lm_head is sharded over the ranks with one all-gather of candidates.
+
+``--impl reference`` times the reference's own CPU implementation of the path
+(``oracle/_ref`` when it was built from the reference's sources, otherwise the
+oracle port) with all host threads, on the same workload and metric.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# (N, K, count): DeltaNet in-proj, DeltaNet out-proj, attn q+gate, k, v, o, gate, up, down
+PROJECTION_SET = [(6144, 1024, 18), (1024, 2048, 18), (4096, 1024, 6), (512, 1024, 6),
+                  (512, 1024, 6), (1024, 2048, 6), (3584, 1024, 24), (3584, 1024, 24),
+                  (1024, 3584, 24)]
+VOCAB, HIDDEN, TOP_K = 248320, 1024, 50
+SEED = 20250922
+METRIC = "w4a16_gemv_hbm_gbps_m1_projection_set"
+UNIT = "GB/s"
+# dram__bytes_read.sum + dram__bytes_write.sum of one grouped launch, from the
+# ncu capture summarised in profiles/ (None until a capture exists)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def set_bytes(M: int = 1) -> int:
+    return sum(c * (N * K // 2 + N * (K // 128) * 2 + M * K * 2 + M * N * 2)
+               for N, K, c in PROJECTION_SET)
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (6.65 TB/s)"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while a region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-i", str(self.index), "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                smax.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ---------------------------------------------------------------------------
+# reference arm: the reference's CPU GEMV on the host cores
+# ---------------------------------------------------------------------------
+def cpu_pass(orc, use_ref, weights, xs, threads):
+    """One pass of the projection set on the CPU; rows split over threads."""
+    import numpy as np
+    from concurrent.futures import ThreadPoolExecutor
+
+    if not use_ref:
+        for (W, S), x in zip(weights, xs):
+            orc.batch_gemv_bf16(W, S, x[None, :], threads=threads)
+        return
+
+    def work(args):
+        W, S, x = args
+        orc.ref_gemv_bf16(W, S, x)
+
+    jobs = []
+    for (W, S), x in zip(weights, xs):
+        rows = W.shape[0]
+        step = max(16, (rows + threads - 1) // threads)
+        for r0 in range(0, rows, step):
+            jobs.append((W[r0:r0 + step], S[r0:r0 + step], x))
+    with ThreadPoolExecutor(max_workers=threads) as ex:
+        list(ex.map(work, jobs))
+
+
+def cpu_inputs(orc, distinct_layers: int = 1):
+    """Raw packed bytes are enough for timing the CPU GEMV (its cost does not
+    depend on the values); one layer of each kind is built and reused."""
+    import numpy as np
+    rng = np.random.default_rng(SEED)
+    weights, xs = [], []
+    for N, K, c in PROJECTION_SET:
+        W = rng.integers(0, 256, size=(N, K // 2), dtype=np.uint8)
+        S = (0.001 + 0.02 * rng.random((N, K // 128))).astype(np.float16).view(np.uint16)
+        x = orc.f32_to_bf16_bits(rng.standard_normal(K).astype(np.float32))
+        for _ in range(c):
+            weights.append((W, S))
+            xs.append(x)
+    return weights, xs
+
+
+def time_cpu(steps: int, warmup: int, budget_s: float):
+    from oracle import cpu_oracle as orc
+    orc.build()
+    use_ref = orc.have_ref()
+    threads = os.cpu_count() or 1
+    weights, xs = cpu_inputs(orc)
+    for _ in range(max(1, min(warmup, 1))):
+        cpu_pass(orc, use_ref, weights, xs, threads)
+    times = []
+    t_start = time.perf_counter()
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        cpu_pass(orc, use_ref, weights, xs, threads)
+        times.append(time.perf_counter() - t0)
+        if time.perf_counter() - t_start > budget_s:
+            break
+    sec = statistics.median(times)
+    return {"value": set_bytes() / sec / 1e9, "unit": UNIT, "cores": threads,
+            "kind": "reference" if use_ref else "port",
+            "sample": f"{len(times)} full passes of the 132-projection set (237,981,696 B each), "
+                      f"rows split over {threads} threads; median pass {sec * 1e3:.1f} ms"}, sec, len(times)
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    base, sec, n = time_cpu(max(1, args.steps), args.warmup, budget_s=120.0)
+    line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT,
+            "n_gpus": args.gpus, "steps": n, "warmup": min(args.warmup, 1),
+            "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "int4 weights x bf16 activations, fp32 accumulate",
+            "data": "synthetic", "config": workload_config(args.gpus),
+            "cpu_baseline": base,
+            "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0,
+                    "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_gpus: int, copies: int = 0):
+    return {"workload": "BASELINE configs[1]: full M=1 projection set of the 24-layer hybrid "
+                        "stack (132 projections: 1024->6144 x18, 2048->1024 x24, 1024->4096 x6, "
+                        "1024->512 x12, 1024->3584 x48, 3584->1024 x24), G=128 int4 + fp16 scales",
+            "bytes_per_step": set_bytes(), "M": 1,
+            "l2": f"{copies} distinct weight copies rotated (each 238 MB > 126 MB L2)" if copies
+                  else "n/a",
+            "parallelism": "replicas only (one per GPU, no collective)" if n_gpus > 1 else "1 GPU"}
+
+
+# ---------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------
+def build_projection_set(eng, torch, copies: int, seed: int):
+    """Device-resident weights (quantized on the GPU by the library), one
+    contiguous activation buffer and one contiguous output buffer per copy."""
+    gen = torch.Generator(device="cuda").manual_seed(seed)
+    x_elems = sum(c * K for N, K, c in PROJECTION_SET)
+    y_elems = sum(c * N for N, K, c in PROJECTION_SET)
+    x_dev = torch.randn(x_elems, generator=gen, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+    y_dev = torch.zeros(y_elems, device="cuda", dtype=torch.bfloat16)
+    groups, keep = [], []
+    for _ in range(copies):
+        items, xo, yo = [], 0, 0
+        for N, K, c in PROJECTION_SET:
+            for _ in range(c):
+                w = (torch.randn((N, K), generator=gen, device="cuda", dtype=torch.float32) * 0.02
+                     ).to(torch.bfloat16)
+                packed, scale = eng.quantize_w4a16(w)
+                lin = eng.W4A16Linear(packed, scale)
+                items.append((lin, x_dev[xo:xo + K], y_dev[yo:yo + N]))
+                xo += K
+                yo += N
+        keep.append(items)
+        groups.append(eng.LinearGroup(items))
+    return groups, keep, x_dev, y_dev
+
+
+def time_steps(torch, fn, steps, warmup, dist=None):
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+        torch.cuda.synchronize()
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    evs[0].record()
+    for i in range(steps):
+        fn(warmup + i)
+        evs[i + 1].record()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+        torch.cuda.synchronize()
+    total_ms = evs[0].elapsed_time(evs[-1])
+    per = [evs[i].elapsed_time(evs[i + 1]) for i in range(steps)]
+    return total_ms, per
+
+
+def max_over_ranks(torch, dist, ms: float) -> float:
+    if dist is None:
+        return ms
+    t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def bench_lm_head(eng, torch, dist, rank, world, steps, warmup):
+    """Vocabulary projection: rows/s at M=1 and M=32, vocabulary-parallel over
+    `world` ranks (strong scaling: the 248320 rows are split)."""
+    lo, hi = eng.shard_rows(VOCAB, world, rank)
+    gen = torch.Generator(device="cuda").manual_seed(SEED + 3)  # same matrix on every rank
+    out = {}
+    # build the full matrix shard by shard to bound memory: generate all rows in
+    # blocks with one generator stream so that every rank sees the same matrix
+    block = 31040
+    packs, scales = [], []
+    for r0 in range(0, VOCAB, block):
+        w = (torch.randn((block, HIDDEN), generator=gen, device="cuda", dtype=torch.float32) * 0.02
+             ).to(torch.bfloat16)
+        a, b = max(lo, r0), min(hi, r0 + block)
+        if a < b:
+            p, s = eng.quantize_w4a16(w[a - r0:b - r0].contiguous())
+            packs.append(p)
+            scales.append(s)
+    lin = eng.W4A16Linear(torch.cat(packs), torch.cat(scales))
+    # a second copy of the shard so consecutive steps do not reuse L2 lines
+    lin2 = eng.W4A16Linear(lin.weight.clone(), lin.scale.clone())
+    for M in (1, 32):
+        heads = [eng.VocabParallelLmHead(eng.LmHead(l, TOP_K, id_offset=lo, max_rows=M))
+                 for l in (lin, lin2)]
+        x = torch.randn((M, HIDDEN), generator=gen, device="cuda", dtype=torch.float32)
+        x = (x / x.pow(2).mean(dim=1, keepdim=True).sqrt()).to(torch.bfloat16)
+        res = {}
+
+        def step(i):
+            res["out"] = heads[i % 2].forward(x)
+
+        total_ms, _ = time_steps(torch, step, steps, warmup, dist)
+        total_ms = max_over_ranks(torch, dist, total_ms)
+        out[f"M{M}"] = {"rows_per_s": M * steps / (total_ms * 1e-3),
+                        "us_per_call": total_ms * 1e3 / steps,
+                        "shard_rows": hi - lo,
+                        "shard_gbps": (lin.N * lin.K // 2 + lin.N * 16) * steps / (total_ms * 1e-3) / 1e9,
+                        "argmax_row0": int(res["out"][0][0].item())}
+    return out
+
+
+def run_ours(args):
+    import torch
+    import cudalm_agent_b200 as eng
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU path")
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    eng.load_library()
+
+    copies = 3
+    groups, keep, x_dev, y_dev = build_projection_set(eng, torch, copies, SEED + 1 + rank)
+    bytes_step = groups[0].bytes
+    assert bytes_step == set_bytes(), (bytes_step, set_bytes())
+
+    # ---- resident-in-HBM timing: one grouped launch per step ----------------
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    launches0 = eng.launch_count()
+    total_ms, per_step = time_steps(torch, lambda i: groups[i % copies].run(), args.steps,
+                                    args.warmup, dist)
+    launches = eng.launch_count() - launches0 - args.warmup
+    clocks = sampler.stop()
+    total_ms = max_over_ranks(torch, dist, total_ms)
+    value = world * bytes_step * args.steps / (total_ms * 1e-3) / 1e9
+    kernel_ms = statistics.mean(per_step)
+
+    # ---- end to end through the host-buffer call ------------------------------
+    x_host = torch.empty_like(x_dev, device="cpu").pin_memory()
+    x_host.copy_(x_dev)
+    y_host = torch.empty_like(y_dev, device="cpu").pin_memory()
+
+    def e2e_step(i):
+        x_dev.copy_(x_host, non_blocking=True)
+        groups[i % copies].run()
+        y_host.copy_(y_dev, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for i in range(args.warmup):
+        e2e_step(i)
+    if dist is not None:
+        dist.barrier()
+    t0 = time.perf_counter()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for i in range(args.steps):
+        e2e_step(args.warmup + i)
+    ev1.record()
+    torch.cuda.synchronize()
+    e2e_ms = max_over_ranks(torch, dist, max(ev0.elapsed_time(ev1), (time.perf_counter() - t0) * 1e3))
+    e2e_value = world * bytes_step * args.steps / (e2e_ms * 1e-3) / 1e9
+
+    # ---- latency mode: one launch per projection, as the reference calls it ----
+    def per_call(i):
+        for lin, x, y in keep[i % copies]:
+            eng.int4_gemv_bf16(lin.weight, lin.scale, x, y)
+
+    lat_steps = max(3, min(args.steps, 10))
+    lat_ms, _ = time_steps(torch, per_call, lat_steps, 2, dist)
+    lat_ms = max_over_ranks(torch, dist, lat_ms)
+
+    status = eng.device_status()
+    if status != 0:
+        raise SystemExit(f"device status word = {status}: a bounded wait ran out")
+
+    for g in groups:
+        g.close()
+    del groups, keep
+    torch.cuda.empty_cache()
+
+    lm = bench_lm_head(eng, torch, dist, rank, world, max(5, min(args.steps, 50)), 3)
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    peak, peak_src = measured_peaks()
+    achieved = bytes_step / (kernel_ms * 1e-3) / 1e9
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None,
+        "dtype": "int4 weights x bf16 activations, fp32 accumulate", "data": "synthetic",
+        "config": workload_config(world, copies),
+        "clocks": clocks,
+        "e2e": {"value": e2e_value, "unit": UNIT,
+                "h2d_bytes_per_step": x_dev.numel() * 2, "d2h_bytes_per_step": y_dev.numel() * 2,
+                "ms_per_step": e2e_ms / args.steps,
+                "what": "pinned-host activations copied in, one grouped launch, outputs copied "
+                        "back to pinned host, stream synchronised every step; weights resident"},
+        "gpu_launches": int(launches),
+        "roofline": {"bound": "hbm", "kernel": "w4a16_stream_kernel<NT=1> (grouped launch)",
+                     "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
+                     "peak_source": peak_src + ", of measured",
+                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                     "algorithmic_bytes_per_launch": bytes_step,
+                     "avg_launch_ms": kernel_ms},
+        "latency_mode": {"what": "132 separate launches per pass (one per projection)",
+                         "ms_per_pass": lat_ms / lat_steps,
+                         "gbps": bytes_step * lat_steps / (lat_ms * 1e-3) / 1e9,
+                         "us_per_call": lat_ms * 1e3 / lat_steps / 132},
+        "lm_head": {"vocab": VOCAB, "K": HIDDEN, "top_k": TOP_K, "n_gpus": world,
+                    "scaling": "strong (vocabulary rows split over ranks, one all-gather of "
+                               "candidates)" if world > 1 else "single GPU", **lm},
+    }
+    if world == 1:
+        base, _, _ = time_cpu(5, 1, budget_s=25.0)
+        line["cpu_baseline"] = base
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

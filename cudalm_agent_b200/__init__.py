@@ -1,0 +1,17 @@
+"""B200-native W4A16 projection engine: a drop-in for CUDALM's int4-weight x
+bf16-activation linear path (GEMV, batched rows, fused gate+up, vocabulary
+projection with on-device pick, quantize+pack).  See ``include/cudalm_b200.h``
+for the C ABI; this package is its host-side mirror of the reference interface.
+"""
+from .api import (CudalmB200Error, GROUP_SIZE, INT4_MAX, LinearGroup, LmHead, W4A16Linear,
+                  batch_int4_gemv_bf16, device_status, gate_up_bf16, int4_gemv_bf16,
+                  launch_count, library_path, linear_multi, load_library, quantize_w4a16,
+                  topk_merge)
+from .vocab_parallel import VocabParallelLmHead, merge_topk_host, shard_rows
+
+__all__ = [
+    "CudalmB200Error", "GROUP_SIZE", "INT4_MAX", "LinearGroup", "LmHead", "W4A16Linear",
+    "batch_int4_gemv_bf16", "device_status", "gate_up_bf16", "int4_gemv_bf16", "launch_count",
+    "library_path", "linear_multi", "load_library", "quantize_w4a16", "topk_merge",
+    "VocabParallelLmHead", "merge_topk_host", "shard_rows",
+]

@@ -1,0 +1,343 @@
+"""Host-side mirror of CUDALM's W4A16 operator interface over the C ABI.
+
+Function names, argument order and error behaviour follow the reference's C++
+entry points (``cudalm::int4_gemv_bf16``, ``cudalm::kernels::batch_int4_gemv_bf16``,
+``W4A16Linear``, the offline ``quantize_w4a16``), so that tests written against
+the reference read the same here.  Arguments are ``torch`` tensors on a CUDA
+device; torch is used only to own device memory and to name the current stream.
+Every call goes through ``libcudalm_b200.so``; there is no CPU path, and a
+missing library or a non-zero status raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from dataclasses import dataclass
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from . import build as _build
+
+GROUP_SIZE = 128
+INT4_MAX = 7
+MAX_TOP_K = 64
+
+OK = 0
+ERR_BAD_SHAPE = 1
+ERR_NULL = 2
+ERR_MISALIGNED = 3
+ERR_CUDA = 4
+ERR_TIMEOUT = 5
+ERR_UNSUPPORTED = 6
+ERR_TOO_LARGE = 7
+ERR_WORKSPACE = 8
+
+
+class CudalmB200Error(RuntimeError):
+    """A C-ABI call returned a non-zero status (CUDALM itself would abort)."""
+
+    def __init__(self, fn: str, status: int, detail: str):
+        super().__init__(f"{fn} failed: status {status} ({detail})")
+        self.status = status
+
+
+class _LinearStruct(ctypes.Structure):
+    _fields_ = [("weight", ctypes.c_void_p), ("scales", ctypes.c_void_p),
+                ("x", ctypes.c_void_p), ("y", ctypes.c_void_p),
+                ("N", ctypes.c_int32), ("K", ctypes.c_int32),
+                ("M", ctypes.c_int32), ("reserved", ctypes.c_int32)]
+
+
+_vp = ctypes.c_void_p
+_ci = ctypes.c_int
+
+# name -> (restype, argtypes); every symbol include/cudalm_b200.h declares
+SIGNATURES = {
+    "cudalm_b200_status_string": (ctypes.c_char_p, [_ci]),
+    "cudalm_b200_last_cuda_error": (_ci, []),
+    "cudalm_b200_build_info": (ctypes.c_char_p, []),
+    "cudalm_b200_device_status": (_ci, [ctypes.POINTER(_ci)]),
+    "cudalm_b200_int4_gemv_bf16": (_ci, [_vp, _vp, _vp, _vp, _ci, _ci, _vp]),
+    "cudalm_b200_batch_int4_gemv_bf16": (_ci, [_vp, _vp, _vp, _vp, _ci, _ci, _ci, _vp]),
+    "cudalm_b200_linear_multi": (_ci, [ctypes.POINTER(_LinearStruct), _ci, _vp]),
+    "cudalm_b200_group_create": (_ci, [ctypes.POINTER(_LinearStruct), _ci, ctypes.POINTER(_vp)]),
+    "cudalm_b200_group_run": (_ci, [_vp, _vp]),
+    "cudalm_b200_group_destroy": (_ci, [_vp]),
+    "cudalm_b200_group_bytes": (ctypes.c_int64, [_vp]),
+    "cudalm_b200_gate_up_bf16": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _vp]),
+    "cudalm_b200_lm_head_workspace_bytes": (ctypes.c_size_t, [_ci, _ci, _ci, _ci, _ci]),
+    "cudalm_b200_lm_head_topk": (_ci, [_vp, _vp, _vp, _ci, _ci, _ci, _ci, _ci, _vp, _vp, _vp,
+                                      _vp, _vp, ctypes.c_size_t, _vp]),
+    "cudalm_b200_topk_merge": (_ci, [_vp, _vp, _ci, _ci, _ci, _vp, _vp, _vp, _vp]),
+    "cudalm_b200_quantize_w4a16": (_ci, [_vp, _ci, _ci, _vp, _vp, _vp]),
+    "cudalm_b200_kernel_regs": (_ci, [ctypes.c_char_p]),
+    "cudalm_b200_launch_count": (ctypes.c_int64, []),
+}
+
+_lib: Optional[ctypes.CDLL] = None
+
+
+def library_path() -> str:
+    return _build.LIB_PATH
+
+
+def load_library() -> ctypes.CDLL:
+    """Loads ``libcudalm_b200.so`` (it must have been built; see ``build.py``)."""
+    global _lib
+    if _lib is None:
+        path = library_path()
+        if not os.path.exists(path):
+            raise CudalmB200Error("load_library", ERR_UNSUPPORTED,
+                                  f"{path} is missing: run python -m cudalm_agent_b200.build")
+        lib = ctypes.CDLL(path)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib
+
+
+def _check(fn: str, status: int) -> None:
+    if status != OK:
+        lib = load_library()
+        detail = lib.cudalm_b200_status_string(status).decode()
+        if status == ERR_CUDA:
+            detail += f"; cudaError {lib.cudalm_b200_last_cuda_error()}"
+        raise CudalmB200Error(fn, status, detail)
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _need(t: torch.Tensor, dtype: torch.dtype, name: str) -> None:
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (there is no CPU path)")
+    if t.dtype != dtype:
+        raise ValueError(f"{name} must be {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+
+
+def device_status() -> int:
+    """Synchronises and returns (then clears) the device-side status word."""
+    out = _ci(0)
+    _check("device_status", load_library().cudalm_b200_device_status(ctypes.byref(out)))
+    return out.value
+
+
+def launch_count() -> int:
+    return int(load_library().cudalm_b200_launch_count())
+
+
+@dataclass
+class W4A16Linear:
+    """One projection: packed int4 weight ``[N, K/2]`` uint8 and fp16 group
+    scales ``[N, K/128]`` (CUDALM include/cudalm/weight_loader.h:58-63)."""
+    weight: torch.Tensor
+    scale: torch.Tensor
+    N: int = 0
+    K: int = 0
+
+    def __post_init__(self):
+        _need(self.weight, torch.uint8, "weight")
+        _need(self.scale, torch.float16, "scale")
+        n, half_k = self.weight.shape
+        # CUDALM src/runtime/weight_loader_v2.cpp:479-482: N = dim0, K = 2*dim1
+        self.N, self.K = int(n), int(half_k) * 2
+        if tuple(self.scale.shape) != (self.N, self.K // GROUP_SIZE):
+            raise ValueError("scale must be [N, K/128]")
+
+    def bytes(self, M: int = 1) -> int:
+        return self.N * self.K // 2 + self.N * (self.K // GROUP_SIZE) * 2 + M * self.K * 2 + M * self.N * 2
+
+
+def int4_gemv_bf16(weight: torch.Tensor, scales: torch.Tensor, x: torch.Tensor,
+                   y: Optional[torch.Tensor] = None, N: Optional[int] = None,
+                   K: Optional[int] = None) -> torch.Tensor:
+    """``y[n] = sum_k q[n,k] * scale[n,k/128] * x[k]`` (CUDALM
+    include/cudalm/kernels/int4_gemv_bf16.h:46-48).  x bf16 ``[K]`` -> y bf16 ``[N]``."""
+    _need(weight, torch.uint8, "weight")
+    _need(scales, torch.float16, "scales")
+    _need(x, torch.bfloat16, "x")
+    N = int(weight.shape[0]) if N is None else N
+    K = int(weight.shape[1]) * 2 if K is None else K
+    if y is None:
+        y = torch.empty(N, dtype=torch.bfloat16, device=x.device)
+    _need(y, torch.bfloat16, "y")
+    st = load_library().cudalm_b200_int4_gemv_bf16(_ptr(weight), _ptr(scales), _ptr(x), _ptr(y),
+                                                   N, K, _stream())
+    _check("int4_gemv_bf16", st)
+    return y
+
+
+def batch_int4_gemv_bf16(weight: torch.Tensor, scales: torch.Tensor, x: torch.Tensor,
+                         y: Optional[torch.Tensor] = None, N: Optional[int] = None,
+                         K: Optional[int] = None, B: Optional[int] = None) -> torch.Tensor:
+    """B rows against the same weights (CUDALM include/cudalm/kernels/batch_decode.h:61-63):
+    x bf16 ``[B, K]`` -> y bf16 ``[B, N]``."""
+    _need(weight, torch.uint8, "weight")
+    _need(scales, torch.float16, "scales")
+    _need(x, torch.bfloat16, "x")
+    N = int(weight.shape[0]) if N is None else N
+    K = int(weight.shape[1]) * 2 if K is None else K
+    B = int(x.shape[0]) if B is None else B
+    if y is None:
+        y = torch.empty((B, N), dtype=torch.bfloat16, device=x.device)
+    _need(y, torch.bfloat16, "y")
+    st = load_library().cudalm_b200_batch_int4_gemv_bf16(_ptr(weight), _ptr(scales), _ptr(x),
+                                                         _ptr(y), N, K, B, _stream())
+    _check("batch_int4_gemv_bf16", st)
+    return y
+
+
+def _fill(desc: _LinearStruct, lin: W4A16Linear, x: torch.Tensor, y: torch.Tensor) -> None:
+    _need(x, torch.bfloat16, "x")
+    _need(y, torch.bfloat16, "y")
+    M = 1 if x.dim() == 1 else int(x.shape[0])
+    if x.numel() != M * lin.K or y.numel() != M * lin.N:
+        raise ValueError("x must be [M, K] and y [M, N]")
+    desc.weight, desc.scales = _ptr(lin.weight), _ptr(lin.scale)
+    desc.x, desc.y = _ptr(x), _ptr(y)
+    desc.N, desc.K, desc.M, desc.reserved = lin.N, lin.K, M, 0
+
+
+def linear_multi(items: Sequence[Tuple[W4A16Linear, torch.Tensor, torch.Tensor]]) -> None:
+    """Up to four independent projections ``(linear, x, y)`` in one launch."""
+    arr = (_LinearStruct * len(items))()
+    for d, (lin, x, y) in zip(arr, items):
+        _fill(d, lin, x, y)
+    _check("linear_multi", load_library().cudalm_b200_linear_multi(arr, len(items), _stream()))
+
+
+def gate_up_bf16(gate: W4A16Linear, up: W4A16Linear, x: torch.Tensor,
+                 gate_y: Optional[torch.Tensor] = None,
+                 up_y: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The MLP's gate and up projections over the shared input in one launch
+    (CUDALM src/runtime/qwen35_deltanet.cpp:236-243 issues them as two calls)."""
+    _need(x, torch.bfloat16, "x")
+    if gate.N != up.N or gate.K != up.K:
+        raise ValueError("gate and up must have the same shape")
+    M = 1 if x.dim() == 1 else int(x.shape[0])
+    shape = (gate.N,) if x.dim() == 1 else (M, gate.N)
+    if gate_y is None:
+        gate_y = torch.empty(shape, dtype=torch.bfloat16, device=x.device)
+    if up_y is None:
+        up_y = torch.empty(shape, dtype=torch.bfloat16, device=x.device)
+    st = load_library().cudalm_b200_gate_up_bf16(
+        _ptr(gate.weight), _ptr(gate.scale), _ptr(up.weight), _ptr(up.scale), _ptr(x),
+        _ptr(gate_y), _ptr(up_y), gate.N, gate.K, M, _stream())
+    _check("gate_up_bf16", st)
+    return gate_y, up_y
+
+
+class LinearGroup:
+    """Any number of independent projections run by one launch.  The
+    descriptor table lives on the device; ``run()`` only launches."""
+
+    def __init__(self, items: Sequence[Tuple[W4A16Linear, torch.Tensor, torch.Tensor]]):
+        arr = (_LinearStruct * len(items))()
+        for d, (lin, x, y) in zip(arr, items):
+            _fill(d, lin, x, y)
+        self._keep = list(items)  # the tensors must outlive the group
+        handle = _vp()
+        _check("group_create",
+               load_library().cudalm_b200_group_create(arr, len(items), ctypes.byref(handle)))
+        self._handle = handle
+
+    @property
+    def bytes(self) -> int:
+        return int(load_library().cudalm_b200_group_bytes(self._handle))
+
+    def run(self) -> None:
+        _check("group_run", load_library().cudalm_b200_group_run(self._handle, _stream()))
+
+    def close(self) -> None:
+        if self._handle is not None:
+            h, self._handle = self._handle, None
+            _check("group_destroy", load_library().cudalm_b200_group_destroy(h))
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def quantize_w4a16(W: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """bf16 ``W [N, K]`` -> (packed uint8 ``[N, K/2]``, fp16 scale ``[N, K/128]``),
+    bit-exact with CUDALM tools/common/w4a16_quant.py:25-60 (which also returns
+    the unpacked q and the fp32 scale; those are not produced here)."""
+    if W.dim() != 2:
+        raise ValueError(f"expected 2-D W, got {W.dim()}D")
+    _need(W, torch.bfloat16, "W")
+    N, K = int(W.shape[0]), int(W.shape[1])
+    if K % GROUP_SIZE != 0:
+        raise ValueError(f"K must be a multiple of {GROUP_SIZE}, got {K}")
+    packed = torch.empty((N, K // 2), dtype=torch.uint8, device=W.device)
+    scale = torch.empty((N, K // GROUP_SIZE), dtype=torch.float16, device=W.device)
+    st = load_library().cudalm_b200_quantize_w4a16(_ptr(W), N, K, _ptr(packed), _ptr(scale), _stream())
+    _check("quantize_w4a16", st)
+    return packed, scale
+
+
+class LmHead:
+    """Vocabulary projection stored as W4A16 with an on-device pick.
+
+    ``rows`` are this rank's vocabulary rows; ``id_offset`` is the token id of
+    row 0.  ``forward(x)`` returns ``(argmax [M] int32, topk_idx [M, k] int32,
+    topk_val [M, k] bf16)``, ordered by value descending with ties to the lower
+    id (CUDALM include/cudalm/greedy.h:28-39, include/cudalm/sampling.h:152-166).
+    """
+
+    def __init__(self, rows: W4A16Linear, top_k: int = 50, id_offset: int = 0,
+                 max_rows: int = 32, keep_logits: bool = False):
+        if not 1 <= top_k <= MAX_TOP_K:
+            raise ValueError(f"top_k must be in 1..{MAX_TOP_K}")
+        self.rows, self.top_k, self.id_offset = rows, top_k, id_offset
+        self.max_rows = max_rows
+        dev = rows.weight.device
+        self.logits = (torch.empty((max_rows, rows.N), dtype=torch.bfloat16, device=dev)
+                       if keep_logits else None)
+        nbytes = int(load_library().cudalm_b200_lm_head_workspace_bytes(
+            rows.N, rows.K, max_rows, top_k, 0 if keep_logits else 1))
+        # 256-byte aligned by the caching allocator (512-byte granularity)
+        self.workspace = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        self.argmax = torch.empty(max_rows, dtype=torch.int32, device=dev)
+        self.topk_idx = torch.empty((max_rows, top_k), dtype=torch.int32, device=dev)
+        self.topk_val = torch.empty((max_rows, top_k), dtype=torch.bfloat16, device=dev)
+
+    def forward(self, x: torch.Tensor):
+        _need(x, torch.bfloat16, "x")
+        M = 1 if x.dim() == 1 else int(x.shape[0])
+        if M > self.max_rows:
+            raise ValueError(f"M={M} exceeds max_rows={self.max_rows}")
+        st = load_library().cudalm_b200_lm_head_topk(
+            _ptr(self.rows.weight), _ptr(self.rows.scale), _ptr(x), self.rows.N, self.rows.K, M,
+            self.top_k, self.id_offset, _ptr(self.logits), _ptr(self.argmax),
+            _ptr(self.topk_idx), _ptr(self.topk_val), _ptr(self.workspace),
+            self.workspace.numel(), _stream())
+        _check("lm_head_topk", st)
+        return self.argmax[:M], self.topk_idx[:M], self.topk_val[:M]
+
+
+def topk_merge(list_idx: torch.Tensor, list_val: torch.Tensor):
+    """Merges ``[L, M, k]`` candidate lists (ids < 0 are padding) into the final
+    ``(argmax [M], topk_idx [M, k], topk_val [M, k])``."""
+    _need(list_idx, torch.int32, "list_idx")
+    _need(list_val, torch.bfloat16, "list_val")
+    L, M, k = (int(v) for v in list_idx.shape)
+    dev = list_idx.device
+    argmax = torch.empty(M, dtype=torch.int32, device=dev)
+    idx = torch.empty((M, k), dtype=torch.int32, device=dev)
+    val = torch.empty((M, k), dtype=torch.bfloat16, device=dev)
+    st = load_library().cudalm_b200_topk_merge(_ptr(list_idx), _ptr(list_val), L, M, k,
+                                               _ptr(argmax), _ptr(idx), _ptr(val), _stream())
+    _check("topk_merge", st)
+    return argmax, idx, val

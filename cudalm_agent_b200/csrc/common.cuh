@@ -1,0 +1,203 @@
+// Shared device/host helpers for the W4A16 projection kernels (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdint>
+
+#include "../../include/cudalm_b200.h"
+
+#if defined(__CUDA_ARCH__) && (__CUDA_ARCH__ < 1000)
+#error "this library is written for sm_100a (B200) only"
+#endif
+
+namespace cb200 {
+
+// ---------------------------------------------------------------------------
+// Host-side bookkeeping
+// ---------------------------------------------------------------------------
+extern thread_local int g_last_cuda_error;
+extern std::atomic<long long> g_launch_count;
+// Device-side status word of the current device (bounded waits report here).
+int* device_status_word();
+int num_sms();
+
+#define CB200_CUDA_TRY(call)                                  \
+  do {                                                        \
+    cudaError_t cb200_e__ = (call);                           \
+    if (cb200_e__ != cudaSuccess) {                           \
+      ::cb200::g_last_cuda_error = static_cast<int>(cb200_e__); \
+      return CUDALM_B200_ERR_CUDA;                            \
+    }                                                         \
+  } while (0)
+
+inline int check_launch() {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    g_last_cuda_error = static_cast<int>(e);
+    return CUDALM_B200_ERR_CUDA;
+  }
+  g_launch_count.fetch_add(1, std::memory_order_relaxed);
+  return CUDALM_B200_OK;
+}
+
+inline bool aligned_to(const void* p, std::uintptr_t a) {
+  return (reinterpret_cast<std::uintptr_t>(p) & (a - 1)) == 0;
+}
+
+// Largest dynamic shared memory a CTA may opt into on B200 (227 KB).
+constexpr int kMaxSmemBytes = 232448;
+
+// ---------------------------------------------------------------------------
+// Device helpers
+// ---------------------------------------------------------------------------
+#ifdef __CUDACC__
+
+__device__ __forceinline__ std::uint32_t smem_u32(const void* p) {
+  return static_cast<std::uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// ---- mbarrier (shared::cta) ------------------------------------------------
+__device__ __forceinline__ void mbar_init(std::uint64_t* bar, std::uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(count)
+               : "memory");
+}
+// Makes freshly initialised barriers visible to the async (bulk-copy) proxy.
+__device__ __forceinline__ void mbar_init_fence() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(std::uint64_t* bar,
+                                                      std::uint32_t tx_bytes) {
+  asm volatile(
+      "mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+      "r"(tx_bytes)
+      : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(std::uint64_t* bar,
+                                              std::uint32_t parity) {
+  std::uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: gives up after `limit` polls (each poll itself blocks for a
+// hardware-defined short time) and returns false; the caller then records a
+// timeout instead of spinning forever.
+__device__ __forceinline__ bool mbar_wait_bounded(std::uint64_t* bar,
+                                                  std::uint32_t parity,
+                                                  std::uint32_t limit) {
+  for (std::uint32_t i = 0; i < limit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+  }
+  return false;
+}
+
+// ---- bulk async copy global -> shared (TMA engine, untiled form) -----------
+// dst and src 16-byte aligned, bytes a multiple of 16.  Completion is
+// signalled on `bar` as `bytes` of transaction count.
+__device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src,
+                                         std::uint32_t bytes, std::uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1], %2, [%3];" ::"r"(smem_u32(smem_dst)),
+      "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+// Same, with an L2 eviction-priority hint (weights are streamed once).
+__device__ __forceinline__ void bulk_g2s_hint(void* smem_dst, const void* gmem_src,
+                                              std::uint32_t bytes,
+                                              std::uint64_t* bar,
+                                              std::uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes"
+      ".L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(smem_u32(smem_dst)),
+      "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ std::uint64_t policy_evict_first() {
+  std::uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+
+// ---- shared-memory loads ---------------------------------------------------
+__device__ __forceinline__ uint4 lds128(std::uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint2 lds64(std::uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ std::uint16_t lds16(std::uint32_t addr) {
+  std::uint16_t v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+  return v;
+}
+
+// ---- int4 -> bf16 dequantisation --------------------------------------------
+// For a 32-bit word holding eight 4-bit two's-complement values n0..n7 (n_i at
+// bits 4i), produces four bf16x2 registers: out[i] = { q(n_i), q(n_{i+4}) }
+// (low half, high half), exact integers in [-8, 7].
+//
+// (n ^ 8) is q + 8 in [0, 15]; OR-ing it under the bf16 pattern 0x4300 (128.0,
+// whose ulp is 1) gives the bf16 number 136 + q; subtracting 136.0 (0x4308)
+// is exact.  One LOP3 computes (w & 0x000F000F) ^ 0x43084308 for two nibbles.
+__device__ __forceinline__ std::uint32_t lop3_and_xor(std::uint32_t a,
+                                                      std::uint32_t b,
+                                                      std::uint32_t c) {
+  std::uint32_t d;
+  asm("lop3.b32 %0, %1, %2, %3, 0x6a;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ __forceinline__ std::uint32_t sub_bf16x2(std::uint32_t a, std::uint32_t b) {
+  std::uint32_t d;
+  asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ void dequant_word_bf16x2(std::uint32_t w,
+                                                    std::uint32_t (&out)[4]) {
+  constexpr std::uint32_t kMask = 0x000F000Fu;
+  constexpr std::uint32_t kMagic = 0x43084308u;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    out[i] = sub_bf16x2(lop3_and_xor(w >> (4 * i), kMask, kMagic), kMagic);
+  }
+}
+
+// ---- legacy-path tensor-core MMA (m16n8k16, bf16 x bf16 -> fp32) -------------
+__device__ __forceinline__ void mma_m16n8k16_bf16(float (&c)[4], std::uint32_t a0,
+                                                  std::uint32_t a1, std::uint32_t a2,
+                                                  std::uint32_t a3, std::uint32_t b0,
+                                                  std::uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 "
+      "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ float bf16_bits_to_float(std::uint16_t b) {
+  return __uint_as_float(static_cast<std::uint32_t>(b) << 16);
+}
+__device__ __forceinline__ std::uint16_t float_to_bf16_bits(float f) {
+  return __bfloat16_as_ushort(__float2bfloat16_rn(f));
+}
+
+#endif  // __CUDACC__
+
+}  // namespace cb200

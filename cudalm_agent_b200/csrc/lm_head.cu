@@ -1,0 +1,386 @@
+// Vocabulary projection with an on-device token pick: W4A16 GEMV over the
+// vocabulary rows, then argmax and top-k per activation row.
+//
+// Ordering rule (CUDALM include/cudalm/greedy.h:28-39 and
+// include/cudalm/sampling.h:152-166): candidates are ordered by their bf16
+// logit value, descending, compared as floats (so -0 ties with +0); ties go to
+// the lower token id.  Element 0 of the top-k list is therefore the argmax.
+//
+// Three launches per call, all on the caller's stream:
+//   1. the streaming projection kernel writes the bf16 logits and, per CTA and
+//      activation row, the largest logit that CTA produced;
+//   2. collect: the k-th largest of those per-CTA maxima is a lower bound on the
+//      k-th largest logit (each maximum is a distinct logit), so only logits
+//      at or above it can be in the top-k; they are appended to a per-row
+//      candidate list (typically 50-150 entries out of the whole vocabulary);
+//   3. select: one CTA per row sorts its candidates by (value desc, id asc) and
+//      writes the first k.  A row whose candidate list overflowed (e.g. all
+//      logits equal) is redone by an exact search over the full row.
+//
+// Candidates are 64-bit composites: bits 63..48 = the bf16 logit mapped to an
+// unsigned key that grows with the value, bits 47..16 = ~id, bits 15..0 = the
+// logit's original bits, so that one unsigned compare implements the ordering
+// rule and the value can be reported unchanged.
+#include <cstring>
+
+#include "common.cuh"
+
+namespace cb200 {
+
+int run_linear_with_cta_max(const cudalm_b200_linear& l, float* cta_max, int* grid_out,
+                            cudaStream_t stream);
+int stream_rows_per_pass(int K);
+int run_linear_any(const cudalm_b200_linear& l, cudaStream_t stream);
+
+namespace {
+
+constexpr int kMaxTopK = 64;
+constexpr int kCandCap = 2048;     // candidate slots per row
+constexpr int kMaxPassRows = 32;   // activation rows per pass
+constexpr int kMaxCtas = 1024;     // per-CTA maxima slots
+constexpr int kSelectThreads = 256;
+
+// bf16 bits -> unsigned key that increases with the float value; -0 maps to +0.
+__device__ __forceinline__ std::uint32_t order_key(std::uint16_t bits) {
+  std::uint32_t b = bits;
+  if (b == 0x8000u) b = 0u;
+  return (b & 0x8000u) ? (~b & 0xFFFFu) : (b | 0x8000u);
+}
+__device__ __forceinline__ std::uint64_t make_composite(std::uint16_t bits, std::uint32_t id) {
+  return (static_cast<std::uint64_t>(order_key(bits)) << 48) |
+         (static_cast<std::uint64_t>(static_cast<std::uint32_t>(~id)) << 16) | bits;
+}
+__device__ __forceinline__ std::uint32_t composite_id(std::uint64_t c) {
+  return ~static_cast<std::uint32_t>(c >> 16);
+}
+__device__ __forceinline__ std::uint16_t composite_bits(std::uint64_t c) {
+  return static_cast<std::uint16_t>(c & 0xFFFFu);
+}
+
+struct Workspace {
+  int* counts;              // [kMaxPassRows]
+  float* cta_max;           // [kMaxCtas][rows]
+  std::uint64_t* cand;      // [rows][kCandCap]
+  std::uint16_t* logits;    // [rows][N] when the caller gave no logits buffer
+};
+
+constexpr size_t kCountsBytes = 256;
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+size_t workspace_layout(int N, int rows, bool need_logits, unsigned char* base, Workspace* ws) {
+  size_t off = 0;
+  if (ws) ws->counts = reinterpret_cast<int*>(base + off);
+  off += kCountsBytes;
+  if (ws) ws->cta_max = reinterpret_cast<float*>(base + off);
+  off += align_up(static_cast<size_t>(kMaxCtas) * rows * sizeof(float), 256);
+  if (ws) ws->cand = reinterpret_cast<std::uint64_t*>(base + off);
+  off += align_up(static_cast<size_t>(rows) * kCandCap * sizeof(std::uint64_t), 256);
+  if (ws) ws->logits = reinterpret_cast<std::uint16_t*>(base + off);
+  if (need_logits) off += align_up(static_cast<size_t>(rows) * N * sizeof(std::uint16_t), 256);
+  return off;
+}
+
+// ---------------------------------------------------------------------------
+// collect: grid (slices, rows).  Each CTA derives the row's bound from the
+// per-CTA maxima and scans its slice of the row's logits.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+lm_head_collect_kernel(const std::uint16_t* __restrict__ logits, int N, int rows,
+                       const float* __restrict__ cta_max, int ncta, int k, int id_offset,
+                       int* __restrict__ counts, std::uint64_t* __restrict__ cand) {
+  __shared__ float smax[kMaxCtas];
+  __shared__ float bound;
+  const int m = blockIdx.y;
+  const int tid = threadIdx.x;
+  for (int i = tid; i < ncta; i += blockDim.x) smax[i] = cta_max[static_cast<size_t>(i) * rows + m];
+  if (tid == 0) bound = -INFINITY;
+  __syncthreads();
+  if (ncta >= k) {
+    // the entry with exactly k-1 entries ahead of it (value desc, index asc)
+    for (int i = tid; i < ncta; i += blockDim.x) {
+      const float v = smax[i];
+      int ahead = 0;
+      for (int j = 0; j < ncta; ++j) {
+        const float u = smax[j];
+        ahead += (u > v) || (u == v && j < i);
+      }
+      if (ahead == k - 1) bound = v;
+    }
+  }
+  __syncthreads();
+  const float b = bound;
+  const std::uint16_t* row = logits + static_cast<size_t>(m) * N;
+  const long long per = (static_cast<long long>(N) + gridDim.x - 1) / gridDim.x;
+  const long long lo = per * blockIdx.x;
+  long long hi = lo + per;
+  if (hi > N) hi = N;
+  for (long long i = lo + tid; i < hi; i += blockDim.x) {
+    const std::uint16_t bits = row[i];
+    if (bf16_bits_to_float(bits) >= b) {
+      const int pos = atomicAdd(&counts[m], 1);
+      if (pos < kCandCap)
+        cand[static_cast<size_t>(m) * kCandCap + pos] =
+            make_composite(bits, static_cast<std::uint32_t>(id_offset) + static_cast<std::uint32_t>(i));
+    }
+  }
+}
+
+// Bitonic sort, descending, of n (a power of two) composites in shared memory.
+__device__ void bitonic_sort_desc(std::uint64_t* a, int n, int tid, int nthreads) {
+  for (int size = 2; size <= n; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      __syncthreads();
+      for (int i = tid; i < (n >> 1); i += nthreads) {
+        const int lo = 2 * i - (i & (stride - 1));
+        const int hi = lo + stride;
+        const bool desc = (lo & size) == 0;
+        const std::uint64_t x = a[lo], y = a[hi];
+        if ((x < y) == desc) {
+          a[lo] = y;
+          a[hi] = x;
+        }
+      }
+    }
+  }
+  __syncthreads();
+}
+
+// CTA-wide sum of one int per thread (result to every thread).
+__device__ int block_sum(int v, int* scratch, int tid, int nthreads) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+  __syncthreads();
+  if ((tid & 31) == 0) scratch[tid >> 5] = v;
+  __syncthreads();
+  int total = 0;
+  for (int w = 0; w < (nthreads >> 5); ++w) total += scratch[w];
+  return total;
+}
+
+// ---------------------------------------------------------------------------
+// select: one CTA per row.  Also used to merge already-selected lists (the
+// vocabulary-parallel case), which arrive as (id, bf16 value) pairs.
+// ---------------------------------------------------------------------------
+struct SelectArgs {
+  // candidate source A: composites collected by lm_head_collect_kernel
+  const std::uint64_t* cand;
+  const int* counts;
+  // candidate source B: lists[l][m][k] of ids and values (ids < 0 are padding)
+  const std::int32_t* list_idx;
+  const std::uint16_t* list_val;
+  int n_lists;
+  int list_k;
+  // full logits of this shard, for the exact search after an overflow
+  const std::uint16_t* logits;
+  int N;
+  int id_offset;
+  int rows;
+  int k;
+  std::int32_t* argmax_out;
+  std::int32_t* topk_idx;
+  std::uint16_t* topk_val;
+};
+
+__global__ void __launch_bounds__(kSelectThreads)
+lm_head_select_kernel(const SelectArgs a) {
+  __shared__ std::uint64_t buf[kCandCap];
+  __shared__ int scratch[kSelectThreads / 32];
+  __shared__ int s_take;
+  const int m = blockIdx.x;
+  const int tid = threadIdx.x;
+  int n = 0;
+  bool overflow = false;
+  if (a.cand) {
+    n = a.counts[m];
+    overflow = n > kCandCap;
+    if (!overflow)
+      for (int i = tid; i < n; i += kSelectThreads) buf[i] = a.cand[static_cast<size_t>(m) * kCandCap + i];
+  } else {
+    n = a.n_lists * a.list_k;  // host guarantees n <= kCandCap
+    for (int i = tid; i < n; i += kSelectThreads) {
+      const int l = i / a.list_k, j = i - l * a.list_k;
+      const size_t src = (static_cast<size_t>(l) * a.rows + m) * a.list_k + j;
+      const std::int32_t id = a.list_idx[src];
+      buf[i] = id < 0 ? 0ull : make_composite(a.list_val[src], static_cast<std::uint32_t>(id));
+    }
+  }
+
+  if (overflow) {
+    // Exact search over the whole row.  (1) bisection on the 16-bit value key
+    // for the k-th largest value; (2) everything above it is taken; (3) of the
+    // entries equal to it, the lowest ids are taken by an ordered scan.
+    const std::uint16_t* row = a.logits + static_cast<size_t>(m) * a.N;
+    const int kk = a.k < a.N ? a.k : a.N;
+    std::uint32_t T = 0;
+    for (int bit = 15; bit >= 0; --bit) {
+      const std::uint32_t trial = T | (1u << bit);
+      int c = 0;
+      for (int i = tid; i < a.N; i += kSelectThreads) c += order_key(row[i]) >= trial;
+      if (block_sum(c, scratch, tid, kSelectThreads) >= kk) T = trial;
+    }
+    int c = 0;
+    for (int i = tid; i < a.N; i += kSelectThreads) c += order_key(row[i]) > T;
+    const int n_gt = block_sum(c, scratch, tid, kSelectThreads);
+    if (tid == 0) s_take = 0;
+    __syncthreads();
+    // entries above T: any order (sorted below)
+    for (int i = tid; i < a.N; i += kSelectThreads) {
+      if (order_key(row[i]) > T) {
+        const int pos = atomicAdd(&s_take, 1);
+        buf[pos] = make_composite(row[i], static_cast<std::uint32_t>(a.id_offset + i));
+      }
+    }
+    __syncthreads();
+    // entries equal to T, in id order, until kk are taken
+    int need = kk - n_gt;
+    for (int base = 0; base < a.N && need > 0; base += kSelectThreads) {
+      const int i = base + tid;
+      const bool eq = i < a.N && order_key(row[i]) == T;
+      // rank of this thread among the block's matches
+      const unsigned ballot = __ballot_sync(0xffffffffu, eq);
+      __syncthreads();
+      if ((tid & 31) == 0) scratch[tid >> 5] = __popc(ballot);
+      __syncthreads();
+      int before = 0, total = 0;
+      for (int w = 0; w < kSelectThreads / 32; ++w) {
+        if (w < (tid >> 5)) before += scratch[w];
+        total += scratch[w];
+      }
+      const int rank = before + __popc(ballot & ((1u << (tid & 31)) - 1u));
+      if (eq && rank < need)
+        buf[n_gt + (kk - n_gt - need) + rank] =
+            make_composite(row[i], static_cast<std::uint32_t>(a.id_offset + i));
+      need -= total < need ? total : need;
+    }
+    n = kk;
+    __syncthreads();
+  }
+
+  // pad to a power of two (at least 64) with zeros, which sort last
+  int P = 64;
+  while (P < n) P <<= 1;
+  __syncthreads();
+  for (int i = n + tid; i < P; i += kSelectThreads) buf[i] = 0ull;
+  bitonic_sort_desc(buf, P, tid, kSelectThreads);
+
+  const int kk = a.k;
+  for (int j = tid; j < kk; j += kSelectThreads) {
+    const std::uint64_t c = buf[j];
+    const bool real = (j < n) && c != 0ull;
+    a.topk_idx[static_cast<size_t>(m) * kk + j] = real ? static_cast<std::int32_t>(composite_id(c)) : -1;
+    a.topk_val[static_cast<size_t>(m) * kk + j] =
+        real ? composite_bits(c) : static_cast<std::uint16_t>(0xFF80u);
+    if (j == 0 && a.argmax_out) a.argmax_out[m] = real ? static_cast<std::int32_t>(composite_id(c)) : -1;
+  }
+}
+
+__global__ void zero_counts_kernel(int* counts, int n) {
+  if (threadIdx.x < n) counts[threadIdx.x] = 0;
+}
+
+}  // namespace
+}  // namespace cb200
+
+using namespace cb200;
+
+extern "C" {
+
+size_t cudalm_b200_lm_head_workspace_bytes(int N, int K, int M, int top_k, int need_logits) {
+  (void)K;
+  (void)top_k;
+  if (N < 1 || M < 1) return 0;
+  const int rows = M < kMaxPassRows ? M : kMaxPassRows;
+  return workspace_layout(N, rows, need_logits != 0, nullptr, nullptr);
+}
+
+int cudalm_b200_lm_head_topk(const uint8_t* weight, const uint16_t* scales, const uint16_t* x,
+                             int N, int K, int M, int top_k, int id_offset,
+                             uint16_t* logits_out, int32_t* argmax_out, int32_t* topk_idx,
+                             uint16_t* topk_val, void* workspace, size_t workspace_bytes,
+                             void* stream) {
+  if (!weight || !scales || !x || !topk_idx || !topk_val) return CUDALM_B200_ERR_NULL;
+  if (N < 1 || K <= 0 || (K % 128) != 0 || M < 1 || id_offset < 0) return CUDALM_B200_ERR_BAD_SHAPE;
+  if (top_k < 1 || top_k > kMaxTopK) return CUDALM_B200_ERR_TOO_LARGE;
+  if (!workspace) return CUDALM_B200_ERR_WORKSPACE;
+  if (!aligned_to(workspace, 256)) return CUDALM_B200_ERR_MISALIGNED;
+  if (workspace_bytes < cudalm_b200_lm_head_workspace_bytes(N, K, M, top_k, logits_out == nullptr))
+    return CUDALM_B200_ERR_WORKSPACE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+  int per_pass = stream_rows_per_pass(K);
+  if (per_pass > kMaxPassRows) per_pass = kMaxPassRows;
+  const bool staged = per_pass > 0 && aligned_to(weight, 16);
+  if (!staged) per_pass = kMaxPassRows;
+  const int rows_cap = M < kMaxPassRows ? M : kMaxPassRows;
+
+  for (int m0 = 0; m0 < M; m0 += per_pass) {
+    const int rows = (M - m0 < per_pass) ? (M - m0) : per_pass;
+    Workspace ws;
+    workspace_layout(N, rows_cap, logits_out == nullptr, static_cast<unsigned char*>(workspace), &ws);
+    // the maxima table is indexed [cta][rows of this pass]
+    uint16_t* logits = logits_out ? logits_out + static_cast<size_t>(m0) * N : ws.logits;
+    cudalm_b200_linear l{weight, scales, x + static_cast<size_t>(m0) * K, logits, N, K, rows, 0};
+
+    zero_counts_kernel<<<1, 64, 0, st>>>(ws.counts, kMaxPassRows);
+    if (int rc = check_launch()) return rc;
+
+    int ncta = 0;
+    if (staged) {
+      if (int rc = run_linear_with_cta_max(l, ws.cta_max, &ncta, st)) return rc;
+      if (ncta > kMaxCtas) return CUDALM_B200_ERR_TOO_LARGE;
+    } else {
+      // no per-CTA maxima on the slow path: every logit is a candidate, and a
+      // row longer than the candidate list takes the exact search
+      if (int rc = run_linear_any(l, st)) return rc;
+      ncta = 0;
+    }
+
+    int slices = (N + 4095) / 4096;
+    const int cap = num_sms() * 8 / rows > 1 ? num_sms() * 8 / rows : 1;
+    if (slices > cap) slices = cap;
+    if (slices < 1) slices = 1;
+    lm_head_collect_kernel<<<dim3(slices, rows), 256, 0, st>>>(logits, N, rows, ws.cta_max, ncta,
+                                                               top_k, id_offset, ws.counts, ws.cand);
+    if (int rc = check_launch()) return rc;
+
+    SelectArgs a;
+    std::memset(&a, 0, sizeof(a));
+    a.cand = ws.cand;
+    a.counts = ws.counts;
+    a.logits = logits;
+    a.N = N;
+    a.id_offset = id_offset;
+    a.rows = rows;
+    a.k = top_k;
+    a.argmax_out = argmax_out ? argmax_out + m0 : nullptr;
+    a.topk_idx = topk_idx + static_cast<size_t>(m0) * top_k;
+    a.topk_val = topk_val + static_cast<size_t>(m0) * top_k;
+    lm_head_select_kernel<<<rows, kSelectThreads, 0, st>>>(a);
+    if (int rc = check_launch()) return rc;
+  }
+  return CUDALM_B200_OK;
+}
+
+int cudalm_b200_topk_merge(const int32_t* list_idx, const uint16_t* list_val, int n_lists, int M,
+                           int k, int32_t* argmax_out, int32_t* topk_idx, uint16_t* topk_val,
+                           void* stream) {
+  if (!list_idx || !list_val || !topk_idx || !topk_val) return CUDALM_B200_ERR_NULL;
+  if (n_lists < 1 || M < 1 || k < 1) return CUDALM_B200_ERR_BAD_SHAPE;
+  if (k > kMaxTopK || static_cast<long long>(n_lists) * k > kCandCap) return CUDALM_B200_ERR_TOO_LARGE;
+  SelectArgs a;
+  std::memset(&a, 0, sizeof(a));
+  a.list_idx = list_idx;
+  a.list_val = list_val;
+  a.n_lists = n_lists;
+  a.list_k = k;
+  a.rows = M;
+  a.k = k;
+  a.argmax_out = argmax_out;
+  a.topk_idx = topk_idx;
+  a.topk_val = topk_val;
+  lm_head_select_kernel<<<M, kSelectThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  return check_launch();
+}
+
+}  // extern "C"

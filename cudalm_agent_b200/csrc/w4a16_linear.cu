@@ -1,0 +1,405 @@
+// W4A16 linear projections: M = 1 GEMV, batched rows, several projections per
+// launch, fused gate+up.  Host entry points of the C ABI plus the streaming
+// kernel they launch.
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <vector>
+
+#include "w4a16_stream.cuh"
+
+namespace cb200 {
+
+// ---------------------------------------------------------------------------
+// Fallback for inputs the streaming kernel does not take: a weight base that is
+// not 16-byte aligned (CUDALM src/kernels/int4_gemv_bf16.cu:174-213 keeps such
+// calls legal) or K above the staged limit.  One warp per output row, byte
+// loads, fp32 accumulation in a fixed order.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+w4a16_fallback_kernel(const std::uint8_t* __restrict__ W, const std::uint16_t* __restrict__ S,
+                      const std::uint16_t* __restrict__ x, std::uint16_t* __restrict__ y, int N,
+                      int K, int M) {
+  const int lane = threadIdx.x & 31;
+  const long long row = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= N) return;
+  const std::uint8_t* wrow = W + row * (K >> 1);
+  const std::uint16_t* srow = S + row * (K >> 7);
+  for (int m = 0; m < M; ++m) {
+    const std::uint16_t* xm = x + static_cast<std::size_t>(m) * K;
+    float acc = 0.f;
+    for (int g = 0; g < (K >> 7); ++g) {
+      const float s = __half2float(__ushort_as_half(srow[g]));
+      float part = 0.f;
+      for (int b = lane; b < 64; b += 32) {
+        const std::uint8_t byte = wrow[g * 64 + b];
+        const int lo = static_cast<int>(static_cast<std::int8_t>((byte & 0x0Fu) << 4)) >> 4;
+        const int hi = static_cast<int>(static_cast<std::int8_t>(byte)) >> 4;
+        const int k = g * 128 + 2 * b;
+        part = fmaf(static_cast<float>(lo), bf16_bits_to_float(xm[k]), part);
+        part = fmaf(static_cast<float>(hi), bf16_bits_to_float(xm[k + 1]), part);
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
+      acc = fmaf(s, part, acc);
+    }
+    if (lane == 0) y[static_cast<std::size_t>(m) * N + row] = float_to_bf16_bits(acc);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+namespace {
+
+constexpr int kCG = 4;               // groups per chunk (512 values of k)
+constexpr int kRS = kCG * 64 + 64;   // stage row stride
+constexpr int kMaxStreamK = 4096;    // largest K the staged path takes
+
+inline int round_up(int v, int a) { return (v + a - 1) / a * a; }
+
+struct Plan {
+  int nt;       // MMA column tiles: activations rows per pass = 8 * nt
+  int nwarps;   // 16 or 8
+  int depth;
+  int stage_bytes;
+  int x_bytes;
+  int smem_bytes;
+};
+
+// Chooses the kernel shape for the largest K and M of a launch.  Returns false
+// when even 8 rows of activations do not fit beside the rings.
+bool make_plan(int kmax, int mmax, Plan* out) {
+  const int stage = kMTileRows * kRS + round_up(kmax / 4, 128);
+  int nt = 1;
+  while (nt * 8 < mmax && nt < 8) nt *= 2;
+  // at least 4 KB: the region doubles as reduction scratch at the kernel's end
+  int x_bytes = round_up(mmax * (2 * kmax + 32), 128);
+  if (x_bytes < 4096) x_bytes = 4096;
+  for (int nwarps : {16, 8}) {
+    if (nt == 8 && nwarps == 16) continue;  // 32 accumulators per lane need the larger register budget
+    const int fixed = nwarps * kMaxDepth * 8 + x_bytes;
+    const int avail = kMaxSmemBytes - fixed;
+    if (avail < 2 * nwarps * stage) continue;
+    int depth = avail / (nwarps * stage);
+    if (depth > kMaxDepth) depth = kMaxDepth;
+    *out = Plan{nt, nwarps, depth, stage, x_bytes, fixed + nwarps * depth * stage};
+    return true;
+  }
+  return false;
+}
+
+// Largest number of activation rows one pass can take for this K.
+int max_rows_per_pass(int k) {
+  int best = 0;
+  for (int m : {8, 16, 32, 64}) {
+    Plan pl;
+    if (make_plan(k, m, &pl)) best = m;
+  }
+  return best;
+}
+
+template <int NT, int NWARPS, bool CTA_MAX>
+int launch_instance(const StreamParams& p, const Plan& pl, int grid, cudaStream_t stream) {
+  auto kern = w4a16_stream_kernel<NT, kCG, NWARPS, CTA_MAX>;
+  // the attribute is per device; set it on every device this process uses
+  static std::mutex mu;
+  static std::vector<int> done_devices;
+  int dev = 0;
+  CB200_CUDA_TRY(cudaGetDevice(&dev));
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    bool done = false;
+    for (int d : done_devices) done |= (d == dev);
+    if (!done) {
+      const cudaError_t attr_err = cudaFuncSetAttribute(
+          kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmemBytes);
+      if (attr_err != cudaSuccess) {
+        g_last_cuda_error = static_cast<int>(attr_err);
+        return CUDALM_B200_ERR_CUDA;
+      }
+      done_devices.push_back(dev);
+    }
+  }
+  kern<<<grid, NWARPS * 32, pl.smem_bytes, stream>>>(p);
+  return check_launch();
+}
+
+int launch_stream(StreamParams& p, int kmax, int mmax, cudaStream_t stream,
+                  int* grid_out = nullptr) {
+  Plan pl;
+  if (!make_plan(kmax, mmax, &pl)) return CUDALM_B200_ERR_UNSUPPORTED;
+  p.depth = pl.depth;
+  p.stage_bytes = pl.stage_bytes;
+  p.x_bytes = pl.x_bytes;
+  p.status = device_status_word();
+  if (p.status == nullptr) return CUDALM_B200_ERR_CUDA;
+  int grid = num_sms();
+  if (grid > p.total_mt) grid = p.total_mt;
+  if (grid < 1) grid = 1;
+  if (grid_out) *grid_out = grid;
+  const bool want_max = p.cta_max != nullptr;
+#define CB200_CASE(NT_, NW_)                                                        \
+  if (pl.nt == NT_ && pl.nwarps == NW_)                                             \
+    return want_max ? launch_instance<NT_, NW_, true>(p, pl, grid, stream)          \
+                    : launch_instance<NT_, NW_, false>(p, pl, grid, stream);
+  CB200_CASE(1, 16) CB200_CASE(2, 16) CB200_CASE(4, 16)
+  CB200_CASE(1, 8) CB200_CASE(2, 8) CB200_CASE(4, 8) CB200_CASE(8, 8)
+#undef CB200_CASE
+  return CUDALM_B200_ERR_UNSUPPORTED;
+}
+
+int validate(const cudalm_b200_linear& l) {
+  if (!l.weight || !l.scales || !l.x || !l.y) return CUDALM_B200_ERR_NULL;
+  if (l.N < 1 || l.K <= 0 || (l.K % 128) != 0 || l.M < 1) return CUDALM_B200_ERR_BAD_SHAPE;
+  return CUDALM_B200_OK;
+}
+
+bool stream_eligible(const cudalm_b200_linear& l) {
+  return aligned_to(l.weight, 16) && l.K <= kMaxStreamK;
+}
+
+LinearDev to_dev(const cudalm_b200_linear& l, int mt_begin) {
+  LinearDev d;
+  d.W = l.weight;
+  d.S = l.scales;
+  d.x = l.x;
+  d.y = l.y;
+  d.N = l.N;
+  d.K = l.K;
+  d.M = l.M;
+  d.mt_begin = mt_begin;
+  d.flags = aligned_to(l.scales, 16) ? kFlagScalesBulk : 0;
+  d.pad = 0;
+  return d;
+}
+
+int run_fallback(const cudalm_b200_linear& l, cudaStream_t stream) {
+  const int rows_per_block = 8;
+  const int grid = (l.N + rows_per_block - 1) / rows_per_block;
+  w4a16_fallback_kernel<<<grid, rows_per_block * 32, 0, stream>>>(l.weight, l.scales, l.x, l.y,
+                                                                  l.N, l.K, l.M);
+  return check_launch();
+}
+
+// One projection with any M: passes of as many rows as fit in shared memory.
+int run_single(cudalm_b200_linear l, cudaStream_t stream) {
+  if (int rc = validate(l)) return rc;
+  if (!stream_eligible(l)) return run_fallback(l, stream);
+  const int per_pass = max_rows_per_pass(l.K);
+  if (per_pass == 0) return run_fallback(l, stream);
+  const int M = l.M;
+  for (int m0 = 0; m0 < M; m0 += per_pass) {
+    cudalm_b200_linear part = l;
+    part.M = (M - m0 < per_pass) ? (M - m0) : per_pass;
+    part.x = l.x + static_cast<std::size_t>(m0) * l.K;
+    part.y = l.y + static_cast<std::size_t>(m0) * l.N;
+    StreamParams p;
+    std::memset(&p, 0, sizeof(p));
+    p.table = nullptr;
+    p.inl[0] = to_dev(part, 0);
+    p.n_desc = 1;
+    p.total_mt = (l.N + kMTileRows - 1) / kMTileRows;
+    if (int rc = launch_stream(p, l.K, part.M, stream)) return rc;
+  }
+  return CUDALM_B200_OK;
+}
+
+}  // namespace
+
+// Used by the vocabulary projection: one staged launch of a single projection
+// (M rows in one pass) that also records the per-CTA maxima.  Returns
+// ERR_UNSUPPORTED when the projection cannot take the staged path in one pass.
+int run_linear_with_cta_max(const cudalm_b200_linear& l, float* cta_max, int* grid_out,
+                            cudaStream_t stream) {
+  if (int rc = validate(l)) return rc;
+  if (!stream_eligible(l)) return CUDALM_B200_ERR_UNSUPPORTED;
+  if (max_rows_per_pass(l.K) < l.M) return CUDALM_B200_ERR_UNSUPPORTED;
+  StreamParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.inl[0] = to_dev(l, 0);
+  p.n_desc = 1;
+  p.total_mt = (l.N + kMTileRows - 1) / kMTileRows;
+  p.cta_max = cta_max;
+  return launch_stream(p, l.K, l.M, stream, grid_out);
+}
+
+int stream_rows_per_pass(int K) {
+  return (K > 0 && K % 128 == 0 && K <= kMaxStreamK) ? max_rows_per_pass(K) : 0;
+}
+
+int run_linear_any(const cudalm_b200_linear& l, cudaStream_t stream) { return run_single(l, stream); }
+
+}  // namespace cb200
+
+// ---------------------------------------------------------------------------
+// C ABI
+// ---------------------------------------------------------------------------
+using namespace cb200;
+
+struct cudalm_b200_group {
+  LinearDev* table_dev = nullptr;
+  int count = 0;
+  int total_mt = 0;
+  int kmax = 0;
+  int mmax = 0;
+  long long bytes = 0;
+  int device = 0;
+};
+
+extern "C" {
+
+int cudalm_b200_int4_gemv_bf16(const uint8_t* weight, const uint16_t* scales, const uint16_t* x,
+                               uint16_t* y, int N, int K, void* stream) {
+  cudalm_b200_linear l{weight, scales, x, y, N, K, 1, 0};
+  return run_single(l, static_cast<cudaStream_t>(stream));
+}
+
+int cudalm_b200_batch_int4_gemv_bf16(const uint8_t* weight, const uint16_t* scales,
+                                     const uint16_t* x, uint16_t* y, int N, int K, int B,
+                                     void* stream) {
+  cudalm_b200_linear l{weight, scales, x, y, N, K, B, 0};
+  return run_single(l, static_cast<cudaStream_t>(stream));
+}
+
+int cudalm_b200_linear_multi(const cudalm_b200_linear* linears, int count, void* stream) {
+  if (!linears) return CUDALM_B200_ERR_NULL;
+  if (count < 1 || count > CUDALM_B200_MAX_INLINE_LINEARS) return CUDALM_B200_ERR_BAD_SHAPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  bool all_stream = true;
+  int kmax = 0, mmax = 0;
+  for (int i = 0; i < count; ++i) {
+    if (int rc = validate(linears[i])) return rc;
+    if (linears[i].reserved != 0) return CUDALM_B200_ERR_BAD_SHAPE;
+    all_stream &= stream_eligible(linears[i]);
+    kmax = linears[i].K > kmax ? linears[i].K : kmax;
+    mmax = linears[i].M > mmax ? linears[i].M : mmax;
+  }
+  Plan pl;
+  if (!all_stream || mmax > CUDALM_B200_MAX_GROUP_M || !make_plan(kmax, mmax, &pl)) {
+    // not all of them fit one staged launch: run them one by one
+    for (int i = 0; i < count; ++i)
+      if (int rc = run_single(linears[i], st)) return rc;
+    return CUDALM_B200_OK;
+  }
+  StreamParams p;
+  std::memset(&p, 0, sizeof(p));
+  int mt = 0;
+  for (int i = 0; i < count; ++i) {
+    p.inl[i] = to_dev(linears[i], mt);
+    mt += (linears[i].N + kMTileRows - 1) / kMTileRows;
+  }
+  p.n_desc = count;
+  p.total_mt = mt;
+  return launch_stream(p, kmax, mmax, st);
+}
+
+int cudalm_b200_gate_up_bf16(const uint8_t* gate_weight, const uint16_t* gate_scales,
+                             const uint8_t* up_weight, const uint16_t* up_scales,
+                             const uint16_t* x, uint16_t* gate_y, uint16_t* up_y, int N, int K,
+                             int M, void* stream) {
+  if (M < 1) return CUDALM_B200_ERR_BAD_SHAPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // rows of x beyond what one launch holds go in further passes
+  int per_pass = (K > 0 && K % 128 == 0 && K <= kMaxStreamK) ? max_rows_per_pass(K) : 0;
+  if (per_pass == 0) per_pass = M;
+  for (int m0 = 0; m0 < M; m0 += per_pass) {
+    const int mm = (M - m0 < per_pass) ? (M - m0) : per_pass;
+    cudalm_b200_linear two[2] = {
+        {gate_weight, gate_scales, x ? x + static_cast<size_t>(m0) * K : x,
+         gate_y ? gate_y + static_cast<size_t>(m0) * N : gate_y, N, K, mm, 0},
+        {up_weight, up_scales, x ? x + static_cast<size_t>(m0) * K : x,
+         up_y ? up_y + static_cast<size_t>(m0) * N : up_y, N, K, mm, 0}};
+    if (int rc = cudalm_b200_linear_multi(two, 2, st)) return rc;
+  }
+  return CUDALM_B200_OK;
+}
+
+int cudalm_b200_group_create(const cudalm_b200_linear* linears, int count,
+                             cudalm_b200_group** group_out) {
+  if (!linears || !group_out) return CUDALM_B200_ERR_NULL;
+  if (count < 1) return CUDALM_B200_ERR_BAD_SHAPE;
+  std::vector<LinearDev> tbl(static_cast<size_t>(count));
+  int mt = 0, kmax = 0, mmax = 0;
+  long long bytes = 0;
+  for (int i = 0; i < count; ++i) {
+    const cudalm_b200_linear& l = linears[i];
+    if (int rc = validate(l)) return rc;
+    if (l.reserved != 0) return CUDALM_B200_ERR_BAD_SHAPE;
+    if (!aligned_to(l.weight, 16)) return CUDALM_B200_ERR_MISALIGNED;
+    if (l.K > kMaxStreamK || l.M > CUDALM_B200_MAX_GROUP_M) return CUDALM_B200_ERR_UNSUPPORTED;
+    tbl[static_cast<size_t>(i)] = to_dev(l, mt);
+    mt += (l.N + kMTileRows - 1) / kMTileRows;
+    kmax = l.K > kmax ? l.K : kmax;
+    mmax = l.M > mmax ? l.M : mmax;
+    bytes += static_cast<long long>(l.N) * (l.K / 2) + static_cast<long long>(l.N) * (l.K / 128) * 2 +
+             static_cast<long long>(l.M) * l.K * 2 + static_cast<long long>(l.M) * l.N * 2;
+  }
+  Plan pl;
+  if (!make_plan(kmax, mmax, &pl)) return CUDALM_B200_ERR_UNSUPPORTED;
+  cudalm_b200_group* g = new cudalm_b200_group();
+  g->count = count;
+  g->total_mt = mt;
+  g->kmax = kmax;
+  g->mmax = mmax;
+  g->bytes = bytes;
+  cudaError_t e = cudaGetDevice(&g->device);
+  if (e == cudaSuccess) e = cudaMalloc(&g->table_dev, sizeof(LinearDev) * tbl.size());
+  if (e == cudaSuccess)
+    e = cudaMemcpy(g->table_dev, tbl.data(), sizeof(LinearDev) * tbl.size(), cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) {
+    g_last_cuda_error = static_cast<int>(e);
+    if (g->table_dev) cudaFree(g->table_dev);
+    delete g;
+    return CUDALM_B200_ERR_CUDA;
+  }
+  *group_out = g;
+  return CUDALM_B200_OK;
+}
+
+int cudalm_b200_group_run(const cudalm_b200_group* group, void* stream) {
+  if (!group) return CUDALM_B200_ERR_NULL;
+  StreamParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.table = group->table_dev;
+  p.n_desc = group->count;
+  p.total_mt = group->total_mt;
+  return launch_stream(p, group->kmax, group->mmax, static_cast<cudaStream_t>(stream));
+}
+
+int cudalm_b200_group_destroy(cudalm_b200_group* group) {
+  if (!group) return CUDALM_B200_OK;
+  cudaError_t e = cudaFree(group->table_dev);
+  delete group;
+  if (e != cudaSuccess) {
+    g_last_cuda_error = static_cast<int>(e);
+    return CUDALM_B200_ERR_CUDA;
+  }
+  return CUDALM_B200_OK;
+}
+
+int64_t cudalm_b200_group_bytes(const cudalm_b200_group* group) {
+  return group ? group->bytes : 0;
+}
+
+int cudalm_b200_kernel_regs(const char* kernel_name) {
+  if (!kernel_name) return -1;
+  const void* fn = nullptr;
+#define CB200_NAME(NT_, NW_)                                                     \
+  if (std::strcmp(kernel_name, "w4a16_stream_nt" #NT_ "_w" #NW_) == 0)           \
+    fn = reinterpret_cast<const void*>(&w4a16_stream_kernel<NT_, kCG, NW_, false>);
+  CB200_NAME(1, 16) CB200_NAME(2, 16) CB200_NAME(4, 16)
+  CB200_NAME(1, 8) CB200_NAME(2, 8) CB200_NAME(4, 8) CB200_NAME(8, 8)
+#undef CB200_NAME
+  if (std::strcmp(kernel_name, "w4a16_fallback") == 0)
+    fn = reinterpret_cast<const void*>(&w4a16_fallback_kernel);
+  if (!fn) return -1;
+  cudaFuncAttributes attr;
+  if (cudaFuncGetAttributes(&attr, fn) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return -1;
+  }
+  return attr.numRegs;
+}
+
+}  // extern "C"

@@ -1,0 +1,184 @@
+/*
+ * cudalm_b200.h -- C ABI of the B200-native W4A16 projection engine.
+ *
+ * A drop-in for the CUDALM inference engine's int4-weight x bf16-activation
+ * linear path.  Every entry point takes plain pointers and sizes, enqueues work
+ * on the caller's CUDA stream and returns a status code; none of them aborts,
+ * synchronises, or (unless stated) allocates.  All tensor pointers are
+ * caller-owned DEVICE memory.
+ *
+ * Data layouts (CUDALM include/cudalm/kernels/int4_gemv_bf16.h:29-48):
+ *   weight  uint8 [N, K/2] row-major; low nibble = k = 2b, high nibble =
+ *           k = 2b+1; nibbles are 4-bit two's complement (0x8 decodes to -8)
+ *   scales  IEEE binary16 [N, K/128] row-major, one per 128 consecutive k
+ *   x       bfloat16 [K] or [M, K]
+ *   y       bfloat16 [N] or [M, N]
+ * Math:   y[m,n] = bf16_rn( sum_k float(q[n,k]) * float(scale[n,k/128]) *
+ *                           float(x[m,k]) ), fp32 accumulation, one rounding.
+ *
+ * 16-bit float data is passed as uint16_t* holding the raw bits so that this
+ * header needs no CUDA headers.  `stream` is a cudaStream_t passed as void*.
+ */
+#ifndef CUDALM_B200_H_
+#define CUDALM_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define CUDALM_B200_API __attribute__((visibility("default")))
+#else
+#define CUDALM_B200_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes.  CUDALM itself aborts on a contract violation
+ * (include/cudalm/cuda_check.h:53-63); this ABI reports it instead and the
+ * C++ shim in cudalm_b200_shims.hpp restores the abort for drop-in callers. */
+enum {
+  CUDALM_B200_OK = 0,
+  CUDALM_B200_ERR_BAD_SHAPE = 1,   /* N < 1, K <= 0, K % 128 != 0, M < 1, ... */
+  CUDALM_B200_ERR_NULL = 2,        /* a required pointer is null            */
+  CUDALM_B200_ERR_MISALIGNED = 3,  /* a pointer misses a stated alignment   */
+  CUDALM_B200_ERR_CUDA = 4,        /* a CUDA runtime call failed            */
+  CUDALM_B200_ERR_TIMEOUT = 5,     /* a bounded device-side wait ran out    */
+  CUDALM_B200_ERR_UNSUPPORTED = 6, /* legal in CUDALM but outside this build */
+  CUDALM_B200_ERR_TOO_LARGE = 7,   /* exceeds a stated fixed capacity       */
+  CUDALM_B200_ERR_WORKSPACE = 8    /* workspace missing or too small        */
+};
+
+CUDALM_B200_API const char* cudalm_b200_status_string(int status);
+/* cudaError_t of the most recent CUDALM_B200_ERR_CUDA on this host thread. */
+CUDALM_B200_API int cudalm_b200_last_cuda_error(void);
+/* Library build info: "sm_100a;<git-less build tag>". */
+CUDALM_B200_API const char* cudalm_b200_build_info(void);
+
+/* Reads (and clears) the device-side status word of the current device.  The
+ * kernels bound every wait; a wait that runs out stores ERR_TIMEOUT there and
+ * the kernel returns without touching its outputs further.  This call
+ * synchronises the device; it is for tests and diagnostics, not the hot path. */
+CUDALM_B200_API int cudalm_b200_device_status(int* status_out);
+
+/* ---- M = 1 GEMV -------------------------------------------------------
+ * Replaces cudalm::int4_gemv_bf16
+ * (CUDALM include/cudalm/kernels/int4_gemv_bf16.h:46-48,
+ *  src/kernels/int4_gemv_bf16.cu:221-243).
+ * Preconditions: N >= 1, K > 0, K % 128 == 0.  No alignment is required of
+ * any pointer (a weight base that is not 16-byte aligned takes a slower
+ * kernel, as in CUDALM). */
+CUDALM_B200_API int cudalm_b200_int4_gemv_bf16(const uint8_t* weight, const uint16_t* scales,
+                               const uint16_t* x, uint16_t* y, int N, int K,
+                               void* stream);
+
+/* ---- batched decode, M = B rows -----------------------------------------
+ * Replaces cudalm::kernels::batch_int4_gemv_bf16
+ * (CUDALM include/cudalm/kernels/batch_decode.h:61-63,
+ *  src/kernels/batch_decode.cu:95-190,647-659): x is [B, K], y is [B, N].
+ * Unlike CUDALM's, the weights are read once for all B rows. */
+CUDALM_B200_API int cudalm_b200_batch_int4_gemv_bf16(const uint8_t* weight,
+                                     const uint16_t* scales, const uint16_t* x,
+                                     uint16_t* y, int N, int K, int B,
+                                     void* stream);
+
+/* ---- several projections in one launch ------------------------------------
+ * One descriptor per projection.  Used for the projections of a layer that
+ * share an input (CUDALM src/runtime/qwen35_deltanet.cpp:166-181: qkv, z, b, a;
+ * src/runtime/qwen35_full_attention.cpp:211-231: q, k, v; the MLP's gate and
+ * up, qwen35_deltanet.cpp:236-243) and for streaming a whole model's set.
+ * The projections of one call must be independent of one another. */
+typedef struct cudalm_b200_linear {
+  const uint8_t* weight;  /* [N, K/2]            */
+  const uint16_t* scales; /* fp16 [N, K/128]     */
+  const uint16_t* x;      /* bf16 [M, K]         */
+  uint16_t* y;            /* bf16 [M, N]         */
+  int32_t N;
+  int32_t K;
+  int32_t M;              /* rows of x, 1..CUDALM_B200_MAX_GROUP_M */
+  int32_t reserved;       /* must be 0           */
+} cudalm_b200_linear;
+
+#define CUDALM_B200_MAX_INLINE_LINEARS 4
+#define CUDALM_B200_MAX_GROUP_M 64
+
+/* Up to CUDALM_B200_MAX_INLINE_LINEARS projections, descriptors in HOST
+ * memory, passed to the kernel by value: allocates nothing. */
+CUDALM_B200_API int cudalm_b200_linear_multi(const cudalm_b200_linear* linears, int count,
+                             void* stream);
+
+/* Any number of projections.  create() copies the descriptor table to the
+ * device (it allocates, and synchronises once); run() only launches. */
+typedef struct cudalm_b200_group cudalm_b200_group;
+CUDALM_B200_API int cudalm_b200_group_create(const cudalm_b200_linear* linears, int count,
+                             cudalm_b200_group** group_out);
+CUDALM_B200_API int cudalm_b200_group_run(const cudalm_b200_group* group, void* stream);
+CUDALM_B200_API int cudalm_b200_group_destroy(cudalm_b200_group* group);
+/* Algorithmic bytes one run() moves: sum of N*K/2 + N*(K/128)*2 + M*K*2 + M*N*2. */
+CUDALM_B200_API int64_t cudalm_b200_group_bytes(const cudalm_b200_group* group);
+
+/* ---- fused gate + up ------------------------------------------------------
+ * Replaces the two calls at CUDALM src/runtime/qwen35_deltanet.cpp:236-243 /
+ * src/runtime/qwen35_full_attention.cpp:317-326 with one launch over the shared
+ * input x [M, K]; gate_y and up_y are [M, N] each and equal the two separate
+ * calls row for row. */
+CUDALM_B200_API int cudalm_b200_gate_up_bf16(const uint8_t* gate_weight,
+                             const uint16_t* gate_scales,
+                             const uint8_t* up_weight, const uint16_t* up_scales,
+                             const uint16_t* x, uint16_t* gate_y, uint16_t* up_y,
+                             int N, int K, int M, void* stream);
+
+/* ---- vocabulary projection with on-device token pick --------------------------
+ * Replaces the lm_head call cudalm::bf16_gemv / kernels::batch_bf16_gemv
+ * (CUDALM include/cudalm/kernels/bf16_gemv.h:39-40,
+ *  include/cudalm/kernels/batch_decode.h:77-79; call sites
+ *  src/runtime/qwen35_model.cpp:177-181,290-292,500-502) and the host-side pick
+ * that follows it (src/runtime/scheduler.cpp:59-108, argmax_bf16 in
+ * include/cudalm/greedy.h:28-39, the top-k order of
+ * include/cudalm/sampling.h:152-166) for an lm_head stored as W4A16.
+ *
+ * weight/scales are this caller's rows [N, ...] of the vocabulary matrix;
+ * id_offset is the token id of row 0 (non-zero for a vocabulary-parallel shard).
+ * Outputs, per activation row m: argmax_out[m] (may be null), topk_idx[m][top_k]
+ * and topk_val[m][top_k] (bf16 bits) ordered by value descending, ties by lower
+ * id; when N < top_k the tail is filled with id -1.  logits_out (may be null) is
+ * the full bf16 logits [M, N], as CUDALM's call produces.  top_k <= 64.
+ * workspace: device memory, 256-byte aligned, of at least
+ * cudalm_b200_lm_head_workspace_bytes(..., need_logits = logits_out == NULL). */
+CUDALM_B200_API size_t cudalm_b200_lm_head_workspace_bytes(int N, int K, int M, int top_k,
+                                                           int need_logits);
+CUDALM_B200_API int cudalm_b200_lm_head_topk(
+    const uint8_t* weight, const uint16_t* scales, const uint16_t* x, int N, int K,
+    int M, int top_k, int id_offset, uint16_t* logits_out, int32_t* argmax_out,
+    int32_t* topk_idx, uint16_t* topk_val, void* workspace, size_t workspace_bytes,
+    void* stream);
+
+/* Merges n_lists candidate lists (one per vocabulary shard, gathered from the
+ * ranks) into the final pick: list_idx/list_val are [n_lists, M, k]; ids < 0 are
+ * padding.  Same ordering rule; n_lists * k <= 2048. */
+CUDALM_B200_API int cudalm_b200_topk_merge(const int32_t* list_idx, const uint16_t* list_val,
+                                           int n_lists, int M, int k, int32_t* argmax_out,
+                                           int32_t* topk_idx, uint16_t* topk_val,
+                                           void* stream);
+
+/* ---- quantize + pack --------------------------------------------------------
+ * GPU form of CUDALM's offline quantizer quantize_w4a16
+ * (CUDALM tools/common/w4a16_quant.py:25-60): bf16 W [N, K] ->
+ * packed int4 [N, K/2] and fp16 scales [N, K/128], bit-exact with it.
+ * W must be 16-byte aligned; packed 4-byte aligned. */
+CUDALM_B200_API int cudalm_b200_quantize_w4a16(const uint16_t* w_bf16, int N, int K,
+                               uint8_t* packed, uint16_t* scales, void* stream);
+
+/* ---- introspection ---------------------------------------------------------
+ * Registers per thread / static+dynamic shared memory of the named kernel
+ * (CUDALM exposes the same for its kernels: int4_gemv_bf16_rowtile4_regs(),
+ * src/kernels/int4_gemv_bf16.cu:247-253).  Returns -1 when unknown. */
+CUDALM_B200_API int cudalm_b200_kernel_regs(const char* kernel_name);
+/* Number of kernels this library has launched from the calling process. */
+CUDALM_B200_API int64_t cudalm_b200_launch_count(void);
+
+#ifdef __cplusplus
+} /* extern "C" */
+#endif
+#endif /* CUDALM_B200_H_ */

@@ -1,0 +1,83 @@
+"""Seeded input builders shared by the tests (numpy side; torch only to move bits)."""
+import numpy as np
+
+BASE_SEED = 20250922
+
+
+def bf16_bits(orc, a):
+    return orc.f32_to_bf16_bits(np.asarray(a, np.float32))
+
+
+def make_weights(orc, N, K, seed, std=0.02, threads=4):
+    """fp32 ~N(0, std) -> bf16 -> the oracle's quantizer (the benchmark recipe)."""
+    rng = np.random.default_rng(seed)
+    w = (rng.standard_normal((N, K), dtype=np.float32) * np.float32(std))
+    wb = orc.f32_to_bf16_bits(w)
+    packed, scale = orc.quantize_w4a16(wb, threads=threads)
+    return wb, packed, scale
+
+
+def raw_weights(N, K, seed, kind="random"):
+    """Full-domain packed bytes and scales, as the reference's kernel tests use
+    (tests/cuda/test_w4a16_qwen35_optimized.cpp:86-129)."""
+    rng = np.random.default_rng(seed)
+    if kind == "zero":
+        W = np.zeros((N, K // 2), np.uint8)
+    elif kind == "small":
+        W = (rng.integers(0, 3, (N, K // 2)) | (rng.integers(0, 3, (N, K // 2)) << 4)).astype(np.uint8)
+    elif kind == "boundary":
+        nib = np.array([0x7, 0x9, 0x8, 0x0, 0xF, 0x7, 0x8, 0xF], np.uint8)
+        W = (nib[rng.integers(0, 8, (N, K // 2))] | (nib[rng.integers(0, 8, (N, K // 2))] << 4)).astype(np.uint8)
+    else:
+        W = rng.integers(0, 256, (N, K // 2), dtype=np.uint8)
+    S = (0.001 + 0.02 * rng.random((N, K // 128))).astype(np.float16).view(np.uint16)
+    if kind == "boundary":
+        S[rng.random((N, K // 128)) < 0.2] = 0
+    return W, S
+
+
+def make_x(orc, shape, seed, kind="normal"):
+    rng = np.random.default_rng(seed)
+    if kind == "zero":
+        x = np.zeros(shape, np.float32)
+    elif kind == "small":
+        x = (0.01 * rng.random(shape) - 0.005).astype(np.float32)
+    elif kind == "outlier":
+        x = rng.standard_normal(shape).astype(np.float32)
+        x[rng.random(shape) < 0.01] *= 20.0
+    elif kind == "rmsnorm":
+        x = rng.standard_normal(shape).astype(np.float32)
+        x = x / np.sqrt((x * x).mean(axis=-1, keepdims=True))
+    elif kind == "uniform":
+        x = (rng.random(shape) * 2 - 1).astype(np.float32)
+    else:
+        x = rng.standard_normal(shape).astype(np.float32)
+    return orc.f32_to_bf16_bits(x)
+
+
+def to_dev(a, dtype=None):
+    import torch
+    t = torch.from_numpy(np.ascontiguousarray(a).view(np.int16) if a.dtype == np.uint16 else np.ascontiguousarray(a))
+    if a.dtype == np.uint16:
+        t = t.view(dtype)
+    return t.cuda()
+
+
+def from_dev(t):
+    import torch
+    if t.dtype in (torch.bfloat16, torch.float16):
+        return t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+    return t.cpu().numpy()
+
+
+def check_close(orc, got_bits, want_bits, label=""):
+    """Both gates: max|err| <= 1e-2 * RMS(want) (the benchmark's) and
+    |a - r| <= 1e-2 + 1e-2|r| (CUDALM include/cudalm/stage_compare.h:117-137)."""
+    got = orc.bf16_bits_to_f32(got_bits).astype(np.float64).ravel()
+    want = orc.bf16_bits_to_f32(want_bits).astype(np.float64).ravel()
+    assert np.all(np.isfinite(got)), label
+    err = np.abs(got - want)
+    rms = np.sqrt(np.mean(want * want))
+    assert err.max() <= 1e-2 * rms + 1e-30 or err.max() == 0, \
+        f"{label}: max err {err.max():.4g} > 1e-2 * rms {rms:.4g}"
+    assert np.all(err <= 1e-2 + 1e-2 * np.abs(want)), label
