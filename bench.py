@@ -32,7 +32,6 @@ import argparse
 import json
 import os
 import statistics
-import subprocess
 import sys
 import threading
 import time
@@ -68,54 +67,59 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while a region runs."""
-
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Samples SM clock and throttle reasons through NVML from a thread while
+    the timed region runs (a few ms between samples)."""
 
     def __init__(self, index: int):
-        self.index, self.proc, self.lines = index, None, []
+        self.index, self.sm, self.reasons, self.smax = index, [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        self._err = None
+
+    def _run(self):
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            # NVML indexes physical devices; honour CUDA_VISIBLE_DEVICES when it lists indices
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+            idx = self.index
+            if vis and all(v.strip().isdigit() for v in vis.split(",")):
+                idx = int(vis.split(",")[self.index])
+            h = nv.nvmlDeviceGetHandleByIndex(idx)
+            self.smax = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+            names = {
+                getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+                getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+                getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+                getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+            }
+            get_reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons",
+                                  getattr(nv, "nvmlDeviceGetCurrentClocksThrottleReasons", None))
+            while not self._stop.is_set():
+                self.sm.append(float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)))
+                if get_reasons is not None:
+                    mask = int(get_reasons(h))
+                    for bit, name in names.items():
+                        if mask & bit:
+                            self.reasons.add(name)
+                time.sleep(0.002)
+        except Exception as e:  # NVML missing or refused: report, do not fail the bench
+            self._err = repr(e)
 
     def start(self):
-        try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-i", str(self.index), "-lms", "100"],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            threading.Thread(target=self._read, daemon=True).start()
-        except OSError:
-            self.proc = None
-
-    def _read(self):
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+        time.sleep(0.05)  # let the first samples land before the timed region
 
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, smax, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 9:
-                continue
-            try:
-                sm.append(float(parts[1]))
-                smax.append(float(parts[2]))
-            except ValueError:
-                continue
-            for name, val in zip(names, parts[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None,
-                "sm_max_mhz": max(smax) if smax else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=5)
+        out = {"sm_mhz": statistics.median(self.sm) if self.sm else None,
+               "sm_max_mhz": self.smax, "samples": len(self.sm), "reasons": sorted(self.reasons)}
+        if self._err:
+            out["error"] = self._err
+        return out
 
 
 # ---------------------------------------------------------------------------
@@ -324,7 +328,12 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     eng.load_library()
 
-    copies = 3
+    copies = max(2, args.copies)
+    if args.only == "lm_head":
+        lm = bench_lm_head(eng, torch, dist, rank, world, max(5, min(args.steps, 50)), 3)
+        if rank == 0:
+            print(json.dumps({"lm_head": lm}), flush=True)
+        return
     groups, keep, x_dev, y_dev = build_projection_set(eng, torch, copies, SEED + 1 + rank)
     bytes_step = groups[0].bytes
     assert bytes_step == set_bytes(), (bytes_step, set_bytes())
@@ -384,7 +393,8 @@ def run_ours(args):
     del groups, keep
     torch.cuda.empty_cache()
 
-    lm = bench_lm_head(eng, torch, dist, rank, world, max(5, min(args.steps, 50)), 3)
+    lm = {} if args.only == "set" else bench_lm_head(eng, torch, dist, rank, world,
+                                                      max(5, min(args.steps, 50)), 3)
 
     if rank != 0:
         if dist is not None:
@@ -420,7 +430,7 @@ def run_ours(args):
                     "scaling": "strong (vocabulary rows split over ranks, one all-gather of "
                                "candidates)" if world > 1 else "single GPU", **lm},
     }
-    if world == 1:
+    if world == 1 and not args.skip_cpu:
         base, _, _ = time_cpu(5, 1, budget_s=25.0)
         line["cpu_baseline"] = base
     print(json.dumps(line), flush=True)
@@ -434,6 +444,10 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--only", default="all", choices=["all", "set", "lm_head"],
+                    help="profiling aid: run only the projection set or only the lm_head")
+    ap.add_argument("--copies", type=int, default=3, help="distinct weight copies rotated")
+    ap.add_argument("--skip-cpu", action="store_true", help="profiling aid: no CPU baseline")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3

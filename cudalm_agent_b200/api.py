@@ -79,7 +79,8 @@ _lib: Optional[ctypes.CDLL] = None
 
 
 def library_path() -> str:
-    return _build.LIB_PATH
+    """Path of the native library; ``CUDALM_B200_LIBRARY`` overrides the in-tree build."""
+    return os.environ.get("CUDALM_B200_LIBRARY") or _build.LIB_PATH
 
 
 def load_library() -> ctypes.CDLL:

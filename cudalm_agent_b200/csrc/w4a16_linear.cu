@@ -52,7 +52,14 @@ w4a16_fallback_kernel(const std::uint8_t* __restrict__ W, const std::uint16_t* _
 // ---------------------------------------------------------------------------
 namespace {
 
-constexpr int kCG = 4;               // groups per chunk (512 values of k)
+#ifndef CB200_CG
+#define CB200_CG 4
+#endif
+constexpr int kCG = CB200_CG;        // groups per chunk (CG * 128 values of k)
+#ifndef CB200_DEQUANT
+#define CB200_DEQUANT 0
+#endif
+constexpr int kDQ = CB200_DEQUANT;   // 0: magic-number dequant, 1: through bf16's tiny numbers
 constexpr int kRS = kCG * 64 + 64;   // stage row stride
 constexpr int kMaxStreamK = 4096;    // largest K the staged path takes
 
@@ -74,7 +81,7 @@ bool make_plan(int kmax, int mmax, Plan* out) {
   int nt = 1;
   while (nt * 8 < mmax && nt < 8) nt *= 2;
   // at least 4 KB: the region doubles as reduction scratch at the kernel's end
-  int x_bytes = round_up(mmax * (2 * kmax + 32), 128);
+  int x_bytes = round_up((mmax + 1) * (2 * kmax + 32), 128);  // + the all-zero row
   if (x_bytes < 4096) x_bytes = 4096;
   for (int nwarps : {16, 8}) {
     if (nt == 8 && nwarps == 16) continue;  // 32 accumulators per lane need the larger register budget
@@ -83,6 +90,9 @@ bool make_plan(int kmax, int mmax, Plan* out) {
     if (avail < 2 * nwarps * stage) continue;
     int depth = avail / (nwarps * stage);
     if (depth > kMaxDepth) depth = kMaxDepth;
+#if CB200_LOADER == 2
+    if (depth > 3) depth = 3;
+#endif
     *out = Plan{nt, nwarps, depth, stage, x_bytes, fixed + nwarps * depth * stage};
     return true;
   }
@@ -101,7 +111,7 @@ int max_rows_per_pass(int k) {
 
 template <int NT, int NWARPS, bool CTA_MAX>
 int launch_instance(const StreamParams& p, const Plan& pl, int grid, cudaStream_t stream) {
-  auto kern = w4a16_stream_kernel<NT, kCG, NWARPS, CTA_MAX>;
+  auto kern = w4a16_stream_kernel<NT, kCG, NWARPS, CTA_MAX, kDQ>;
   // the attribute is per device; set it on every device this process uses
   static std::mutex mu;
   static std::vector<int> done_devices;
@@ -159,7 +169,10 @@ bool stream_eligible(const cudalm_b200_linear& l) {
   return aligned_to(l.weight, 16) && l.K <= kMaxStreamK;
 }
 
-LinearDev to_dev(const cudalm_b200_linear& l, int mt_begin) {
+inline int chunks_per_mtile(int K) { return ((K >> 7) + kCG - 1) / kCG; }
+inline int mtiles(int N) { return (N + kMTileRows - 1) / kMTileRows; }
+
+LinearDev to_dev(const cudalm_b200_linear& l, int mt_begin, int cost_begin) {
   LinearDev d;
   d.W = l.weight;
   d.S = l.scales;
@@ -170,7 +183,7 @@ LinearDev to_dev(const cudalm_b200_linear& l, int mt_begin) {
   d.M = l.M;
   d.mt_begin = mt_begin;
   d.flags = aligned_to(l.scales, 16) ? kFlagScalesBulk : 0;
-  d.pad = 0;
+  d.cost_begin = cost_begin;
   return d;
 }
 
@@ -197,9 +210,10 @@ int run_single(cudalm_b200_linear l, cudaStream_t stream) {
     StreamParams p;
     std::memset(&p, 0, sizeof(p));
     p.table = nullptr;
-    p.inl[0] = to_dev(part, 0);
+    p.inl[0] = to_dev(part, 0, 0);
     p.n_desc = 1;
-    p.total_mt = (l.N + kMTileRows - 1) / kMTileRows;
+    p.total_mt = mtiles(l.N);
+    p.total_cost = p.total_mt * chunks_per_mtile(l.K);
     if (int rc = launch_stream(p, l.K, part.M, stream)) return rc;
   }
   return CUDALM_B200_OK;
@@ -217,9 +231,10 @@ int run_linear_with_cta_max(const cudalm_b200_linear& l, float* cta_max, int* gr
   if (max_rows_per_pass(l.K) < l.M) return CUDALM_B200_ERR_UNSUPPORTED;
   StreamParams p;
   std::memset(&p, 0, sizeof(p));
-  p.inl[0] = to_dev(l, 0);
+  p.inl[0] = to_dev(l, 0, 0);
   p.n_desc = 1;
-  p.total_mt = (l.N + kMTileRows - 1) / kMTileRows;
+  p.total_mt = mtiles(l.N);
+  p.total_cost = p.total_mt * chunks_per_mtile(l.K);
   p.cta_max = cta_max;
   return launch_stream(p, l.K, l.M, stream, grid_out);
 }
@@ -241,6 +256,7 @@ struct cudalm_b200_group {
   LinearDev* table_dev = nullptr;
   int count = 0;
   int total_mt = 0;
+  int total_cost = 0;
   int kmax = 0;
   int mmax = 0;
   long long bytes = 0;
@@ -284,13 +300,15 @@ int cudalm_b200_linear_multi(const cudalm_b200_linear* linears, int count, void*
   }
   StreamParams p;
   std::memset(&p, 0, sizeof(p));
-  int mt = 0;
+  int mt = 0, cost = 0;
   for (int i = 0; i < count; ++i) {
-    p.inl[i] = to_dev(linears[i], mt);
-    mt += (linears[i].N + kMTileRows - 1) / kMTileRows;
+    p.inl[i] = to_dev(linears[i], mt, cost);
+    mt += mtiles(linears[i].N);
+    cost += mtiles(linears[i].N) * chunks_per_mtile(linears[i].K);
   }
   p.n_desc = count;
   p.total_mt = mt;
+  p.total_cost = cost;
   return launch_stream(p, kmax, mmax, st);
 }
 
@@ -321,15 +339,17 @@ int cudalm_b200_group_create(const cudalm_b200_linear* linears, int count,
   if (count < 1) return CUDALM_B200_ERR_BAD_SHAPE;
   std::vector<LinearDev> tbl(static_cast<size_t>(count));
   int mt = 0, kmax = 0, mmax = 0;
-  long long bytes = 0;
+  long long bytes = 0, cost = 0;
   for (int i = 0; i < count; ++i) {
     const cudalm_b200_linear& l = linears[i];
     if (int rc = validate(l)) return rc;
     if (l.reserved != 0) return CUDALM_B200_ERR_BAD_SHAPE;
     if (!aligned_to(l.weight, 16)) return CUDALM_B200_ERR_MISALIGNED;
     if (l.K > kMaxStreamK || l.M > CUDALM_B200_MAX_GROUP_M) return CUDALM_B200_ERR_UNSUPPORTED;
-    tbl[static_cast<size_t>(i)] = to_dev(l, mt);
-    mt += (l.N + kMTileRows - 1) / kMTileRows;
+    tbl[static_cast<size_t>(i)] = to_dev(l, mt, static_cast<int>(cost));
+    mt += mtiles(l.N);
+    cost += static_cast<long long>(mtiles(l.N)) * chunks_per_mtile(l.K);
+    if (cost > 0x3fffffff) return CUDALM_B200_ERR_TOO_LARGE;
     kmax = l.K > kmax ? l.K : kmax;
     mmax = l.M > mmax ? l.M : mmax;
     bytes += static_cast<long long>(l.N) * (l.K / 2) + static_cast<long long>(l.N) * (l.K / 128) * 2 +
@@ -340,6 +360,7 @@ int cudalm_b200_group_create(const cudalm_b200_linear* linears, int count,
   cudalm_b200_group* g = new cudalm_b200_group();
   g->count = count;
   g->total_mt = mt;
+  g->total_cost = static_cast<int>(cost);
   g->kmax = kmax;
   g->mmax = mmax;
   g->bytes = bytes;
@@ -364,6 +385,7 @@ int cudalm_b200_group_run(const cudalm_b200_group* group, void* stream) {
   p.table = group->table_dev;
   p.n_desc = group->count;
   p.total_mt = group->total_mt;
+  p.total_cost = group->total_cost;
   return launch_stream(p, group->kmax, group->mmax, static_cast<cudaStream_t>(stream));
 }
 
@@ -387,7 +409,7 @@ int cudalm_b200_kernel_regs(const char* kernel_name) {
   const void* fn = nullptr;
 #define CB200_NAME(NT_, NW_)                                                     \
   if (std::strcmp(kernel_name, "w4a16_stream_nt" #NT_ "_w" #NW_) == 0)           \
-    fn = reinterpret_cast<const void*>(&w4a16_stream_kernel<NT_, kCG, NW_, false>);
+    fn = reinterpret_cast<const void*>(&w4a16_stream_kernel<NT_, kCG, NW_, false, kDQ>);
   CB200_NAME(1, 16) CB200_NAME(2, 16) CB200_NAME(4, 16)
   CB200_NAME(1, 8) CB200_NAME(2, 8) CB200_NAME(4, 8) CB200_NAME(8, 8)
 #undef CB200_NAME

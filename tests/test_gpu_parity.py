@@ -339,3 +339,26 @@ def test_lm_head_full_vocabulary_argmax(eng, orc):
         _check_pick(orc, logits, from_dev(argmax), from_dev(idx), from_dev(val), 50)
         for m in range(M):
             assert from_dev(argmax)[m] == orc.argmax_bf16(want[m]), f"M={M} row {m}"
+
+
+def test_second_opinion_reference_cuda_kernel(eng, orc):
+    """The reference's own CUDA kernel (its sources compiled for sm_100a into
+    oracle/_ref) on the same inputs: it, this library and the CPU oracle must
+    agree under the same gate.  Skipped where the bridge was not built."""
+    import torch
+    if not orc.have_ref():
+        pytest.skip("oracle/_ref not built")
+    R = orc.ref()
+    for N, K in ((3584, 1024), (1024, 3584), (512, 1024)):
+        W, S = raw_weights(N, K, 55 + N)
+        x = make_x(orc, (K,), 56, "outlier")
+        dW, dS, dx = to_dev(W), to_dev(S, torch.float16), to_dev(x, torch.bfloat16)
+        y_ref = torch.empty(N, dtype=torch.bfloat16, device="cuda")
+        R.ref_gpu_int4_gemv_bf16(dW.data_ptr(), dS.data_ptr(), dx.data_ptr(), y_ref.data_ptr(), N, K,
+                                 torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        want = orc.gemv_bf16(W, S, x)
+        check_close(orc, from_dev(y_ref), want, f"reference CUDA kernel vs CPU {N}x{K}")
+        ours = from_dev(eng.int4_gemv_bf16(dW, dS, dx))
+        check_close(orc, ours, want, f"this library vs CPU {N}x{K}")
+        check_close(orc, ours, from_dev(y_ref), f"this library vs reference CUDA kernel {N}x{K}")
