@@ -131,22 +131,17 @@ __device__ __forceinline__ std::uint64_t policy_evict_first() {
 }
 
 // ---- shared-memory loads ---------------------------------------------------
-__device__ __forceinline__ uint4 lds128(std::uint32_t addr) {
-  uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "r"(addr));
-  return v;
+// Plain (non-volatile) loads: the compiler is free to hoist them above earlier
+// tensor-core instructions, which is what hides their latency.  They stay
+// behind the mbarrier wait because that asm clobbers memory.
+__device__ __forceinline__ uint4 lds128(const std::uint8_t* p) {
+  return *reinterpret_cast<const uint4*>(p);
 }
-__device__ __forceinline__ uint2 lds64(std::uint32_t addr) {
-  uint2 v;
-  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
-  return v;
+__device__ __forceinline__ uint2 lds64(const std::uint8_t* p) {
+  return *reinterpret_cast<const uint2*>(p);
 }
-__device__ __forceinline__ std::uint16_t lds16(std::uint32_t addr) {
-  std::uint16_t v;
-  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
-  return v;
+__device__ __forceinline__ std::uint16_t lds16(const std::uint8_t* p) {
+  return *reinterpret_cast<const std::uint16_t*>(p);
 }
 
 // ---- int4 -> bf16 dequantisation --------------------------------------------
@@ -184,7 +179,7 @@ __device__ __forceinline__ void mma_m16n8k16_bf16(float (&c)[4], std::uint32_t a
                                                   std::uint32_t a1, std::uint32_t a2,
                                                   std::uint32_t a3, std::uint32_t b0,
                                                   std::uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 "
       "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])

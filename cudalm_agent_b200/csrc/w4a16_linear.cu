@@ -56,11 +56,8 @@ namespace {
 #define CB200_CG 4
 #endif
 constexpr int kCG = CB200_CG;        // groups per chunk (CG * 128 values of k)
-#ifndef CB200_DEQUANT
-#define CB200_DEQUANT 0
-#endif
-constexpr int kDQ = CB200_DEQUANT;   // 0: magic-number dequant, 1: through bf16's tiny numbers
-constexpr int kRS = kCG * 64 + 64;   // stage row stride
+constexpr int kRS = kCG * 64;        // stage row stride
+constexpr int kBarrierBytes = 1024;  // mbarrier area at the start of shared memory
 constexpr int kMaxStreamK = 4096;    // largest K the staged path takes
 
 inline int round_up(int v, int a) { return (v + a - 1) / a * a; }
@@ -83,16 +80,17 @@ bool make_plan(int kmax, int mmax, Plan* out) {
   // at least 4 KB: the region doubles as reduction scratch at the kernel's end
   int x_bytes = round_up((mmax + 1) * (2 * kmax + 32), 128);  // + the all-zero row
   if (x_bytes < 4096) x_bytes = 4096;
-  for (int nwarps : {16, 8}) {
-    if (nt == 8 && nwarps == 16) continue;  // 32 accumulators per lane need the larger register budget
-    const int fixed = nwarps * kMaxDepth * 8 + x_bytes;
+#ifdef CB200_WARPS
+  for (int nwarps : {CB200_WARPS}) {
+#else
+  for (int nwarps : {16, 12, 8}) {
+#endif
+    if (nt == 8 && nwarps != 8) continue;  // 32 accumulators per lane need the larger register budget
+    const int fixed = kBarrierBytes + x_bytes;
     const int avail = kMaxSmemBytes - fixed;
     if (avail < 2 * nwarps * stage) continue;
     int depth = avail / (nwarps * stage);
     if (depth > kMaxDepth) depth = kMaxDepth;
-#if CB200_LOADER == 2
-    if (depth > 3) depth = 3;
-#endif
     *out = Plan{nt, nwarps, depth, stage, x_bytes, fixed + nwarps * depth * stage};
     return true;
   }
@@ -111,7 +109,7 @@ int max_rows_per_pass(int k) {
 
 template <int NT, int NWARPS, bool CTA_MAX>
 int launch_instance(const StreamParams& p, const Plan& pl, int grid, cudaStream_t stream) {
-  auto kern = w4a16_stream_kernel<NT, kCG, NWARPS, CTA_MAX, kDQ>;
+  auto kern = w4a16_stream_kernel<NT, kCG, NWARPS, CTA_MAX>;
   // the attribute is per device; set it on every device this process uses
   static std::mutex mu;
   static std::vector<int> done_devices;
@@ -154,6 +152,7 @@ int launch_stream(StreamParams& p, int kmax, int mmax, cudaStream_t stream,
     return want_max ? launch_instance<NT_, NW_, true>(p, pl, grid, stream)          \
                     : launch_instance<NT_, NW_, false>(p, pl, grid, stream);
   CB200_CASE(1, 16) CB200_CASE(2, 16) CB200_CASE(4, 16)
+  CB200_CASE(1, 12) CB200_CASE(2, 12) CB200_CASE(4, 12)
   CB200_CASE(1, 8) CB200_CASE(2, 8) CB200_CASE(4, 8) CB200_CASE(8, 8)
 #undef CB200_CASE
   return CUDALM_B200_ERR_UNSUPPORTED;
@@ -172,19 +171,60 @@ bool stream_eligible(const cudalm_b200_linear& l) {
 inline int chunks_per_mtile(int K) { return ((K >> 7) + kCG - 1) / kCG; }
 inline int mtiles(int N) { return (N + kMTileRows - 1) / kMTileRows; }
 
-LinearDev to_dev(const cudalm_b200_linear& l, int mt_begin, int cost_begin) {
-  LinearDev d;
-  d.W = l.weight;
-  d.S = l.scales;
-  d.x = l.x;
-  d.y = l.y;
-  d.N = l.N;
-  d.K = l.K;
-  d.M = l.M;
-  d.mt_begin = mt_begin;
-  d.flags = aligned_to(l.scales, 16) ? kFlagScalesBulk : 0;
-  d.cost_begin = cost_begin;
-  return d;
+// cuTensorMapEncodeTiled, fetched from the driver at first use (the library
+// links no driver stub, so it still loads on a machine without a GPU).
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static std::once_flag once;
+  static EncodeTiledFn fn = nullptr;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) ==
+            cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+    else
+      (void)cudaGetLastError();
+  });
+  return fn;
+}
+
+// Describes the packed weight matrix to the TMA unit as uint32 [N][K/8] with a
+// box of 16 rows x kCG*16 words (= kCG groups of 128 nibbles per row).
+int encode_weight_map(const std::uint8_t* weight, int N, int K, CUtensorMap* out) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return CUDALM_B200_ERR_CUDA;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K / 8), static_cast<cuuint64_t>(N)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K / 2)};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(kCG * 16), static_cast<cuuint32_t>(kMTileRows)};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2,
+                        const_cast<std::uint8_t*>(weight), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    g_last_cuda_error = static_cast<int>(r);
+    return CUDALM_B200_ERR_CUDA;
+  }
+  return CUDALM_B200_OK;
+}
+
+int to_dev(const cudalm_b200_linear& l, int mt_begin, int cost_begin, LinearDev* d) {
+  if (int rc = encode_weight_map(l.weight, l.N, l.K, &d->tmap)) return rc;
+  d->S = l.scales;
+  d->x = l.x;
+  d->y = l.y;
+  d->N = l.N;
+  d->K = l.K;
+  d->M = l.M;
+  d->mt_begin = mt_begin;
+  d->flags = aligned_to(l.scales, 16) ? kFlagScalesBulk : 0;
+  d->cost_begin = cost_begin;
+  return CUDALM_B200_OK;
 }
 
 int run_fallback(const cudalm_b200_linear& l, cudaStream_t stream) {
@@ -210,7 +250,7 @@ int run_single(cudalm_b200_linear l, cudaStream_t stream) {
     StreamParams p;
     std::memset(&p, 0, sizeof(p));
     p.table = nullptr;
-    p.inl[0] = to_dev(part, 0, 0);
+    if (int rc = to_dev(part, 0, 0, &p.inl[0])) return rc;
     p.n_desc = 1;
     p.total_mt = mtiles(l.N);
     p.total_cost = p.total_mt * chunks_per_mtile(l.K);
@@ -231,7 +271,7 @@ int run_linear_with_cta_max(const cudalm_b200_linear& l, float* cta_max, int* gr
   if (max_rows_per_pass(l.K) < l.M) return CUDALM_B200_ERR_UNSUPPORTED;
   StreamParams p;
   std::memset(&p, 0, sizeof(p));
-  p.inl[0] = to_dev(l, 0, 0);
+  if (int rc = to_dev(l, 0, 0, &p.inl[0])) return rc;
   p.n_desc = 1;
   p.total_mt = mtiles(l.N);
   p.total_cost = p.total_mt * chunks_per_mtile(l.K);
@@ -302,7 +342,7 @@ int cudalm_b200_linear_multi(const cudalm_b200_linear* linears, int count, void*
   std::memset(&p, 0, sizeof(p));
   int mt = 0, cost = 0;
   for (int i = 0; i < count; ++i) {
-    p.inl[i] = to_dev(linears[i], mt, cost);
+    if (int rc = to_dev(linears[i], mt, cost, &p.inl[i])) return rc;
     mt += mtiles(linears[i].N);
     cost += mtiles(linears[i].N) * chunks_per_mtile(linears[i].K);
   }
@@ -346,7 +386,7 @@ int cudalm_b200_group_create(const cudalm_b200_linear* linears, int count,
     if (l.reserved != 0) return CUDALM_B200_ERR_BAD_SHAPE;
     if (!aligned_to(l.weight, 16)) return CUDALM_B200_ERR_MISALIGNED;
     if (l.K > kMaxStreamK || l.M > CUDALM_B200_MAX_GROUP_M) return CUDALM_B200_ERR_UNSUPPORTED;
-    tbl[static_cast<size_t>(i)] = to_dev(l, mt, static_cast<int>(cost));
+    if (int rc = to_dev(l, mt, static_cast<int>(cost), &tbl[static_cast<size_t>(i)])) return rc;
     mt += mtiles(l.N);
     cost += static_cast<long long>(mtiles(l.N)) * chunks_per_mtile(l.K);
     if (cost > 0x3fffffff) return CUDALM_B200_ERR_TOO_LARGE;
@@ -409,8 +449,9 @@ int cudalm_b200_kernel_regs(const char* kernel_name) {
   const void* fn = nullptr;
 #define CB200_NAME(NT_, NW_)                                                     \
   if (std::strcmp(kernel_name, "w4a16_stream_nt" #NT_ "_w" #NW_) == 0)           \
-    fn = reinterpret_cast<const void*>(&w4a16_stream_kernel<NT_, kCG, NW_, false, kDQ>);
+    fn = reinterpret_cast<const void*>(&w4a16_stream_kernel<NT_, kCG, NW_, false>);
   CB200_NAME(1, 16) CB200_NAME(2, 16) CB200_NAME(4, 16)
+  CB200_NAME(1, 12) CB200_NAME(2, 12) CB200_NAME(4, 12)
   CB200_NAME(1, 8) CB200_NAME(2, 8) CB200_NAME(4, 8) CB200_NAME(8, 8)
 #undef CB200_NAME
   if (std::strcmp(kernel_name, "w4a16_fallback") == 0)
