@@ -13,12 +13,21 @@ std::atomic<long long> g_launch_count{0};
 __device__ int g_status_word = 0;
 
 int* device_status_word() {
+  // one lookup per device; the address never changes afterwards
+  static std::atomic<int*> cached[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = -1;
+  if (dev >= 0) {
+    int* hit = cached[dev].load(std::memory_order_acquire);
+    if (hit) return hit;
+  }
   void* p = nullptr;
   cudaError_t e = cudaGetSymbolAddress(&p, g_status_word);
   if (e != cudaSuccess) {
     g_last_cuda_error = static_cast<int>(e);
     return nullptr;
   }
+  if (dev >= 0) cached[dev].store(static_cast<int*>(p), std::memory_order_release);
   return static_cast<int*>(p);
 }
 

@@ -78,7 +78,8 @@ bool make_plan(int kmax, int mmax, Plan* out) {
   int nt = 1;
   while (nt * 8 < mmax && nt < 8) nt *= 2;
   // at least 4 KB: the region doubles as reduction scratch at the kernel's end
-  int x_bytes = round_up((mmax + 1) * (2 * kmax + 32), 128);  // + the all-zero row
+  // activations, + the all-zero row, + the per-group offset sums [K/128][8*nt]
+  int x_bytes = round_up((mmax + 1) * (2 * kmax + 32) + (kmax / 128) * nt * 8 * 4, 128);
   if (x_bytes < 4096) x_bytes = 4096;
 #ifdef CB200_WARPS
   for (int nwarps : {CB200_WARPS}) {
@@ -129,12 +130,32 @@ int launch_instance(const StreamParams& p, const Plan& pl, int grid, cudaStream_
       done_devices.push_back(dev);
     }
   }
-  kern<<<grid, NWARPS * 32, pl.smem_bytes, stream>>>(p);
+  // Programmatic dependent launch: the next kernel in the stream may start its
+  // CTAs while this one drains.  Only kernels that execute
+  // griddepcontrol.launch_dependents let their successor start early, and the
+  // streaming kernel touches nothing an earlier kernel may have written
+  // (activations, outputs) before its griddepcontrol.wait.
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid));
+  cfg.blockDim = dim3(NWARPS * 32);
+  cfg.dynamicSmemBytes = static_cast<size_t>(pl.smem_bytes);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t le = cudaLaunchKernelEx(&cfg, kern, p);
+  if (le != cudaSuccess) {
+    g_last_cuda_error = static_cast<int>(le);
+    (void)cudaGetLastError();
+    return CUDALM_B200_ERR_CUDA;
+  }
   return check_launch();
 }
 
 int launch_stream(StreamParams& p, int kmax, int mmax, cudaStream_t stream,
-                  int* grid_out = nullptr) {
+                  int* grid_out = nullptr, int forced_grid = 0) {
   Plan pl;
   if (!make_plan(kmax, mmax, &pl)) return CUDALM_B200_ERR_UNSUPPORTED;
   p.depth = pl.depth;
@@ -145,6 +166,7 @@ int launch_stream(StreamParams& p, int kmax, int mmax, cudaStream_t stream,
   int grid = num_sms();
   if (grid > p.total_mt) grid = p.total_mt;
   if (grid < 1) grid = 1;
+  if (forced_grid > 0) grid = forced_grid;  // a group's per-CTA ranges were cut for this grid
   if (grid_out) *grid_out = grid;
   const bool want_max = p.cta_max != nullptr;
 #define CB200_CASE(NT_, NW_)                                                        \
@@ -294,6 +316,8 @@ using namespace cb200;
 
 struct cudalm_b200_group {
   LinearDev* table_dev = nullptr;
+  int2* ranges_dev = nullptr;  // per-CTA {first m-tile, projection}, grid + 1 entries
+  int grid = 0;
   int count = 0;
   int total_mt = 0;
   int total_cost = 0;
@@ -404,13 +428,37 @@ int cudalm_b200_group_create(const cudalm_b200_linear* linears, int count,
   g->kmax = kmax;
   g->mmax = mmax;
   g->bytes = bytes;
+  // per-CTA ranges: equal shares of chunks, rounded up to whole m-tiles
+  g->grid = num_sms() < mt ? num_sms() : mt;
+  std::vector<int2> ranges(static_cast<size_t>(g->grid) + 1);
+  {
+    int d = 0;
+    for (int b = 0; b <= g->grid; ++b) {
+      const long long c = static_cast<long long>(b) * cost / g->grid;
+      if (c >= cost) {
+        ranges[static_cast<size_t>(b)] = make_int2(mt, count);
+        continue;
+      }
+      while (d + 1 < count && tbl[static_cast<size_t>(d) + 1].cost_begin <= c) ++d;
+      const LinearDev& L = tbl[static_cast<size_t>(d)];
+      const int nch = chunks_per_mtile(L.K);
+      int first = L.mt_begin + static_cast<int>((c - L.cost_begin + nch - 1) / nch);
+      int dd = d;
+      if (first >= L.mt_begin + mtiles(L.N)) dd = d + 1;  // rounded up into the next projection
+      ranges[static_cast<size_t>(b)] = make_int2(first, dd);
+    }
+  }
   cudaError_t e = cudaGetDevice(&g->device);
   if (e == cudaSuccess) e = cudaMalloc(&g->table_dev, sizeof(LinearDev) * tbl.size());
   if (e == cudaSuccess)
     e = cudaMemcpy(g->table_dev, tbl.data(), sizeof(LinearDev) * tbl.size(), cudaMemcpyHostToDevice);
+  if (e == cudaSuccess) e = cudaMalloc(&g->ranges_dev, sizeof(int2) * ranges.size());
+  if (e == cudaSuccess)
+    e = cudaMemcpy(g->ranges_dev, ranges.data(), sizeof(int2) * ranges.size(), cudaMemcpyHostToDevice);
   if (e != cudaSuccess) {
     g_last_cuda_error = static_cast<int>(e);
     if (g->table_dev) cudaFree(g->table_dev);
+    if (g->ranges_dev) cudaFree(g->ranges_dev);
     delete g;
     return CUDALM_B200_ERR_CUDA;
   }
@@ -426,12 +474,16 @@ int cudalm_b200_group_run(const cudalm_b200_group* group, void* stream) {
   p.n_desc = group->count;
   p.total_mt = group->total_mt;
   p.total_cost = group->total_cost;
-  return launch_stream(p, group->kmax, group->mmax, static_cast<cudaStream_t>(stream));
+  p.cta_ranges = group->ranges_dev;
+  return launch_stream(p, group->kmax, group->mmax, static_cast<cudaStream_t>(stream), nullptr,
+                       group->grid);
 }
 
 int cudalm_b200_group_destroy(cudalm_b200_group* group) {
   if (!group) return CUDALM_B200_OK;
   cudaError_t e = cudaFree(group->table_dev);
+  const cudaError_t e2 = cudaFree(group->ranges_dev);
+  if (e == cudaSuccess) e = e2;
   delete group;
   if (e != cudaSuccess) {
     g_last_cuda_error = static_cast<int>(e);

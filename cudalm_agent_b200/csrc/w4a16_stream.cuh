@@ -26,6 +26,9 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#ifdef CB200_TIMING
+#include <cstdio>
+#endif
 
 namespace cb200 {
 
@@ -57,6 +60,10 @@ struct StreamParams {
   int x_bytes;      // activation region
   int* status;      // device status word
   float* cta_max;   // [gridDim.x][M] when the kernel is built with CTA_MAX
+  // Optional, for launches with a device table: per CTA {first m-tile, its
+  // projection}, gridDim.x + 1 entries, so that a CTA finds its range with two
+  // loads instead of a chain of dependent table look-ups.
+  const int2* cta_ranges;
 };
 
 #ifdef __CUDACC__
@@ -116,11 +123,15 @@ struct Cursor {
     S = L->S;
     nch = (G + CG - 1) / CG;
   }
-  __device__ __forceinline__ void start(const StreamParams& p, int mt0, int mt_hi) {
+  // d_hint: a projection at or before the one that holds mt0
+  __device__ __forceinline__ void start(const StreamParams& p, int mt0, int mt_hi, int d_hint) {
     mt = mt0;
     chunk = 0;
     valid = mt0 < mt_hi;
-    if (valid) bind(p, find_desc(p, mt0));
+    if (valid) {
+      bind(p, d_hint);
+      while (mt >= mt_end) bind(p, d + 1);
+    }
   }
   // Next item of this warp: next chunk, else the warp's next m-tile (`stride`
   // m-tiles further on), moving to a later projection when needed.
@@ -210,19 +221,49 @@ __device__ __forceinline__ bool wait_stage(std::uint64_t* bar, std::uint32_t par
 // Values are stored times 2^64 (even i) or 2^60 (odd i); both are exact in bf16
 // for |x| < 2^63.  Row M (one past the real rows) is all zeros: MMA columns
 // beyond M read it, so the fragment loads need no predicate.
+__device__ __forceinline__ void store_x_value(std::uint8_t* xs, int rsx, int n, int k,
+                                              std::uint16_t bits) {
+  const int g = k >> 7, r = k & 127, t = r >> 5, q = r & 31, w = q >> 3, i = q & 7;
+  const int j = 2 * w + ((i & 3) >> 1);
+  const int e = 2 * (i & 1) + (i >> 2);
+  const float f = bf16_bits_to_float(bits) * ((i & 1) ? CB200_X_SCALE_ODD : CB200_X_SCALE_EVEN);
+  *reinterpret_cast<std::uint16_t*>(xs + n * rsx + ((((g * 8 + j) * 4 + t) * 4 + e) * 2)) =
+      float_to_bf16_bits(f);
+}
+
 __device__ __forceinline__ void fill_x_fragments(std::uint8_t* xs, const std::uint16_t* x,
                                                  int M, int K, int rsx, int tid,
                                                  int nthreads) {
   const int total = M * K;
-  for (int idx = tid; idx < total; idx += nthreads) {
-    const int n = idx / K;
-    const int k = idx - n * K;
-    const int g = k >> 7, r = k & 127, t = r >> 5, q = r & 31, w = q >> 3, i = q & 7;
-    const int j = 2 * w + ((i & 3) >> 1);
-    const int e = 2 * (i & 1) + (i >> 2);
-    const float f = bf16_bits_to_float(__ldg(x + idx)) * ((i & 1) ? CB200_X_SCALE_ODD : CB200_X_SCALE_EVEN);
-    *reinterpret_cast<std::uint16_t*>(xs + n * rsx + ((((g * 8 + j) * 4 + t) * 4 + e) * 2)) =
-        float_to_bf16_bits(f);
+  if ((reinterpret_cast<std::uintptr_t>(x) & 7u) == 0) {
+    // four values per 8-byte load, four loads in flight per thread
+    const int quads = total >> 2;
+    for (int q0 = tid; q0 < quads; q0 += 4 * nthreads) {
+      uint2 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int qi = q0 + u * nthreads;
+        v[u] = qi < quads ? __ldg(reinterpret_cast<const uint2*>(x) + qi) : make_uint2(0u, 0u);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int qi = q0 + u * nthreads;
+        if (qi < quads) {
+          const int idx = qi << 2;
+          const int n = idx / K;
+          const int k = idx - n * K;
+          store_x_value(xs, rsx, n, k, static_cast<std::uint16_t>(v[u].x & 0xFFFFu));
+          store_x_value(xs, rsx, n, k + 1, static_cast<std::uint16_t>(v[u].x >> 16));
+          store_x_value(xs, rsx, n, k + 2, static_cast<std::uint16_t>(v[u].y & 0xFFFFu));
+          store_x_value(xs, rsx, n, k + 3, static_cast<std::uint16_t>(v[u].y >> 16));
+        }
+      }
+    }
+  } else {
+    for (int idx = tid; idx < total; idx += nthreads) {
+      const int n = idx / K;
+      store_x_value(xs, rsx, n, idx - n * K, __ldg(x + idx));
+    }
   }
   for (int idx = tid; idx < K / 2; idx += nthreads)
     *reinterpret_cast<std::uint32_t*>(xs + M * rsx + idx * 4) = 0u;
@@ -232,17 +273,67 @@ __device__ __forceinline__ void fill_x_fragments(std::uint8_t* xs, const std::ui
 // the integer in its low byte times 2^-133 (the subnormals run on linearly into
 // the first normal binade), so (w & 0x000F000F) and (w & 0x00F000F0) are
 // already bf16 pairs holding n * 2^-133 and 16 n * 2^-133: four of a word's
-// eight nibbles need no shift.  XOR 8 (folded into the same LOP3) turns the
-// two's-complement nibble n into q + 8, and an exact bf16 subtraction of 8 (or
-// 128) units leaves q * 2^-133 (or q * 2^-129).  For a word holding n0..n7 (n_i
-// at bits 4i): out[i] = { q(n_i), q(n_{i+4}) } (low half, high half), with the
-// 2^-129 factor on odd i.
+// eight nibbles need no shift.  XOR 8, folded into the same LOP3, turns the
+// two's-complement nibble n into the offset-binary u = q + 8 in [0, 15].  For a
+// word holding n0..n7 (n_i at bits 4i): out[i] = { u(n_i), u(n_{i+4}) } (low
+// half, high half) times 2^-133 (even i) or 2^-129 (odd i).
+//
+// The offset is removed per quantisation group, not per value:
+//   sum_k q_k x_k = sum_k u_k x_k - 8 sum_k x_k,
+// where the second sum is the same for every weight row.  It is computed once
+// per projection and activation row (build_bias) by the very same MMA sequence
+// fed with the constant u = 8, so that an all-zero group cancels to an exact
+// zero, and subtracted from each group sum before the scale is applied.
+constexpr std::uint32_t kBiasEven = 0x00080008u;  // { 8, 8 } * 2^-133
+constexpr std::uint32_t kBiasOdd = 0x00800080u;   // { 8, 8 } * 2^-129
 __device__ __forceinline__ void dequant_word(std::uint32_t w, std::uint32_t (&out)[4]) {
   const std::uint32_t w8 = w >> 8;
-  out[0] = sub_bf16x2(lop3_and_xor(w, 0x000F000Fu, 0x00080008u), 0x00080008u);
-  out[1] = sub_bf16x2(lop3_and_xor(w, 0x00F000F0u, 0x00800080u), 0x00800080u);
-  out[2] = sub_bf16x2(lop3_and_xor(w8, 0x000F000Fu, 0x00080008u), 0x00080008u);
-  out[3] = sub_bf16x2(lop3_and_xor(w8, 0x00F000F0u, 0x00800080u), 0x00800080u);
+  out[0] = lop3_and_xor(w, 0x000F000Fu, kBiasEven);
+  out[1] = lop3_and_xor(w, 0x00F000F0u, kBiasOdd);
+  out[2] = lop3_and_xor(w8, 0x000F000Fu, kBiasEven);
+  out[3] = lop3_and_xor(w8, 0x00F000F0u, kBiasOdd);
+}
+
+// Offset sums: bias[g][n] = (sum over group g of 8 * x[n][k]) * 2^-69, for the
+// 8*NT MMA columns n, written by the lanes that own row 0 of the fragment.
+// The instruction sequence mirrors one_group() in consume_chunk exactly.
+template <int NT>
+__device__ __forceinline__ void build_bias(const std::uint8_t* xs, float* bias, int G, int rsx,
+                                           int M, int warp, int lane, int nwarps) {
+  const int r8 = lane >> 2, t = lane & 3;
+  const std::uint8_t* xrow[NT];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    const int n = nt * 8 + r8;
+    xrow[nt] = xs + (n < M ? n : M) * rsx + t * 8;
+  }
+  for (int g = warp; g < G; g += nwarps) {
+    float part[NT][2][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int c = 0; c < 2; ++c)
+        part[nt][c][0] = part[nt][c][1] = part[nt][c][2] = part[nt][c][3] = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int j = 2 * w + h;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          const uint2 b = lds64(xrow[nt] + g * 256 + j * 32);
+          mma_m16n8k16_bf16(part[nt][h], kBiasEven, kBiasEven, kBiasOdd, kBiasOdd, b.x, b.y);
+        }
+      }
+    }
+    if (r8 == 0) {
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        bias[g * (NT * 8) + nt * 8 + 2 * t] = part[nt][0][0] + part[nt][1][0];
+        bias[g * (NT * 8) + nt * 8 + 2 * t + 1] = part[nt][0][1] + part[nt][1][1];
+      }
+    }
+  }
 }
 
 // One chunk of one m-tile: acc[nt][0..3] += sum over the chunk's groups (times
@@ -250,8 +341,8 @@ __device__ __forceinline__ void dequant_word(std::uint32_t w, std::uint32_t (&ou
 // m-tile, activation rows (columns of the MMA) nt*8 + 2t and nt*8 + 2t + 1.
 template <int NT, int CG>
 __device__ __forceinline__ void consume_chunk(const std::uint8_t* stage, const std::uint8_t* xs,
-                                              int G, int g0, int cg, int rsx, int M, int lane,
-                                              float (&acc)[NT][4]) {
+                                              const float* bias, int G, int g0, int cg, int rsx,
+                                              int M, int lane, float (&acc)[NT][4]) {
   constexpr int RS = CG * 64;
   const int r8 = lane >> 2, t = lane & 3;
   const std::uint8_t* wa = stage + r8 * RS + t * 16;
@@ -264,6 +355,7 @@ __device__ __forceinline__ void consume_chunk(const std::uint8_t* stage, const s
     const int n = nt * 8 + r8;
     xrow[nt] = xs + (n < M ? n : M) * rsx + g0 * 256 + t * 8;
   }
+  const float* brow = bias + g0 * (NT * 8) + 2 * t;
   auto one_group = [&](int g) {
     const uint4 qa = lds128(wa + g * 64);
     const uint4 qb = lds128(wb + g * 64);
@@ -295,10 +387,11 @@ __device__ __forceinline__ void consume_chunk(const std::uint8_t* stage, const s
     }
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
-      acc[nt][0] = fmaf(s_lo, part[nt][0][0] + part[nt][1][0], acc[nt][0]);
-      acc[nt][1] = fmaf(s_lo, part[nt][0][1] + part[nt][1][1], acc[nt][1]);
-      acc[nt][2] = fmaf(s_hi, part[nt][0][2] + part[nt][1][2], acc[nt][2]);
-      acc[nt][3] = fmaf(s_hi, part[nt][0][3] + part[nt][1][3], acc[nt][3]);
+      const float2 b8 = *reinterpret_cast<const float2*>(brow + g * (NT * 8) + nt * 8);
+      acc[nt][0] = fmaf(s_lo, (part[nt][0][0] + part[nt][1][0]) - b8.x, acc[nt][0]);
+      acc[nt][1] = fmaf(s_lo, (part[nt][0][1] + part[nt][1][1]) - b8.y, acc[nt][1]);
+      acc[nt][2] = fmaf(s_hi, (part[nt][0][2] + part[nt][1][2]) - b8.x, acc[nt][2]);
+      acc[nt][3] = fmaf(s_hi, (part[nt][0][3] + part[nt][1][3]) - b8.y, acc[nt][3]);
     }
   };
   if (cg == CG) {
@@ -330,8 +423,18 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
   std::uint8_t* ring = xs + p.x_bytes + static_cast<std::size_t>(warp) * depth * p.stage_bytes;
 
   // this CTA's contiguous range of m-tiles: an equal share of the launch's chunks
-  const int mt_lo = mtile_at_cost<CG>(p, static_cast<long long>(blockIdx.x) * p.total_cost / gridDim.x);
-  const int mt_hi = mtile_at_cost<CG>(p, static_cast<long long>(blockIdx.x + 1) * p.total_cost / gridDim.x);
+  int mt_lo, mt_hi, d_first;
+  if (p.cta_ranges) {
+    const int2 r0 = p.cta_ranges[blockIdx.x], r1 = p.cta_ranges[blockIdx.x + 1];
+    mt_lo = r0.x;
+    d_first = r0.y;
+    mt_hi = r1.x;
+  } else {
+    mt_lo = mtile_at_cost<CG>(p, static_cast<long long>(blockIdx.x) * p.total_cost / gridDim.x);
+    mt_hi = mtile_at_cost<CG>(p, static_cast<long long>(blockIdx.x + 1) * p.total_cost / gridDim.x);
+    d_first = mt_lo < mt_hi ? find_desc(p, mt_lo) : p.n_desc;
+  }
+  if (mt_lo >= mt_hi) d_first = p.n_desc;
 
   if (lane == 0) {
     for (int s = 0; s < depth; ++s) mbar_init(&bars[s], 1);
@@ -340,18 +443,31 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
   __syncwarp();
 
   const std::uint64_t policy = policy_evict_first();
+#ifdef CB200_TIMING
+  const long long tm_start = clock64();
+#endif
 
   // Two cursors over this warp's items: `fc` runs ahead issuing copies, `cc`
   // consumes.  The warp takes m-tiles mt_lo + warp, + NWARPS, ...
   Cursor<CG> fc, cc;
-  fc.start(p, mt_lo + warp, mt_hi);
+  fc.start(p, mt_lo + warp, mt_hi, d_first);
   cc = fc;
-  int in_flight = 0;  // stages issued and not yet consumed
+  // Weights and scales are constants of the model: their first copies go out
+  // before this grid waits for its predecessor in the stream, so they overlap
+  // the predecessor's tail.  Activations and outputs are touched only after.
+  int in_flight = 0;          // stages issued and not yet consumed
   for (int s = 0; s < depth && fc.valid; ++s) {
     issue_item<CG>(fc, ring + s * p.stage_bytes, &bars[s], lane, policy);
     fc.advance(p, NWARPS, mt_hi);
     ++in_flight;
   }
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+#ifdef CB200_TIMING
+  long long tm_wait = 0, tm_comp = 0, tm_issue = 0, tm_epi = 0;
+  int tm_chunks = 0;
+#endif
+
   int slot = 0;               // stage the next item arrives in
   std::uint32_t parity = 0;   // phase of that stage's barrier
 
@@ -360,17 +476,29 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
   for (int nt = 0; nt < NT; ++nt) vmax[nt][0] = vmax[nt][1] = -INFINITY;
 
   bool dead = false;  // a wait ran out: stop computing, keep attending barriers
-  const int d_first = mt_lo < mt_hi ? find_desc(p, mt_lo) : p.n_desc;
   for (int d = d_first; d < p.n_desc; ++d) {
     const LinearDev* L = desc_table(p) + d;
     if (L->mt_begin >= mt_hi) break;
     const int LN = L->N, LK = L->K, LM = L->M;
     const int rsx = 2 * LK + 32;
+    const int G = LK >> 7;
+    float* bias = reinterpret_cast<float*>(xs + (LM + 1) * rsx);
+    std::uint16_t* y = L->y;
+#ifdef CB200_TIMING
+    const long long tf0 = clock64();
+#endif
     __syncthreads();  // every warp is done with the previous activations
     fill_x_fragments(xs, L->x, LM, LK, rsx, tid, NWARPS * 32);
     __syncthreads();
-    const int G = LK >> 7;
-    std::uint16_t* y = L->y;
+#ifdef CB200_TIMING
+    const long long tf1 = clock64();
+#endif
+    build_bias<NT>(xs, bias, G, rsx, LM, warp, lane, NWARPS);
+    __syncthreads();
+#ifdef CB200_TIMING
+    if (false)
+      printf("  desc %d: start->here %lld, fill %lld, bias %lld\n", d, tf0 - tm_start, tf1 - tf0, clock64() - tf1);
+#endif
 
     while (cc.valid && cc.d == d) {
       float acc[NT][4];
@@ -380,20 +508,35 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
       const int nch = cc.nch;
       for (int ch = 0; ch < nch; ++ch) {
         std::uint8_t* stage = ring + slot * p.stage_bytes;
+#ifdef CB200_TIMING
+        const long long tm0 = clock64();
+#endif
         if (!dead && !wait_stage(&bars[slot], parity)) {
           dead = true;
           if (lane == 0) atomicExch(p.status, CUDALM_B200_ERR_TIMEOUT);
         }
+#ifdef CB200_TIMING
+        const long long tm1 = clock64();
+        tm_wait += tm1 - tm0;
+#endif
         if (!dead) {
           const int g0 = ch * CG;
-          consume_chunk<NT, CG>(stage, xs, G, g0, min(CG, G - g0), rsx, LM, lane, acc);
+          consume_chunk<NT, CG>(stage, xs, bias, G, g0, min(CG, G - g0), rsx, LM, lane, acc);
           __syncwarp();
+#ifdef CB200_TIMING
+          const long long tm2 = clock64();
+          tm_comp += tm2 - tm1;
+          ++tm_chunks;
+#endif
           --in_flight;
           if (fc.valid) {
             issue_item<CG>(fc, stage, &bars[slot], lane, policy);
             fc.advance(p, NWARPS, mt_hi);
             ++in_flight;
           }
+#ifdef CB200_TIMING
+          tm_issue += clock64() - tm2;
+#endif
         }
         if (++slot == depth) {
           slot = 0;
@@ -401,6 +544,9 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
         }
         cc.advance(p, NWARPS, mt_hi);
       }
+#ifdef CB200_TIMING
+      const long long te0 = clock64();
+#endif
       if (!dead) {
         const int r8 = lane >> 2, t = lane & 3;
         const int row_lo = row0 + r8, row_hi = row_lo + 8;
@@ -431,9 +577,18 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
           }
         }
       }
+#ifdef CB200_TIMING
+      tm_epi += clock64() - te0;
+#endif
     }
   }
 
+#ifdef CB200_TIMING  // measurement aid: where one warp's cycles went
+  if (lane == 0 && (blockIdx.x % 6 == 3) && warp == 0)
+    printf("cta %3d mt [%d,%d) d_first %d K %d: chunks %d total %lld; per chunk wait %lld comp %lld issue %lld; epilogues %lld\n",
+           blockIdx.x, mt_lo, mt_hi, d_first, desc_table(p)[d_first < p.n_desc ? d_first : 0].K, tm_chunks, clock64() - tm_start, tm_wait / max(tm_chunks, 1),
+           tm_comp / max(tm_chunks, 1), tm_issue / max(tm_chunks, 1), tm_epi);
+#endif
   if (dead) {
     // Give copies still in flight a bounded chance to land before the CTA's
     // shared memory is released.
