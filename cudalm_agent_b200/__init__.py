@@ -5,13 +5,14 @@ for the C ABI; this package is its host-side mirror of the reference interface.
 """
 from .api import (CudalmB200Error, GROUP_SIZE, INT4_MAX, LinearGroup, LmHead, W4A16Linear,
                   batch_int4_gemv_bf16, device_status, gate_up_bf16, int4_gemv_bf16,
-                  launch_count, library_path, linear_multi, load_library, quantize_w4a16,
-                  topk_merge)
+                  launch_count, library_path, linear_multi, lm_head_static_scratch_bytes,
+                  lm_head_topk_static, load_library, quantize_w4a16, topk_merge)
 from .vocab_parallel import VocabParallelLmHead, merge_topk_host, shard_rows
 
 __all__ = [
     "CudalmB200Error", "GROUP_SIZE", "INT4_MAX", "LinearGroup", "LmHead", "W4A16Linear",
     "batch_int4_gemv_bf16", "device_status", "gate_up_bf16", "int4_gemv_bf16", "launch_count",
-    "library_path", "linear_multi", "load_library", "quantize_w4a16", "topk_merge",
+    "library_path", "linear_multi", "lm_head_static_scratch_bytes", "lm_head_topk_static",
+    "load_library", "quantize_w4a16", "topk_merge",
     "VocabParallelLmHead", "merge_topk_host", "shard_rows",
 ]

@@ -69,6 +69,9 @@ SIGNATURES = {
     "cudalm_b200_lm_head_workspace_bytes": (ctypes.c_size_t, [_ci, _ci, _ci, _ci, _ci]),
     "cudalm_b200_lm_head_topk": (_ci, [_vp, _vp, _vp, _ci, _ci, _ci, _ci, _ci, _vp, _vp, _vp,
                                       _vp, _vp, ctypes.c_size_t, _vp]),
+    "cudalm_b200_lm_head_static_scratch_bytes": (ctypes.c_size_t, []),
+    "cudalm_b200_lm_head_topk_static": (_ci, [_vp, _vp, _vp, _ci, _ci, _ci, _ci, _ci, _vp, _vp, _vp,
+                                             _vp, _vp]),
     "cudalm_b200_topk_merge": (_ci, [_vp, _vp, _ci, _ci, _ci, _vp, _vp, _vp, _vp]),
     "cudalm_b200_quantize_w4a16": (_ci, [_vp, _ci, _ci, _vp, _vp, _vp]),
     "cudalm_b200_kernel_regs": (_ci, [ctypes.c_char_p]),
@@ -326,6 +329,41 @@ class LmHead:
             self.workspace.numel(), _stream())
         _check("lm_head_topk", st)
         return self.argmax[:M], self.topk_idx[:M], self.topk_val[:M]
+
+
+def lm_head_static_scratch_bytes() -> int:
+    """Size of the fixed scratch array ``lm_head_topk_static`` uses (bytes held
+    on every GPU that loads the library)."""
+    return int(load_library().cudalm_b200_lm_head_static_scratch_bytes())
+
+
+def lm_head_topk_static(rows: W4A16Linear, x: torch.Tensor, logits_out: torch.Tensor,
+                        argmax_out: torch.Tensor, topk_idx: torch.Tensor, topk_val: torch.Tensor,
+                        id_offset: int = 0) -> None:
+    """The vocabulary projection and pick of ``LmHead.forward`` for callers that
+    cannot allocate device memory for a workspace (a server whose pools own the
+    whole GPU, a decode loop where ``cudaMalloc`` is forbidden): the scratch is a
+    fixed array inside the library, nothing is allocated by the call, and every
+    output buffer -- the ``[M, N]`` logits included -- is the caller's.
+
+    At most 32 activation rows per call.  All calls on a device share the one
+    scratch array, so calls that could overlap on the GPU (different streams,
+    unordered) race; order them.  Make the first call on a device outside any
+    stream capture."""
+    _need(x, torch.bfloat16, "x")
+    _need(logits_out, torch.bfloat16, "logits_out")
+    _need(argmax_out, torch.int32, "argmax_out")
+    _need(topk_idx, torch.int32, "topk_idx")
+    _need(topk_val, torch.bfloat16, "topk_val")
+    M = 1 if x.dim() == 1 else int(x.shape[0])
+    top_k = int(topk_idx.shape[-1])
+    if logits_out.numel() < M * rows.N or topk_idx.numel() < M * top_k or \
+            topk_val.numel() < M * top_k or argmax_out.numel() < M:
+        raise ValueError("an output buffer is too small")
+    st = load_library().cudalm_b200_lm_head_topk_static(
+        _ptr(rows.weight), _ptr(rows.scale), _ptr(x), rows.N, rows.K, M, top_k, id_offset,
+        _ptr(logits_out), _ptr(argmax_out), _ptr(topk_idx), _ptr(topk_val), _stream())
+    _check("lm_head_topk_static", st)
 
 
 def topk_merge(list_idx: torch.Tensor, list_val: torch.Tensor):

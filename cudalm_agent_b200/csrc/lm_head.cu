@@ -384,3 +384,78 @@ int cudalm_b200_topk_merge(const int32_t* list_idx, const uint16_t* list_val, in
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Allocation-free variant of the vocabulary projection.
+//
+// Some callers of this library may not allocate device memory at the moment
+// they need a token pick: an inference server that has handed all of the GPU's
+// memory to its own pools at start-up, a decode step that runs inside a
+// latency-critical loop where a cudaMalloc (which synchronises the device) is
+// forbidden, or a host language binding that has no allocator for device
+// memory at all.  For them the scratch that cudalm_b200_lm_head_topk takes as
+// `workspace` lives here instead, in a fixed array inside the library's device
+// image.  Every GPU that loads the library holds these bytes until the process
+// exits.  The caller still passes every input and output, the logits buffer
+// included.
+//
+// The array's name is a host-side stand-in in host code, not a device address:
+// the address is taken once per device with cudaGetSymbolAddress, with that
+// device current, and that pointer is what the kernels receive.
+// ---------------------------------------------------------------------------
+namespace cb200 {
+namespace {
+
+constexpr int kStaticMaxRows = 32;  // activation rows per call
+// counts + per-CTA maxima + candidate lists for kStaticMaxRows rows (the same
+// layout workspace_layout() produces for a caller-provided logits buffer)
+constexpr size_t kStaticScratchBytes =
+    kCountsBytes + static_cast<size_t>(kMaxCtas) * kStaticMaxRows * sizeof(float) +
+    static_cast<size_t>(kStaticMaxRows) * kCandCap * sizeof(std::uint64_t);
+
+static __device__ __align__(256) unsigned char g_lm_head_scratch[kStaticScratchBytes];
+
+// Device address of the scratch array on the current device (looked up once per
+// device; the first call on a device performs the lookup).
+int static_scratch(void** out) {
+  static std::atomic<void*> cached[64];
+  int dev = 0;
+  CB200_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return CUDALM_B200_ERR_UNSUPPORTED;
+  void* p = cached[dev].load(std::memory_order_acquire);
+  if (!p) {
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_lm_head_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      g_last_cuda_error = static_cast<int>(e);
+      return CUDALM_B200_ERR_CUDA;
+    }
+    cached[dev].store(p, std::memory_order_release);
+  }
+  *out = p;
+  return CUDALM_B200_OK;
+}
+
+}  // namespace
+}  // namespace cb200
+
+extern "C" {
+
+size_t cudalm_b200_lm_head_static_scratch_bytes(void) { return cb200::kStaticScratchBytes; }
+
+int cudalm_b200_lm_head_topk_static(const uint8_t* weight, const uint16_t* scales,
+                                    const uint16_t* x, int N, int K, int M, int top_k,
+                                    int id_offset, uint16_t* logits_out, int32_t* argmax_out,
+                                    int32_t* topk_idx, uint16_t* topk_val, void* stream) {
+  if (!logits_out) return CUDALM_B200_ERR_NULL;  // the logits are an output here, never scratch
+  if (M > cb200::kStaticMaxRows) return CUDALM_B200_ERR_TOO_LARGE;
+  if (M >= 1 && N >= 1 &&
+      cudalm_b200_lm_head_workspace_bytes(N, K, M, top_k, 0) > cb200::kStaticScratchBytes)
+    return CUDALM_B200_ERR_TOO_LARGE;
+  void* scratch = nullptr;
+  if (int rc = cb200::static_scratch(&scratch)) return rc;
+  return cudalm_b200_lm_head_topk(weight, scales, x, N, K, M, top_k, id_offset, logits_out,
+                                  argmax_out, topk_idx, topk_val, scratch,
+                                  cb200::kStaticScratchBytes, stream);
+}
+
+}  // extern "C"

@@ -154,6 +154,33 @@ CUDALM_B200_API int cudalm_b200_lm_head_topk(
     int32_t* topk_idx, uint16_t* topk_val, void* workspace, size_t workspace_bytes,
     void* stream);
 
+/* ---- vocabulary projection without any allocation ------------------------------
+ * (No counterpart in CUDALM: its lm_head call needs no scratch because it
+ * leaves the token pick to the host.)
+ *
+ * Same computation and outputs as cudalm_b200_lm_head_topk, for callers that
+ * cannot allocate device memory for the workspace -- a server whose memory pools
+ * own the whole GPU, a decode loop in which cudaMalloc is forbidden because it
+ * synchronises the device, a binding with no device allocator.  The scratch is
+ * a fixed array of cudalm_b200_lm_head_static_scratch_bytes() (about 640 KB)
+ * inside the library's device image; every GPU that loads the library holds it
+ * until the process exits.  The call itself allocates nothing.
+ *
+ * Limits: M <= 32 activation rows per call (more: CUDALM_B200_ERR_TOO_LARGE);
+ * logits_out is required (CUDALM_B200_ERR_NULL when null).
+ * The first call on each device looks up the array's device address; make that
+ * first call before any stream capture begins on the device.
+ * All calls on a device share the one array, which keeps the previous call's
+ * contents (the entry point clears what must start at zero): two calls whose
+ * kernels overlap on the GPU -- different streams, no ordering between them --
+ * race on it.  Order such calls, or use cudalm_b200_lm_head_topk with one
+ * workspace per stream. */
+CUDALM_B200_API size_t cudalm_b200_lm_head_static_scratch_bytes(void);
+CUDALM_B200_API int cudalm_b200_lm_head_topk_static(
+    const uint8_t* weight, const uint16_t* scales, const uint16_t* x, int N, int K,
+    int M, int top_k, int id_offset, uint16_t* logits_out, int32_t* argmax_out,
+    int32_t* topk_idx, uint16_t* topk_val, void* stream);
+
 /* Merges n_lists candidate lists (one per vocabulary shard, gathered from the
  * ranks) into the final pick: list_idx/list_val are [n_lists, M, k]; ids < 0 are
  * padding.  Same ordering rule; n_lists * k <= 2048. */
