@@ -312,6 +312,60 @@ def bench_lm_head(eng, torch, dist, rank, world, steps, warmup):
     return out
 
 
+def bench_cohorts(eng, torch, steps, warmup):
+    """Batched decode (BASELINE configs[2]): M = 8, 16, 32, 64 rows through the
+    MLP projections of 24 layers -- fused gate+up (K=1024 -> 2 x 3584) and down
+    (K=3584 -> 1024), distinct weights per layer (137 MB of weights > L2)."""
+    gen = torch.Generator(device="cuda").manual_seed(SEED + 2)
+    layers = []
+    for _ in range(24):
+        ws = []
+        for N, K in ((3584, 1024), (3584, 1024), (1024, 3584)):
+            w = (torch.randn((N, K), generator=gen, device="cuda", dtype=torch.float32) * 0.02
+                 ).to(torch.bfloat16)
+            ws.append(eng.W4A16Linear(*eng.quantize_w4a16(w)))
+        layers.append(ws)
+    out = {}
+    for M in (8, 16, 32, 64):
+        x = torch.randn((M, 1024), generator=gen, device="cuda", dtype=torch.float32)
+        x[torch.rand((M, 1024), generator=gen, device="cuda") < 0.01] *= 20.0
+        x = x.to(torch.bfloat16)
+        h = torch.randn((M, 3584), generator=gen, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+        gy = torch.empty((M, 3584), device="cuda", dtype=torch.bfloat16)
+        uy = torch.empty((M, 3584), device="cuda", dtype=torch.bfloat16)
+        dy = torch.empty((M, 1024), device="cuda", dtype=torch.bfloat16)
+
+        def step(i):
+            for g, u, d in layers:
+                eng.gate_up_bf16(g, u, x, gy, uy)
+                eng.batch_int4_gemv_bf16(d.weight, d.scale, h, dy)
+
+        l0 = eng.launch_count()
+        total_ms, _ = time_steps(torch, step, steps, warmup)
+        launches = (eng.launch_count() - l0) // (steps + warmup)
+        nbytes = sum(g.bytes(M) + u.bytes(M) - M * 1024 * 2 + d.bytes(M) for g, u, d in layers)
+        flops = 2 * M * 24 * (2 * 3584 * 1024 + 1024 * 3584)
+        sec = total_ms * 1e-3 / steps
+        out[f"M{M}"] = {"gbps": nbytes / sec / 1e9, "tflops": flops / sec / 1e12,
+                        "us_per_pass": sec * 1e6, "launches_per_pass": int(launches),
+                        "bytes_per_pass": nbytes}
+    return out
+
+
+def bench_quantize(eng, torch, steps, warmup):
+    """GPU quantize+pack (BASELINE configs[4]): GB/s of bf16 input consumed."""
+    gen = torch.Generator(device="cuda").manual_seed(SEED + 4)
+    out = {}
+    for N, K in ((248320, 1024), (6144, 1024), (1024, 3584)):
+        ws = [(torch.randn((N, K), generator=gen, device="cuda", dtype=torch.float32) * 0.02
+               ).to(torch.bfloat16) for _ in range(2 if N > 100000 else 8)]
+        total_ms, _ = time_steps(torch, lambda i: eng.quantize_w4a16(ws[i % len(ws)]), steps, warmup)
+        sec = total_ms * 1e-3 / steps
+        out[f"{N}x{K}"] = {"input_gbps": N * K * 2 / sec / 1e9,
+                           "traffic_gbps": N * K * 2.515625 / sec / 1e9, "us": sec * 1e6}
+    return out
+
+
 def run_ours(args):
     import torch
     import cudalm_agent_b200 as eng
@@ -396,6 +450,13 @@ def run_ours(args):
     lm = {} if args.only == "set" else bench_lm_head(eng, torch, dist, rank, world,
                                                       max(5, min(args.steps, 50)), 3)
 
+    cohorts, quant = {}, {}
+    if args.only == "all" and rank == 0:
+        cohorts = bench_cohorts(eng, torch, max(5, min(args.steps, 20)), 3)
+        quant = bench_quantize(eng, torch, max(5, min(args.steps, 20)), 3)
+    if dist is not None:
+        dist.barrier()
+
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
@@ -426,6 +487,9 @@ def run_ours(args):
                          "ms_per_pass": lat_ms / lat_steps,
                          "gbps": bytes_step * lat_steps / (lat_ms * 1e-3) / 1e9,
                          "us_per_call": lat_ms * 1e3 / lat_steps / 132},
+        "batched_decode": {"what": "24 layers x (fused gate+up 1024->2x3584, down 3584->1024), "
+                                   "bf16 activations with 1% x20 outliers", **cohorts},
+        "quantize": quant,
         "lm_head": {"vocab": VOCAB, "K": HIDDEN, "top_k": TOP_K, "n_gpus": world,
                     "scaling": "strong (vocabulary rows split over ranks, one all-gather of "
                                "candidates)" if world > 1 else "single GPU", **lm},

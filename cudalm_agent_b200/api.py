@@ -73,6 +73,7 @@ SIGNATURES = {
     "cudalm_b200_lm_head_topk_static": (_ci, [_vp, _vp, _vp, _ci, _ci, _ci, _ci, _ci, _vp, _vp, _vp,
                                              _vp, _vp]),
     "cudalm_b200_topk_merge": (_ci, [_vp, _vp, _ci, _ci, _ci, _vp, _vp, _vp, _vp]),
+    "cudalm_b200_topk_merge_packed": (_ci, [_vp, _ci, _ci, _ci, _ci, _ci, _vp, _vp, _vp, _vp]),
     "cudalm_b200_quantize_w4a16": (_ci, [_vp, _ci, _ci, _vp, _vp, _vp]),
     "cudalm_b200_kernel_regs": (_ci, [ctypes.c_char_p]),
     "cudalm_b200_launch_count": (ctypes.c_int64, []),
@@ -291,6 +292,26 @@ def quantize_w4a16(W: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     return packed, scale
 
 
+def packed_words(rows: int, k: int) -> int:
+    """32-bit words of one packed candidate buffer: ids int32 ``[rows][k]`` then
+    values bf16 ``[rows][k]``."""
+    return rows * k + (rows * k + 1) // 2
+
+
+def topk_merge_packed(gathered: torch.Tensor, rows_cap: int, M: int, k: int):
+    """Merges ``[L, packed_words(rows_cap, k)]`` gathered candidate buffers."""
+    _need(gathered, torch.int32, "gathered")
+    L, words = int(gathered.shape[0]), int(gathered.shape[1])
+    dev = gathered.device
+    argmax = torch.empty(M, dtype=torch.int32, device=dev)
+    idx = torch.empty((M, k), dtype=torch.int32, device=dev)
+    val = torch.empty((M, k), dtype=torch.bfloat16, device=dev)
+    st = load_library().cudalm_b200_topk_merge_packed(_ptr(gathered), L, words, rows_cap, M, k,
+                                                      _ptr(argmax), _ptr(idx), _ptr(val), _stream())
+    _check("topk_merge_packed", st)
+    return argmax, idx, val
+
+
 class LmHead:
     """Vocabulary projection stored as W4A16 with an on-device pick.
 
@@ -314,8 +335,12 @@ class LmHead:
         # 256-byte aligned by the caching allocator (512-byte granularity)
         self.workspace = torch.empty(nbytes, dtype=torch.uint8, device=dev)
         self.argmax = torch.empty(max_rows, dtype=torch.int32, device=dev)
-        self.topk_idx = torch.empty((max_rows, top_k), dtype=torch.int32, device=dev)
-        self.topk_val = torch.empty((max_rows, top_k), dtype=torch.bfloat16, device=dev)
+        # ids and values share one buffer so that a vocabulary-parallel caller can
+        # send both with a single all-gather: int32 [R][k] then bf16 [R][k]
+        n = max_rows * top_k
+        self.packed = torch.empty(packed_words(max_rows, top_k), dtype=torch.int32, device=dev)
+        self.topk_idx = self.packed[:n].view(max_rows, top_k)
+        self.topk_val = self.packed[n:].view(torch.bfloat16)[:n].view(max_rows, top_k)
 
     def forward(self, x: torch.Tensor):
         _need(x, torch.bfloat16, "x")

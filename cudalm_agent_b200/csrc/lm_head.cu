@@ -171,6 +171,8 @@ struct SelectArgs {
   const std::uint16_t* list_val;
   int n_lists;
   int list_k;
+  long long idx_stride;  // elements from one list's ids to the next list's
+  long long val_stride;  // likewise for the values
   // full logits of this shard, for the exact search after an overflow
   const std::uint16_t* logits;
   int N;
@@ -200,9 +202,10 @@ lm_head_select_kernel(const SelectArgs a) {
     n = a.n_lists * a.list_k;  // host guarantees n <= kCandCap
     for (int i = tid; i < n; i += kSelectThreads) {
       const int l = i / a.list_k, j = i - l * a.list_k;
-      const size_t src = (static_cast<size_t>(l) * a.rows + m) * a.list_k + j;
-      const std::int32_t id = a.list_idx[src];
-      buf[i] = id < 0 ? 0ull : make_composite(a.list_val[src], static_cast<std::uint32_t>(id));
+      const size_t within = static_cast<size_t>(m) * a.list_k + j;
+      const std::int32_t id = a.list_idx[static_cast<size_t>(l) * a.idx_stride + within];
+      const std::uint16_t v = a.list_val[static_cast<size_t>(l) * a.val_stride + within];
+      buf[i] = id < 0 ? 0ull : make_composite(v, static_cast<std::uint32_t>(id));
     }
   }
 
@@ -374,6 +377,8 @@ int cudalm_b200_topk_merge(const int32_t* list_idx, const uint16_t* list_val, in
   a.list_val = list_val;
   a.n_lists = n_lists;
   a.list_k = k;
+  a.idx_stride = static_cast<long long>(M) * k;
+  a.val_stride = static_cast<long long>(M) * k;
   a.rows = M;
   a.k = k;
   a.argmax_out = argmax_out;
@@ -459,3 +464,32 @@ int cudalm_b200_lm_head_topk_static(const uint8_t* weight, const uint16_t* scale
 }
 
 }  // extern "C"
+
+// Merge of candidate lists that arrive packed as one buffer per rank, the form
+// in which a single all-gather delivers them: per rank `words_per_list` 32-bit
+// words = ids int32 [rows_cap][k] followed by values bf16 [rows_cap][k].
+extern "C" int cudalm_b200_topk_merge_packed(const int32_t* gathered, int n_lists,
+                                             int words_per_list, int rows_cap, int M, int k,
+                                             int32_t* argmax_out, int32_t* topk_idx,
+                                             uint16_t* topk_val, void* stream) {
+  if (!gathered || !topk_idx || !topk_val) return CUDALM_B200_ERR_NULL;
+  if (n_lists < 1 || M < 1 || k < 1 || rows_cap < M) return CUDALM_B200_ERR_BAD_SHAPE;
+  const long long need = static_cast<long long>(rows_cap) * k + (static_cast<long long>(rows_cap) * k + 1) / 2;
+  if (words_per_list < need) return CUDALM_B200_ERR_BAD_SHAPE;
+  if (k > kMaxTopK || static_cast<long long>(n_lists) * k > kCandCap) return CUDALM_B200_ERR_TOO_LARGE;
+  SelectArgs a;
+  std::memset(&a, 0, sizeof(a));
+  a.list_idx = gathered;
+  a.list_val = reinterpret_cast<const std::uint16_t*>(gathered + static_cast<size_t>(rows_cap) * k);
+  a.n_lists = n_lists;
+  a.list_k = k;
+  a.idx_stride = words_per_list;
+  a.val_stride = 2ll * words_per_list;
+  a.rows = M;
+  a.k = k;
+  a.argmax_out = argmax_out;
+  a.topk_idx = topk_idx;
+  a.topk_val = topk_val;
+  lm_head_select_kernel<<<M, kSelectThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  return check_launch();
+}

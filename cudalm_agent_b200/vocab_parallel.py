@@ -78,12 +78,33 @@ def merge_topk_host(lists_idx: Sequence[torch.Tensor], lists_val: Sequence[torch
     return out_idx[:, 0].clone(), out_idx, out_val
 
 
+def gather_packed(packed: torch.Tensor, group=None) -> torch.Tensor:
+    """All-gathers one rank's packed candidate buffer (int32, see
+    ``api.packed_words``) into ``[world, words]`` with ONE collective.  int32 is
+    carried by every backend, which is what lets the multi-rank logic be tested
+    with gloo on CPU."""
+    world = dist.get_world_size(group)
+    out = torch.empty((world, packed.numel()), dtype=torch.int32, device=packed.device)
+    dist.all_gather_into_tensor(out.view(-1), packed.contiguous().view(-1), group=group)
+    return out
+
+
+def unpack_candidates(gathered: torch.Tensor, rows: int, k: int):
+    """``[world, words]`` -> per-rank lists of ids int32 ``[rows, k]`` and values
+    bf16 ``[rows, k]`` (host-side form, for ``merge_topk_host``)."""
+    n = rows * k
+    ids = [g[:n].view(rows, k) for g in gathered]
+    vals = [g[n:].contiguous().view(torch.bfloat16)[:n].view(rows, k) for g in gathered]
+    return ids, vals
+
+
 class VocabParallelLmHead:
     """Rank-local half of the vocabulary-parallel lm_head.
 
     ``local`` is an ``LmHead`` over this rank's rows with ``id_offset`` set to
     the block's first token id.  ``forward(x)`` runs the local pick, all-gathers
-    the ``[M, k]`` ids and values (one collective each) and merges on the device.
+    the packed ``[max_rows, k]`` ids and values (one collective) and merges on
+    the device.
     """
 
     def __init__(self, local, group: Optional[dist.ProcessGroup] = None):
@@ -92,18 +113,13 @@ class VocabParallelLmHead:
         self.local = local
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
-        k, dev = local.top_k, local.argmax.device
-        self._gidx = torch.empty((self.world, local.max_rows, k), dtype=torch.int32, device=dev)
-        self._gval = torch.empty((self.world, local.max_rows, k), dtype=torch.bfloat16, device=dev)
+        self._gathered = torch.empty((self.world, local.packed.numel()), dtype=torch.int32,
+                                     device=local.packed.device)
 
     def forward(self, x: torch.Tensor):
-        from .api import topk_merge
+        from .api import topk_merge_packed
         argmax, idx, val = self.local.forward(x)
         if self.world == 1:
             return argmax, idx, val
-        M = idx.shape[0]
-        gi = self._gidx[:, :M].contiguous() if M != self.local.max_rows else self._gidx
-        gv = self._gval[:, :M].contiguous() if M != self.local.max_rows else self._gval
-        dist.all_gather_into_tensor(gi.view(-1), idx.contiguous().view(-1), group=self.group)
-        dist.all_gather_into_tensor(gv.view(-1), val.contiguous().view(-1), group=self.group)
-        return topk_merge(gi, gv)
+        dist.all_gather_into_tensor(self._gathered.view(-1), self.local.packed, group=self.group)
+        return topk_merge_packed(self._gathered, self.local.max_rows, idx.shape[0], self.local.top_k)

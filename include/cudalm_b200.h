@@ -189,6 +189,15 @@ CUDALM_B200_API int cudalm_b200_topk_merge(const int32_t* list_idx, const uint16
                                            int32_t* topk_idx, uint16_t* topk_val,
                                            void* stream);
 
+/* The same merge for lists that arrive packed, one buffer of `words_per_list`
+ * 32-bit words per shard: ids int32 [rows_cap][k] followed by values bf16
+ * [rows_cap][k] (the layout in which ONE all-gather delivers them). */
+CUDALM_B200_API int cudalm_b200_topk_merge_packed(const int32_t* gathered, int n_lists,
+                                                  int words_per_list, int rows_cap, int M,
+                                                  int k, int32_t* argmax_out,
+                                                  int32_t* topk_idx, uint16_t* topk_val,
+                                                  void* stream);
+
 /* ---- quantize + pack --------------------------------------------------------
  * GPU form of CUDALM's offline quantizer quantize_w4a16
  * (CUDALM tools/common/w4a16_quant.py:25-60): bf16 W [N, K] ->

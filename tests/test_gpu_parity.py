@@ -362,3 +362,30 @@ def test_second_opinion_reference_cuda_kernel(eng, orc):
         ours = from_dev(eng.int4_gemv_bf16(dW, dS, dx))
         check_close(orc, ours, want, f"this library vs CPU {N}x{K}")
         check_close(orc, ours, from_dev(y_ref), f"this library vs reference CUDA kernel {N}x{K}")
+
+
+def test_packed_merge_equals_host_merge(eng, orc):
+    # the single-all-gather form: per shard ids int32 [R][k] then values bf16 [R][k]
+    import torch
+    rng = np.random.default_rng(14)
+    L, R, M, k = 4, 8, 5, 50
+    words = eng.packed_words(R, k)
+    bufs, li, lv = [], [], []
+    for r in range(L):
+        vals = orc.f32_to_bf16_bits(np.round(rng.standard_normal((R, 500)) * 4).astype(np.float32) / 4)
+        ids = np.full((R, k), -1, np.int32)
+        vv = np.zeros((R, k), np.uint16)
+        for m in range(R):
+            i, v = orc.topk_bf16(vals[m], k)
+            ids[m], vv[m] = i + 500 * r, v
+        buf = np.zeros(words, np.int32)
+        buf[:R * k] = ids.ravel()
+        buf[R * k:R * k + R * k // 2] = vv.ravel().view(np.int32)
+        bufs.append(buf)
+        li.append(torch.from_numpy(ids[:M].copy()))
+        lv.append(to_dev(vv[:M].copy(), torch.bfloat16).cpu())
+    argmax, idx, val = eng.topk_merge_packed(to_dev(np.stack(bufs)), R, M, k)
+    h_arg, h_idx, h_val = eng.merge_topk_host(li, lv, k)
+    assert np.array_equal(from_dev(idx), h_idx.numpy())
+    assert np.array_equal(from_dev(val), from_dev(h_val.cuda()))
+    assert np.array_equal(from_dev(argmax), h_arg.numpy())
