@@ -217,7 +217,41 @@ EncodeTiledFn encode_tiled_fn() {
 
 // Describes the packed weight matrix to the TMA unit as uint32 [N][K/8] with a
 // box of 16 rows x kCG*16 words (= kCG groups of 128 nibbles per row).
+// A tensor map depends only on (address, N, K), so encodings are kept in a small
+// direct-mapped cache: the decode loop calls the same projections every step.
+struct MapCacheEntry {
+  const std::uint8_t* weight = nullptr;
+  int N = 0, K = 0;
+  CUtensorMap map;
+};
+constexpr int kMapCacheSize = 512;
+
+int encode_weight_map_uncached(const std::uint8_t* weight, int N, int K, CUtensorMap* out);
+
 int encode_weight_map(const std::uint8_t* weight, int N, int K, CUtensorMap* out) {
+  static std::mutex mu;
+  static MapCacheEntry cache[kMapCacheSize];
+  const std::uintptr_t h = reinterpret_cast<std::uintptr_t>(weight);
+  const int slot = static_cast<int>(((h >> 8) ^ (h >> 17) ^ static_cast<std::uintptr_t>(N) * 31u) %
+                                    kMapCacheSize);
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    const MapCacheEntry& e = cache[slot];
+    if (e.weight == weight && e.N == N && e.K == K) {
+      *out = e.map;
+      return CUDALM_B200_OK;
+    }
+  }
+  if (int rc = encode_weight_map_uncached(weight, N, K, out)) return rc;
+  std::lock_guard<std::mutex> lk(mu);
+  cache[slot].weight = weight;
+  cache[slot].N = N;
+  cache[slot].K = K;
+  cache[slot].map = *out;
+  return CUDALM_B200_OK;
+}
+
+int encode_weight_map_uncached(const std::uint8_t* weight, int N, int K, CUtensorMap* out) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return CUDALM_B200_ERR_CUDA;
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K / 8), static_cast<cuuint64_t>(N)};
