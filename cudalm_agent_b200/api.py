@@ -75,6 +75,7 @@ SIGNATURES = {
     "cudalm_b200_topk_merge": (_ci, [_vp, _vp, _ci, _ci, _ci, _vp, _vp, _vp, _vp]),
     "cudalm_b200_topk_merge_packed": (_ci, [_vp, _ci, _ci, _ci, _ci, _ci, _vp, _vp, _vp, _vp]),
     "cudalm_b200_quantize_w4a16": (_ci, [_vp, _ci, _ci, _vp, _vp, _vp]),
+    "cudalm_b200_set_tensor_path_min_rows": (_ci, [_ci]),
     "cudalm_b200_kernel_regs": (_ci, [ctypes.c_char_p]),
     "cudalm_b200_launch_count": (ctypes.c_int64, []),
 }
@@ -135,6 +136,12 @@ def device_status() -> int:
     out = _ci(0)
     _check("device_status", load_library().cudalm_b200_device_status(ctypes.byref(out)))
     return out.value
+
+
+def set_tensor_path_min_rows(min_rows: int) -> int:
+    """Batched calls with at least this many rows take the tcgen05 kernel
+    (default 16); returns the previous value."""
+    return int(load_library().cudalm_b200_set_tensor_path_min_rows(int(min_rows)))
 
 
 def launch_count() -> int:

@@ -1,6 +1,7 @@
 // W4A16 linear projections: M = 1 GEMV, batched rows, several projections per
 // launch, fused gate+up.  Host entry points of the C ABI plus the streaming
 // kernel they launch.
+#include <atomic>
 #include <cstdio>
 #include <cstring>
 #include <mutex>
@@ -9,6 +10,13 @@
 #include "w4a16_stream.cuh"
 
 namespace cb200 {
+
+// tensor-memory path for batched rows (w4a16_tc.cu)
+bool tc_eligible(const cudalm_b200_linear& l);
+int run_tc(const cudalm_b200_linear* ls, int count, cudaStream_t stream);
+// Smallest M that takes the tensor-memory kernel (runtime knob; see
+// cudalm_b200_set_tensor_path_min_rows).
+std::atomic<int> g_tc_min_rows{16};
 
 // ---------------------------------------------------------------------------
 // Fallback for inputs the streaming kernel does not take: a weight base that is
@@ -294,6 +302,28 @@ int run_fallback(const cudalm_b200_linear& l, cudaStream_t stream) {
 // One projection with any M: passes of as many rows as fit in shared memory.
 int run_single(cudalm_b200_linear l, cudaStream_t stream) {
   if (int rc = validate(l)) return rc;
+  if (l.M >= g_tc_min_rows.load(std::memory_order_relaxed) && aligned_to(l.weight, 16)) {
+    // widest pass whose activations fit in shared memory beside the stages
+    int rows = 0;
+    for (int r : {64, 32, 16}) {
+      cudalm_b200_linear probe = l;
+      probe.M = r;
+      if (tc_eligible(probe)) {
+        rows = r;
+        break;
+      }
+    }
+    if (rows > 0) {
+      for (int m0 = 0; m0 < l.M; m0 += rows) {
+        cudalm_b200_linear part = l;
+        part.M = (l.M - m0 < rows) ? (l.M - m0) : rows;
+        part.x = l.x + static_cast<std::size_t>(m0) * l.K;
+        part.y = l.y + static_cast<std::size_t>(m0) * l.N;
+        if (int rc = run_tc(&part, 1, stream)) return rc;
+      }
+      return CUDALM_B200_OK;
+    }
+  }
   if (!stream_eligible(l)) return run_fallback(l, stream);
   const int per_pass = max_rows_per_pass(l.K);
   if (per_pass == 0) return run_fallback(l, stream);
@@ -388,6 +418,14 @@ int cudalm_b200_linear_multi(const cudalm_b200_linear* linears, int count, void*
     all_stream &= stream_eligible(linears[i]);
     kmax = linears[i].K > kmax ? linears[i].K : kmax;
     mmax = linears[i].M > mmax ? linears[i].M : mmax;
+  }
+  if (mmax >= g_tc_min_rows.load(std::memory_order_relaxed)) {
+    bool all_tc = true;
+    for (int i = 0; i < count; ++i) all_tc &= tc_eligible(linears[i]);
+    cudalm_b200_linear widest = linears[0];
+    widest.M = mmax;
+    widest.K = kmax;
+    if (all_tc && tc_eligible(widest)) return run_tc(linears, count, st);
   }
   Plan pl;
   if (!all_stream || mmax > CUDALM_B200_MAX_GROUP_M || !make_plan(kmax, mmax, &pl)) {
@@ -524,6 +562,11 @@ int cudalm_b200_group_destroy(cudalm_b200_group* group) {
     return CUDALM_B200_ERR_CUDA;
   }
   return CUDALM_B200_OK;
+}
+
+int cudalm_b200_set_tensor_path_min_rows(int min_rows) {
+  if (min_rows < 1) min_rows = 1;
+  return g_tc_min_rows.exchange(min_rows);
 }
 
 int64_t cudalm_b200_group_bytes(const cudalm_b200_group* group) {

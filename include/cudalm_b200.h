@@ -206,6 +206,14 @@ CUDALM_B200_API int cudalm_b200_topk_merge_packed(const int32_t* gathered, int n
 CUDALM_B200_API int cudalm_b200_quantize_w4a16(const uint16_t* w_bf16, int N, int K,
                                uint8_t* packed, uint16_t* scales, void* stream);
 
+/* ---- runtime knob -------------------------------------------------------------
+ * Batched calls with M >= min_rows rows take the tcgen05 / tensor-memory kernel
+ * (when its shared-memory budget allows), smaller ones the streaming kernel.
+ * Default 16.  Returns the previous value.  (CUDALM has no counterpart: its
+ * batch kernel is the M = 1 kernel with blockIdx.y = b,
+ * src/kernels/batch_decode.cu:95-190.) */
+CUDALM_B200_API int cudalm_b200_set_tensor_path_min_rows(int min_rows);
+
 /* ---- introspection ---------------------------------------------------------
  * Registers per thread / static+dynamic shared memory of the named kernel
  * (CUDALM exposes the same for its kernels: int4_gemv_bf16_rowtile4_regs(),

@@ -389,3 +389,41 @@ def test_packed_merge_equals_host_merge(eng, orc):
     assert np.array_equal(from_dev(idx), h_idx.numpy())
     assert np.array_equal(from_dev(val), from_dev(h_val.cuda()))
     assert np.array_equal(from_dev(argmax), h_arg.numpy())
+
+
+@pytest.mark.parametrize("N,K,M", [(256, 128, 16), (100, 384, 17), (513, 1024, 32), (7168, 1024, 64),
+                                   (1024, 3584, 64), (1024, 2048, 48), (33, 4096, 16), (1023, 1024, 64)])
+def test_tensor_memory_path_shapes(eng, orc, N, K, M):
+    # M >= 16 takes the tcgen05 kernel (several passes when the activations do not
+    # fit shared memory at once); the streaming kernel on the same inputs must agree
+    W, S = raw_weights(N, K, 300 + N + M)
+    x = make_x(orc, (M, K), 301 + K, "outlier")
+    want = orc.batch_gemv_bf16(W, S, x, threads=8)
+    prev = eng.set_tensor_path_min_rows(16)
+    try:
+        got_tc = gpu_batch(eng, W, S, x)
+        eng.set_tensor_path_min_rows(1 << 30)
+        got_stream = gpu_batch(eng, W, S, x)
+    finally:
+        eng.set_tensor_path_min_rows(prev)
+    check_close(orc, got_tc, want, f"tensor-memory path {N}x{K} M={M}")
+    check_close(orc, got_stream, want, f"streaming path {N}x{K} M={M}")
+    check_close(orc, got_tc, got_stream, f"tensor-memory vs streaming {N}x{K} M={M}")
+
+
+def test_tensor_memory_path_zero_and_boundary_inputs(eng, orc):
+    for kind, xkind in (("zero", "normal"), ("boundary", "normal"), ("random", "zero")):
+        W, S = raw_weights(700, 1024, 9, kind)
+        x = make_x(orc, (32, 1024), 10, xkind)
+        got = gpu_batch(eng, W, S, x)
+        check_close(orc, got, orc.batch_gemv_bf16(W, S, x, threads=8), f"tc {kind}/{xkind}")
+        if kind == "zero" or xkind == "zero":
+            assert np.all((got & 0x7FFF) == 0)
+
+
+def test_tensor_memory_path_is_deterministic(eng, orc):
+    W, S = raw_weights(3584, 1024, 11)
+    x = make_x(orc, (64, 1024), 12)
+    a = gpu_batch(eng, W, S, x)
+    for _ in range(3):
+        assert np.array_equal(a, gpu_batch(eng, W, S, x))
