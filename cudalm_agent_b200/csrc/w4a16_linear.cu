@@ -14,6 +14,10 @@ namespace cb200 {
 // tensor-memory path for batched rows (w4a16_tc.cu)
 bool tc_eligible(const cudalm_b200_linear& l);
 int run_tc(const cudalm_b200_linear* ls, int count, cudaStream_t stream);
+struct TcGroup;
+int tc_group_create(const cudalm_b200_linear* ls, int count, TcGroup** out);
+int tc_group_run(const TcGroup* g, cudaStream_t stream);
+void tc_group_destroy(TcGroup* g);
 // Smallest M that takes the tensor-memory kernel (runtime knob; see
 // cudalm_b200_set_tensor_path_min_rows).
 std::atomic<int> g_tc_min_rows{16};
@@ -379,6 +383,7 @@ int run_linear_any(const cudalm_b200_linear& l, cudaStream_t stream) { return ru
 using namespace cb200;
 
 struct cudalm_b200_group {
+  cb200::TcGroup* tc = nullptr;  // set when the group runs on the tensor-memory kernel
   LinearDev* table_dev = nullptr;
   int2* ranges_dev = nullptr;  // per-CTA {first m-tile, projection}, grid + 1 entries
   int grid = 0;
@@ -473,6 +478,31 @@ int cudalm_b200_group_create(const cudalm_b200_linear* linears, int count,
                              cudalm_b200_group** group_out) {
   if (!linears || !group_out) return CUDALM_B200_ERR_NULL;
   if (count < 1) return CUDALM_B200_ERR_BAD_SHAPE;
+  {
+    // batched groups go to the tensor-memory kernel when every projection fits it
+    int m_all = 0;
+    long long tc_bytes = 0;
+    for (int i = 0; i < count; ++i) {
+      const cudalm_b200_linear& l = linears[i];
+      if (int rc = validate(l)) return rc;
+      m_all = l.M > m_all ? l.M : m_all;
+      tc_bytes += static_cast<long long>(l.N) * (l.K / 2) + static_cast<long long>(l.N) * (l.K / 128) * 2 +
+                  static_cast<long long>(l.M) * l.K * 2 + static_cast<long long>(l.M) * l.N * 2;
+    }
+    if (m_all >= g_tc_min_rows.load(std::memory_order_relaxed)) {
+      TcGroup* tg = nullptr;
+      const int rc = tc_group_create(linears, count, &tg);
+      if (rc == CUDALM_B200_OK) {
+        cudalm_b200_group* g = new cudalm_b200_group();
+        g->tc = tg;
+        g->count = count;
+        g->bytes = tc_bytes;
+        *group_out = g;
+        return CUDALM_B200_OK;
+      }
+      if (rc != CUDALM_B200_ERR_UNSUPPORTED) return rc;
+    }
+  }
   std::vector<LinearDev> tbl(static_cast<size_t>(count));
   int mt = 0, kmax = 0, mmax = 0;
   long long bytes = 0, cost = 0;
@@ -540,6 +570,7 @@ int cudalm_b200_group_create(const cudalm_b200_linear* linears, int count,
 
 int cudalm_b200_group_run(const cudalm_b200_group* group, void* stream) {
   if (!group) return CUDALM_B200_ERR_NULL;
+  if (group->tc) return tc_group_run(group->tc, static_cast<cudaStream_t>(stream));
   StreamParams p;
   std::memset(&p, 0, sizeof(p));
   p.table = group->table_dev;
@@ -553,6 +584,11 @@ int cudalm_b200_group_run(const cudalm_b200_group* group, void* stream) {
 
 int cudalm_b200_group_destroy(cudalm_b200_group* group) {
   if (!group) return CUDALM_B200_OK;
+  if (group->tc) {
+    tc_group_destroy(group->tc);
+    delete group;
+    return CUDALM_B200_OK;
+  }
   cudaError_t e = cudaFree(group->table_dev);
   const cudaError_t e2 = cudaFree(group->ranges_dev);
   if (e == cudaSuccess) e = e2;

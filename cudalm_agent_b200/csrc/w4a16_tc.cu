@@ -584,17 +584,16 @@ bool tc_eligible(const cudalm_b200_linear& l) {
   return static_cast<long long>(tc_ntok(l.M)) * l.K * 2 <= kTcMaxBBytes;
 }
 
-// Up to CUDALM_B200_MAX_INLINE_LINEARS projections with the same padded row count.
-int run_tc(const cudalm_b200_linear* ls, int count, cudaStream_t stream) {
-  if (count < 1 || count > CUDALM_B200_MAX_INLINE_LINEARS) return CUDALM_B200_ERR_BAD_SHAPE;
-  TcParams p;
-  std::memset(&p, 0, sizeof(p));
+// Fills `out[count]` and the launch totals; UNSUPPORTED when a projection (or the
+// widest M with the longest K) does not fit the kernel's shared-memory budget.
+int tc_describe(const cudalm_b200_linear* ls, int count, TcDesc* out, int* items_out,
+                int* cost_out, int* kmax_out, int* ntok_out) {
   int items = 0, cost = 0, kmax = 0, ntok = 0;
   for (int i = 0; i < count; ++i) {
     const cudalm_b200_linear& l = ls[i];
     if (!tc_eligible(l)) return CUDALM_B200_ERR_UNSUPPORTED;
     ntok = tc_ntok(l.M) > ntok ? tc_ntok(l.M) : ntok;
-    TcDesc& d = p.inl[i];
+    TcDesc& d = out[i];
     if (int rc = tc_encode(l.weight, l.N, l.K, &d.tmap)) return rc;
     d.S = l.scales;
     d.x = l.x;
@@ -610,14 +609,73 @@ int run_tc(const cudalm_b200_linear* ls, int count, cudaStream_t stream) {
     kmax = l.K > kmax ? l.K : kmax;
   }
   if (static_cast<long long>(ntok) * kmax * 2 > kTcMaxBBytes) return CUDALM_B200_ERR_UNSUPPORTED;
-  p.n_desc = count;
-  p.total_items = items;
-  p.total_cost = cost;
+  *items_out = items;
+  *cost_out = cost;
+  *kmax_out = kmax;
+  *ntok_out = ntok;
+  return CUDALM_B200_OK;
+}
+
+int tc_run_params(TcParams& p, int kmax, int ntok, cudaStream_t stream) {
   p.status = device_status_word();
   if (!p.status) return CUDALM_B200_ERR_CUDA;
   if (ntok == 16) return tc_launch<16>(p, kmax, stream);
   if (ntok == 32) return tc_launch<32>(p, kmax, stream);
   return tc_launch<64>(p, kmax, stream);
+}
+
+// Up to CUDALM_B200_MAX_INLINE_LINEARS projections in one launch.
+int run_tc(const cudalm_b200_linear* ls, int count, cudaStream_t stream) {
+  if (count < 1 || count > CUDALM_B200_MAX_INLINE_LINEARS) return CUDALM_B200_ERR_BAD_SHAPE;
+  TcParams p;
+  std::memset(&p, 0, sizeof(p));
+  int kmax = 0, ntok = 0;
+  if (int rc = tc_describe(ls, count, p.inl, &p.total_items, &p.total_cost, &kmax, &ntok)) return rc;
+  p.n_desc = count;
+  return tc_run_params(p, kmax, ntok, stream);
+}
+
+// Any number of projections: the descriptor table lives on the device.
+struct TcGroup {
+  TcDesc* table_dev = nullptr;
+  int count = 0, items = 0, cost = 0, kmax = 0, ntok = 0;
+};
+
+int tc_group_create(const cudalm_b200_linear* ls, int count, TcGroup** out) {
+  std::vector<TcDesc> tbl(static_cast<size_t>(count));
+  TcGroup* g = new TcGroup();
+  g->count = count;
+  if (int rc = tc_describe(ls, count, tbl.data(), &g->items, &g->cost, &g->kmax, &g->ntok)) {
+    delete g;
+    return rc;
+  }
+  cudaError_t e = cudaMalloc(&g->table_dev, sizeof(TcDesc) * tbl.size());
+  if (e == cudaSuccess)
+    e = cudaMemcpy(g->table_dev, tbl.data(), sizeof(TcDesc) * tbl.size(), cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) {
+    g_last_cuda_error = static_cast<int>(e);
+    if (g->table_dev) cudaFree(g->table_dev);
+    delete g;
+    return CUDALM_B200_ERR_CUDA;
+  }
+  *out = g;
+  return CUDALM_B200_OK;
+}
+
+int tc_group_run(const TcGroup* g, cudaStream_t stream) {
+  TcParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.table = g->table_dev;
+  p.n_desc = g->count;
+  p.total_items = g->items;
+  p.total_cost = g->cost;
+  return tc_run_params(p, g->kmax, g->ntok, stream);
+}
+
+void tc_group_destroy(TcGroup* g) {
+  if (!g) return;
+  cudaFree(g->table_dev);
+  delete g;
 }
 
 }  // namespace cb200

@@ -427,3 +427,23 @@ def test_tensor_memory_path_is_deterministic(eng, orc):
     a = gpu_batch(eng, W, S, x)
     for _ in range(3):
         assert np.array_equal(a, gpu_batch(eng, W, S, x))
+
+
+def test_group_on_tensor_memory_path(eng, orc):
+    import torch
+    M = 32
+    shapes = [(3584, 1024), (3584, 1024), (1024, 2048), (300, 1024), (512, 256)] * 2
+    items, refs = [], []
+    for i, (N, K) in enumerate(shapes):
+        W, S = raw_weights(N, K, 400 + i)
+        x = make_x(orc, (M, K), 500 + i, "outlier")
+        lin = eng.W4A16Linear(to_dev(W), to_dev(S, torch.float16))
+        y = torch.zeros((M, N), dtype=torch.bfloat16, device="cuda")
+        items.append((lin, to_dev(x, torch.bfloat16), y))
+        refs.append(orc.batch_gemv_bf16(W, S, x, threads=8))
+    grp = eng.LinearGroup(items)
+    grp.run()
+    torch.cuda.synchronize()
+    for i, ((lin, _, y), want) in enumerate(zip(items, refs)):
+        check_close(orc, from_dev(y), want, f"tc group item {i} {lin.N}x{lin.K}")
+    grp.close()
