@@ -140,7 +140,7 @@ def device_status() -> int:
 
 def set_tensor_path_min_rows(min_rows: int) -> int:
     """Batched calls with at least this many rows take the tcgen05 kernel
-    (default 16); returns the previous value."""
+    (default 17); returns the previous value."""
     return int(load_library().cudalm_b200_set_tensor_path_min_rows(int(min_rows)))
 
 

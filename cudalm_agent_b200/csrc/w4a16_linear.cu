@@ -20,7 +20,7 @@ int tc_group_run(const TcGroup* g, cudaStream_t stream);
 void tc_group_destroy(TcGroup* g);
 // Smallest M that takes the tensor-memory kernel (runtime knob; see
 // cudalm_b200_set_tensor_path_min_rows).
-std::atomic<int> g_tc_min_rows{16};
+std::atomic<int> g_tc_min_rows{17};
 
 // ---------------------------------------------------------------------------
 // Fallback for inputs the streaming kernel does not take: a weight base that is

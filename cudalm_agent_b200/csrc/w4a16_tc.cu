@@ -42,12 +42,19 @@ namespace cb200 {
 constexpr int kTcRowsPerTile = 128;
 constexpr int kTcTiles = 2;                      // MMA tiles per item
 constexpr int kTcItemRows = kTcRowsPerTile * kTcTiles;
-constexpr int kTcStages = 2;
+constexpr int kTcMaxStages = 4;  // as many as fit beside the activations, at least 2
 constexpr int kTcStageBytes = kTcItemRows * 128;  // two groups of every row of the item
-constexpr int kTcRowWarps = 8;                    // warps 0..7: row threads (tile = warp / 4)
-constexpr int kTcProducerWarp = 8;
-constexpr int kTcMmaWarp = 9;
-constexpr int kTcThreads = 320;
+// Warp roles.  Dequantisation and read-back are separate warps so that the
+// threads that feed the tensor core never wait for its results.
+//   warps 0..7   dequantise: tile = warp >> 2, rows 32 (warp & 3) .. +31 of the tile
+//   warps 8..15  read the accumulators back and fold them in: same row mapping
+//   warp 16      TMA producer
+//   warps 17,18  MMA issuers, one per tile
+constexpr int kTcDequantWarps = 8;
+constexpr int kTcFoldWarp0 = 8;
+constexpr int kTcProducerWarp = 16;
+constexpr int kTcMmaWarp = 17;
+constexpr int kTcThreads = 608;
 constexpr int kTcMaxBBytes = 128 * 1024;          // activations resident in shared memory
 constexpr unsigned long long kTcWaitNs = 400000000ull;
 
@@ -65,6 +72,7 @@ struct alignas(64) TcDesc {
 struct TcParams {
   TcDesc inl[CUDALM_B200_MAX_INLINE_LINEARS];
   const TcDesc* table;
+  int n_stages;
   int n_desc;
   int total_items;
   int total_cost;
@@ -135,6 +143,19 @@ __device__ __forceinline__ void tmem_ld16(std::uint32_t taddr, float* f) {
   for (int i = 0; i < 16; ++i) f[i] = __uint_as_float(r[i]);
 }
 
+__device__ __forceinline__ void tmem_ld8(std::uint32_t taddr, float* f) {
+  std::uint32_t r[8];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(r[i]);
+}
+
 // Shared-memory matrix descriptor of one K=16 slice of the B operand: K-major,
 // no swizzle, core matrices of 8 rows x 16 bytes; 128 bytes between the two
 // core matrices along K (leading byte offset), 256 bytes between 8-row groups
@@ -164,7 +185,6 @@ __device__ __forceinline__ bool tc_wait(std::uint64_t* bar, std::uint32_t parity
   for (;;) {
     for (int i = 0; i < 64; ++i) {
       if (mbar_try_wait(bar, parity)) return true;
-      __nanosleep(32);
     }
     if (*abort_flag) return false;
     unsigned long long t1;
@@ -239,8 +259,8 @@ __device__ __forceinline__ void dequant_word_exact(std::uint32_t w, std::uint32_
 
 // Shared-memory map of the kernel.
 struct TcSmem {
-  std::uint64_t full[kTcStages];
-  std::uint64_t empty[kTcStages];
+  std::uint64_t full[kTcMaxStages];
+  std::uint64_t empty[kTcMaxStages];
   std::uint64_t a_full[kTcTiles][2];
   std::uint64_t a_free[kTcTiles][2];
   std::uint64_t d_full[kTcTiles][2];
@@ -261,6 +281,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
   std::uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   TcSmem* sm = reinterpret_cast<TcSmem*>(smem);
   std::uint8_t* stages = smem + kTcHeaderBytes;                       // 1024-byte aligned
+  const int kTcStages = p.n_stages;
   std::uint8_t* bsm = stages + kTcStages * kTcStageBytes;             // B operand
   volatile int* abort_flag = &sm->abort_flag;
 
@@ -273,7 +294,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
   if (tid == 0) {
     for (int s = 0; s < kTcStages; ++s) {
       mbar_init(&sm->full[s], 1);
-      mbar_init(&sm->empty[s], kTcRowWarps * 32);
+      mbar_init(&sm->empty[s], kTcDequantWarps * 32);
     }
     for (int t = 0; t < kTcTiles; ++t)
       for (int b = 0; b < 2; ++b) {
@@ -359,7 +380,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
         for (int item = i0; item < i1; ++item) sit += (G + 1) / 2;
       }
       sit = __shfl_sync(0xffffffffu, sit, 0);
-    } else if (warp == kTcMmaWarp) {
+    } else if (warp >= kTcMmaWarp) {
       // ---------------- MMA issuer ----------------
       if (lane == 0) {
         const std::uint32_t b_base = smem_u32(bsm);
@@ -368,7 +389,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
             const int buf = git & 1;
             const std::uint32_t use = git >> 1;
             bool ok = true;
-            for (int t = 0; t < kTcTiles && ok; ++t) {
+            {
+              const int t = warp - kTcMmaWarp;
               ok = tc_wait(&sm->a_full[t][buf], use & 1u, abort_flag);
               if (ok && use >= 1) ok = tc_wait(&sm->d_free[t][buf], (use - 1) & 1u, abort_flag);
               if (!ok) break;
@@ -392,42 +414,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
       }
       git = __shfl_sync(0xffffffffu, git, 0);
       for (int item = i0; item < i1; ++item) sit += (G + 1) / 2;
-    } else {
-      // ---------------- row threads: dequantise, feed A, read D back ----------------
+    } else if (warp < kTcDequantWarps) {
+      // ---------------- dequantise and feed the A operand ----------------
       const int tile = warp >> 2;
       const int lrow = (warp & 3) * 32 + lane;                      // row inside the tile
       const std::uint32_t lane_base = static_cast<std::uint32_t>((warp & 3) * 32) << 16;
       const std::uint32_t tile_base = tmem_base + tile * kColsPerTile + lane_base;
       bool alive = true;
       for (int item = i0; item < i1 && alive; ++item) {
-        const int row0 = (item - L->item_begin) * kTcItemRows + tile * kTcRowsPerTile;
-        const int row = row0 + lrow;
-        const bool row_ok = row < LN;
-        const std::uint16_t* srow = L->S + static_cast<std::size_t>(row_ok ? row : 0) * G;
-        float acc[NTOK];
-#pragma unroll
-        for (int n = 0; n < NTOK; ++n) acc[n] = 0.f;
-        float s_prev = 0.f;
-
-        auto fold_previous = [&](std::uint32_t pgit) -> bool {
-          const int pb = pgit & 1;
-          bool ok = tc_wait(&sm->d_full[tile][pb], (pgit >> 1) & 1u, abort_flag);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) return false;
-          tc_fence_after();
-          const std::uint32_t d_addr = tile_base + 128 + pb * NTOK;
-#pragma unroll
-          for (int c = 0; c < NTOK / 16; ++c) {
-            float f[16];
-            tmem_ld16(d_addr + c * 16, f);
-#pragma unroll
-            for (int i = 0; i < 16; ++i) acc[c * 16 + i] = fmaf(s_prev, f[i], acc[c * 16 + i]);
-          }
-          tc_fence_before();
-          mbar_arrive(&sm->d_free[tile][pb]);
-          return true;
-        };
-
         for (int g = 0; g < G && alive; ++g, ++git) {
           const int half = g & 1;
           const int s = sit % kTcStages;
@@ -446,7 +440,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
             dequant_word_exact(v.z, regs + 16 * q + 8);
             dequant_word_exact(v.w, regs + 16 * q + 12);
           }
-          const float s_cur = row_ok ? __half2float(__ushort_as_half(__ldg(srow + g))) : 0.f;
           if (half == 1 || g == G - 1) {
             mbar_arrive(&sm->empty[s]);  // this thread has taken its bytes out of the stage
             ++sit;
@@ -465,21 +458,47 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
           asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
           tc_fence_before();
           mbar_arrive(&sm->a_full[tile][buf]);
-          if (g >= 1) alive = fold_previous(git - 1);
-          s_prev = s_cur;
         }
-        if (alive) alive = fold_previous(git - 1);
+      }
+    } else if (warp < kTcProducerWarp) {
+      // ---------------- read the accumulators back: acc += scale * sum ----------------
+      const int fw = warp - kTcFoldWarp0;
+      const int tile = fw >> 2;
+      const int lrow = (fw & 3) * 32 + lane;
+      const std::uint32_t lane_base = static_cast<std::uint32_t>((fw & 3) * 32) << 16;
+      const std::uint32_t tile_base = tmem_base + tile * kColsPerTile + lane_base;
+      bool alive = true;
+      for (int item = i0; item < i1 && alive; ++item) {
+        const int row = (item - L->item_begin) * kTcItemRows + tile * kTcRowsPerTile + lrow;
+        const bool row_ok = row < LN;
+        const std::uint16_t* srow = L->S + static_cast<std::size_t>(row_ok ? row : 0) * G;
+        float acc[NTOK];
+#pragma unroll
+        for (int n = 0; n < NTOK; ++n) acc[n] = 0.f;
+        for (int g = 0; g < G && alive; ++g, ++git) {
+          const float sc = row_ok ? __half2float(__ushort_as_half(__ldg(srow + g))) : 0.f;
+          const int buf = git & 1;
+          bool ok = tc_wait(&sm->d_full[tile][buf], (git >> 1) & 1u, abort_flag);
+          alive = __all_sync(0xffffffffu, ok);
+          if (!alive) break;
+          tc_fence_after();
+          const std::uint32_t d_addr = tile_base + 128 + buf * NTOK;
+#pragma unroll
+          for (int c = 0; c < NTOK / 16; ++c) {
+            float f[16];
+            tmem_ld16(d_addr + c * 16, f);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) acc[c * 16 + i] = fmaf(sc, f[i], acc[c * 16 + i]);
+          }
+          tc_fence_before();
+          mbar_arrive(&sm->d_free[tile][buf]);
+        }
         if (alive && row_ok) {
           std::uint16_t* y = L->y;
 #pragma unroll
           for (int n = 0; n < NTOK; ++n)
             if (n < LM) y[static_cast<std::size_t>(n) * LN + row] = float_to_bf16_bits(acc[n] * 0x1p69f);
         }
-      }
-      // keep the counters in step with the other roles even after an abort
-      if (!alive) {
-        git = 0;
-        sit = 0;
       }
     }
   }
@@ -537,9 +556,14 @@ int tc_encode(const std::uint8_t* weight, int N, int K, CUtensorMap* out) {
 int tc_ntok(int M) { return M <= 16 ? 16 : (M <= 32 ? 32 : 64); }
 
 template <int NTOK>
-int tc_launch(const TcParams& p, int kmax, cudaStream_t stream) {
+int tc_launch(const TcParams& p_in, int kmax, cudaStream_t stream) {
   auto kern = w4a16_tc_kernel<NTOK>;
-  const int smem = 1024 + kTcHeaderBytes + kTcStages * kTcStageBytes + NTOK * kmax * 2;
+  int n_stages = (kMaxSmemBytes - 1024 - kTcHeaderBytes - NTOK * kmax * 2) / kTcStageBytes;
+  if (n_stages > kTcMaxStages) n_stages = kTcMaxStages;
+  if (n_stages < 2) return CUDALM_B200_ERR_UNSUPPORTED;
+  TcParams p = p_in;
+  p.n_stages = n_stages;
+  const int smem = 1024 + kTcHeaderBytes + n_stages * kTcStageBytes + NTOK * kmax * 2;
   static std::mutex mu;
   static std::vector<int> done;
   int dev = 0;

@@ -209,7 +209,8 @@ CUDALM_B200_API int cudalm_b200_quantize_w4a16(const uint16_t* w_bf16, int N, in
 /* ---- runtime knob -------------------------------------------------------------
  * Batched calls with M >= min_rows rows take the tcgen05 / tensor-memory kernel
  * (when its shared-memory budget allows), smaller ones the streaming kernel.
- * Default 16.  Returns the previous value.  (CUDALM has no counterpart: its
+ * Default 17 (measured crossover on B200: up to 16 rows the streaming kernel with
+ * two MMA column tiles is faster).  Returns the previous value.  (CUDALM has no counterpart: its
  * batch kernel is the M = 1 kernel with blockIdx.y = b,
  * src/kernels/batch_decode.cu:95-190.) */
 CUDALM_B200_API int cudalm_b200_set_tensor_path_min_rows(int min_rows);
