@@ -249,18 +249,20 @@ def time_steps(torch, fn, steps, warmup, dist=None):
     if dist is not None:
         dist.barrier()
         torch.cuda.synchronize()
-    evs = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
-    evs[0].record()
+    # Only two events: an event recorded between two launches would stop the
+    # second kernel from starting while the first drains (the kernels use
+    # programmatic dependent launch), which is how a caller issues them.
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
     for i in range(steps):
         fn(warmup + i)
-        evs[i + 1].record()
+    ev1.record()
     torch.cuda.synchronize()
     if dist is not None:
         dist.barrier()
         torch.cuda.synchronize()
-    total_ms = evs[0].elapsed_time(evs[-1])
-    per = [evs[i].elapsed_time(evs[i + 1]) for i in range(steps)]
-    return total_ms, per
+    total_ms = ev0.elapsed_time(ev1)
+    return total_ms, [total_ms / steps] * steps
 
 
 def max_over_ranks(torch, dist, ms: float) -> float:
