@@ -530,23 +530,37 @@ int cudalm_b200_group_create(const cudalm_b200_linear* linears, int count,
   g->kmax = kmax;
   g->mmax = mmax;
   g->bytes = bytes;
-  // per-CTA ranges: equal shares of chunks, rounded up to whole m-tiles
+  // Per-CTA ranges: equal shares of work, rounded up to whole m-tiles.  Work is
+  // counted in chunks, plus kSwitchCost chunk-equivalents at the start of every
+  // projection: changing projection stalls the whole CTA (barrier, activation
+  // refill, offset sums) for about as long as its 16 warps need for 24 chunks, so
+  // a CTA whose range spans several short projections must get fewer bytes.
+  constexpr long long kSwitchCost = 24;
   g->grid = num_sms() < mt ? num_sms() : mt;
   std::vector<int2> ranges(static_cast<size_t>(g->grid) + 1);
   {
+    const long long total_ext = cost + kSwitchCost * count;
     int d = 0;
     for (int b = 0; b <= g->grid; ++b) {
-      const long long c = static_cast<long long>(b) * cost / g->grid;
-      if (c >= cost) {
+      const long long c = static_cast<long long>(b) * total_ext / g->grid;
+      if (c >= total_ext) {
         ranges[static_cast<size_t>(b)] = make_int2(mt, count);
         continue;
       }
-      while (d + 1 < count && tbl[static_cast<size_t>(d) + 1].cost_begin <= c) ++d;
+      auto ext_begin = [&](int dd) {
+        return static_cast<long long>(tbl[static_cast<size_t>(dd)].cost_begin) + kSwitchCost * dd;
+      };
+      while (d + 1 < count && ext_begin(d + 1) <= c) ++d;
       const LinearDev& L = tbl[static_cast<size_t>(d)];
       const int nch = chunks_per_mtile(L.K);
-      int first = L.mt_begin + static_cast<int>((c - L.cost_begin + nch - 1) / nch);
+      long long within = c - ext_begin(d) - kSwitchCost;
+      if (within < 0) within = 0;
+      int first = L.mt_begin + static_cast<int>((within + nch - 1) / nch);
       int dd = d;
-      if (first >= L.mt_begin + mtiles(L.N)) dd = d + 1;  // rounded up into the next projection
+      if (first >= L.mt_begin + mtiles(L.N)) {  // rounded up into the next projection
+        first = L.mt_begin + mtiles(L.N);
+        dd = d + 1;
+      }
       ranges[static_cast<size_t>(b)] = make_int2(first, dd);
     }
   }

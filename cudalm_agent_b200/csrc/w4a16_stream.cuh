@@ -26,7 +26,7 @@
 #include <cuda.h>
 
 #include "common.cuh"
-#ifdef CB200_TIMING
+#if defined(CB200_TIMING) || defined(CB200_TIMING2)
 #include <cstdio>
 #endif
 
@@ -416,6 +416,10 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
   const int depth = p.depth;
+#ifdef CB200_TIMING2
+  unsigned long long gt_start, gt_wait = 0, gt_first = 0;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt_start));
+#endif
 
   // shared memory: [barriers][activations][NWARPS rings of `depth` stages]
   std::uint64_t* bars = reinterpret_cast<std::uint64_t*>(smem) + warp * kMaxDepth;
@@ -588,6 +592,13 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
     printf("cta %3d mt [%d,%d) d_first %d K %d: chunks %d total %lld; per chunk wait %lld comp %lld issue %lld; epilogues %lld\n",
            blockIdx.x, mt_lo, mt_hi, d_first, desc_table(p)[d_first < p.n_desc ? d_first : 0].K, tm_chunks, clock64() - tm_start, tm_wait / max(tm_chunks, 1),
            tm_comp / max(tm_chunks, 1), tm_issue / max(tm_chunks, 1), tm_epi);
+#endif
+#ifdef CB200_TIMING2
+  if (tid == 0) {
+    unsigned long long gt_end;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt_end));
+    printf("CTA %d start %llu afterwait %llu end %llu\n", blockIdx.x, gt_start, gt_wait, gt_end);
+  }
 #endif
   if (dead) {
     // Give copies still in flight a bounded chance to land before the CTA's
