@@ -489,7 +489,14 @@ int cudalm_b200_group_create(const cudalm_b200_linear* linears, int count,
       tc_bytes += static_cast<long long>(l.N) * (l.K / 2) + static_cast<long long>(l.N) * (l.K / 128) * 2 +
                   static_cast<long long>(l.M) * l.K * 2 + static_cast<long long>(l.M) * l.N * 2;
     }
-    if (m_all >= g_tc_min_rows.load(std::memory_order_relaxed)) {
+    // ... and so do groups of fewer rows that do not fit the streaming kernel's
+    // shared memory (long K with 9..16 rows)
+    int k_all = 0;
+    for (int i = 0; i < count; ++i) k_all = linears[i].K > k_all ? linears[i].K : k_all;
+    Plan probe;
+    const bool stream_fits = m_all <= CUDALM_B200_MAX_GROUP_M && k_all <= kMaxStreamK &&
+                             make_plan(k_all, m_all, &probe);
+    if (m_all >= g_tc_min_rows.load(std::memory_order_relaxed) || !stream_fits) {
       TcGroup* tg = nullptr;
       const int rc = tc_group_create(linears, count, &tg);
       if (rc == CUDALM_B200_OK) {
