@@ -5,6 +5,7 @@
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <algorithm>
 #include <vector>
 
 #include "w4a16_stream.cuh"
@@ -69,7 +70,6 @@ namespace {
 #endif
 constexpr int kCG = CB200_CG;        // groups per chunk (CG * 128 values of k)
 constexpr int kRS = kCG * 64;        // stage row stride
-constexpr int kBarrierBytes = 1024;  // mbarrier area at the start of shared memory
 constexpr int kMaxStreamK = 4096;    // largest K the staged path takes
 
 inline int round_up(int v, int a) { return (v + a - 1) / a * a; }
@@ -80,12 +80,13 @@ struct Plan {
   int depth;
   int stage_bytes;
   int x_bytes;
+  int x_buffers;
   int smem_bytes;
 };
 
 // Chooses the kernel shape for the largest K and M of a launch.  Returns false
 // when even 8 rows of activations do not fit beside the rings.
-bool make_plan(int kmax, int mmax, Plan* out) {
+bool make_plan(int kmax, int mmax, Plan* out, bool several = false) {
   const int stage = kMTileRows * kRS + round_up(kmax / 4, 128);
   int nt = 1;
   while (nt * 8 < mmax && nt < 8) nt *= 2;
@@ -99,12 +100,17 @@ bool make_plan(int kmax, int mmax, Plan* out) {
   for (int nwarps : {16, 12, 8}) {
 #endif
     if (nt == 8 && nwarps != 8) continue;  // 32 accumulators per lane need the larger register budget
-    const int fixed = kBarrierBytes + x_bytes;
+    // a launch of several projections with few rows keeps two activation
+    // buffers, so that a change of projection needs no CTA-wide barrier
+    int x_buffers = (several && static_cast<long long>(mmax) * kmax <= kAsyncFillMaxValues) ? 2 : 1;
+    const int staging = kAsyncFillMaxValues * 2;  // raw activations on their way in
+    if (kMaxSmemBytes - kHeaderBytes - 2 * x_bytes - staging < 2 * nwarps * stage) x_buffers = 1;
+    const int fixed = kHeaderBytes + x_buffers * x_bytes + (x_buffers == 2 ? staging : 0);
     const int avail = kMaxSmemBytes - fixed;
     if (avail < 2 * nwarps * stage) continue;
     int depth = avail / (nwarps * stage);
     if (depth > kMaxDepth) depth = kMaxDepth;
-    *out = Plan{nt, nwarps, depth, stage, x_bytes, fixed + nwarps * depth * stage};
+    *out = Plan{nt, nwarps, depth, stage, x_bytes, x_buffers, fixed + nwarps * depth * stage};
     return true;
   }
   return false;
@@ -169,10 +175,11 @@ int launch_instance(const StreamParams& p, const Plan& pl, int grid, cudaStream_
 int launch_stream(StreamParams& p, int kmax, int mmax, cudaStream_t stream,
                   int* grid_out = nullptr, int forced_grid = 0) {
   Plan pl;
-  if (!make_plan(kmax, mmax, &pl)) return CUDALM_B200_ERR_UNSUPPORTED;
+  if (!make_plan(kmax, mmax, &pl, p.n_desc > 1)) return CUDALM_B200_ERR_UNSUPPORTED;
   p.depth = pl.depth;
   p.stage_bytes = pl.stage_bytes;
   p.x_bytes = pl.x_bytes;
+  p.x_buffers = pl.x_buffers;
   p.status = device_status_word();
   if (p.status == nullptr) return CUDALM_B200_ERR_CUDA;
   int grid = num_sms();
@@ -529,7 +536,7 @@ int cudalm_b200_group_create(const cudalm_b200_linear* linears, int count,
              static_cast<long long>(l.M) * l.K * 2 + static_cast<long long>(l.M) * l.N * 2;
   }
   Plan pl;
-  if (!make_plan(kmax, mmax, &pl)) return CUDALM_B200_ERR_UNSUPPORTED;
+  if (!make_plan(kmax, mmax, &pl, count > 1)) return CUDALM_B200_ERR_UNSUPPORTED;
   cudalm_b200_group* g = new cudalm_b200_group();
   g->count = count;
   g->total_mt = mt;
@@ -537,39 +544,68 @@ int cudalm_b200_group_create(const cudalm_b200_linear* linears, int count,
   g->kmax = kmax;
   g->mmax = mmax;
   g->bytes = bytes;
-  // Per-CTA ranges: equal shares of work, rounded up to whole m-tiles.  Work is
-  // counted in chunks, plus kSwitchCost chunk-equivalents at the start of every
-  // projection: changing projection stalls the whole CTA (barrier, activation
-  // refill, offset sums) for about as long as its 16 warps need for 24 chunks, so
-  // a CTA whose range spans several short projections must get fewer bytes.
-  constexpr long long kSwitchCost = 24;
+  // Per-CTA ranges.  Inside a CTA warp w takes the range's m-tiles w, w + NW,
+  // w + 2 NW, ... whole, so a CTA is as slow as its most loaded warp: 54 m-tiles
+  // of a long K over 8 warps cost as much as 56.  The ranges are therefore cut
+  // by that model: an m-tile weighs its quantisation groups plus what its
+  // chunks and its epilogue cost (measured: issuing a chunk's copies ~1.85
+  // groups' worth of time, an epilogue ~0.7), a change of projection a few
+  // groups more, and a range's cost is the largest per-warp sum.  The smallest
+  // bound T under which greedy ranges cover the launch with one CTA per SM is
+  // found by bisection.
+#ifndef CB200_SWITCH_WEIGHT
+#define CB200_SWITCH_WEIGHT 800
+#endif
+  constexpr long long kSwitchWeight = CB200_SWITCH_WEIGHT;  // hundredths of a group
   g->grid = num_sms() < mt ? num_sms() : mt;
   std::vector<int2> ranges(static_cast<size_t>(g->grid) + 1);
   {
-    const long long total_ext = cost + kSwitchCost * count;
-    int d = 0;
-    for (int b = 0; b <= g->grid; ++b) {
-      const long long c = static_cast<long long>(b) * total_ext / g->grid;
-      if (c >= total_ext) {
-        ranges[static_cast<size_t>(b)] = make_int2(mt, count);
-        continue;
+    const int nw = pl.nwarps;
+    std::vector<int> weight(static_cast<size_t>(count));
+    for (int i = 0; i < count; ++i)
+      weight[static_cast<size_t>(i)] = 100 * (linears[i].K >> 7) + 185 * chunks_per_mtile(linears[i].K) + 73;
+    // greedy cut under bound T; returns the number of CTAs used (grid + 1 when T is too small)
+    auto cut = [&](long long T, std::vector<int2>* out) {
+      int d = 0, pos = 0, used = 0;  // pos: next m-tile to place, d: its projection
+      std::vector<long long> load(static_cast<size_t>(nw));
+      while (pos < mt) {
+        if (used == g->grid) return g->grid + 1;
+        if (out) (*out)[static_cast<size_t>(used)] = make_int2(pos, d);
+        std::fill(load.begin(), load.end(), 0);
+        long long extra = 0;  // changes of projection, paid by every warp
+        long long worst = 0;  // most loaded warp
+        int taken = 0;
+        int dd = d;
+        while (pos < mt) {
+          while (pos >= tbl[static_cast<size_t>(dd)].mt_begin + mtiles(tbl[static_cast<size_t>(dd)].N)) ++dd;
+          const long long sw = (taken > 0 && dd != d) ? kSwitchWeight : 0;
+          long long& slot = load[static_cast<size_t>(taken % nw)];
+          const long long cand = slot + weight[static_cast<size_t>(dd)];
+          const long long worst_then = cand > worst ? cand : worst;
+          if (taken > 0 && worst_then + extra + sw > T) break;
+          worst = worst_then;
+          slot = cand;
+          extra += sw;
+          d = dd;
+          ++taken;
+          ++pos;
+        }
+        // the next range starts in the projection that holds `pos`
+        while (pos < mt && pos >= tbl[static_cast<size_t>(d)].mt_begin + mtiles(tbl[static_cast<size_t>(d)].N)) ++d;
+        ++used;
       }
-      auto ext_begin = [&](int dd) {
-        return static_cast<long long>(tbl[static_cast<size_t>(dd)].cost_begin) + kSwitchCost * dd;
-      };
-      while (d + 1 < count && ext_begin(d + 1) <= c) ++d;
-      const LinearDev& L = tbl[static_cast<size_t>(d)];
-      const int nch = chunks_per_mtile(L.K);
-      long long within = c - ext_begin(d) - kSwitchCost;
-      if (within < 0) within = 0;
-      int first = L.mt_begin + static_cast<int>((within + nch - 1) / nch);
-      int dd = d;
-      if (first >= L.mt_begin + mtiles(L.N)) {  // rounded up into the next projection
-        first = L.mt_begin + mtiles(L.N);
-        dd = d + 1;
-      }
-      ranges[static_cast<size_t>(b)] = make_int2(first, dd);
+      if (out)
+        for (int b = used; b <= g->grid; ++b) (*out)[static_cast<size_t>(b)] = make_int2(mt, count);
+      return used;
+    };
+    long long lo = 0, hi = 0;
+    for (int i = 0; i < count; ++i)
+      hi += static_cast<long long>(mtiles(linears[i].N)) * weight[static_cast<size_t>(i)] + kSwitchWeight;
+    while (lo + 1 < hi) {  // invariant: hi is feasible, lo is not
+      const long long mid = lo + (hi - lo) / 2;
+      if (cut(mid, nullptr) <= g->grid) hi = mid; else lo = mid;
     }
+    (void)cut(hi, &ranges);
   }
   cudaError_t e = cudaGetDevice(&g->device);
   if (e == cudaSuccess) e = cudaMalloc(&g->table_dev, sizeof(LinearDev) * tbl.size());

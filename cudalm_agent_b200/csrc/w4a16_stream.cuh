@@ -9,8 +9,15 @@
 // copy of the m-tile's scales, both completing on the stage's mbarrier.  The
 // warp refills a stage as soon as it has consumed it.  Issuing a TMA copy costs
 // the issuing warp tens of cycles, which is why a stage is one box and not one
-// copy per row.  Nothing but the activation vector is shared between warps, so
-// the only CTA-wide synchronisation is at a change of projection.
+// copy per row.
+//
+// Inside a CTA's range of m-tiles warp w takes m-tiles w, w + NWARPS, ...  The
+// activation vector is the only thing the warps share.  When two activation
+// buffers fit (few rows), a change of projection needs no CTA-wide barrier:
+// the next projection's activations are copied into a staging area while the
+// warps still work from the current buffer, and each warp converts its share
+// into the free buffer when it next looks.  Otherwise the CTA synchronises at
+// the change and refills the single buffer together.
 //
 // Stage layout: 16 row segments of CG*64 bytes, then the m-tile's scale block
 // fp16 [16][K/128].
@@ -26,14 +33,18 @@
 #include <cuda.h>
 
 #include "common.cuh"
-#if defined(CB200_TIMING) || defined(CB200_TIMING2)
-#include <cstdio>
-#endif
 
 namespace cb200 {
 
 constexpr int kMTileRows = 16;
 constexpr int kMaxDepth = 4;
+constexpr int kMaxWarps = 16;
+// shared-memory header: mbarriers [kMaxWarps][kMaxDepth], then CtaControl
+constexpr int kHeaderBytes = 1152;
+// projections of a CTA's range whose descriptors are kept in shared memory
+constexpr int kDescCache = 8;
+// largest M*K one warp refills on its own (the barrier-free change of projection)
+constexpr int kAsyncFillMaxValues = 8192;
 
 enum : int { kFlagScalesBulk = 1 };
 
@@ -57,7 +68,8 @@ struct StreamParams {
   int total_cost;   // chunks in the whole launch
   int depth;        // stages per warp ring, 2..kMaxDepth
   int stage_bytes;  // 16 * CG*64 + scale block of the largest K
-  int x_bytes;      // activation region
+  int x_bytes;      // one activation buffer
+  int x_buffers;    // 1, or 2 for the barrier-free change of projection
   int* status;      // device status word
   float* cta_max;   // [gridDim.x][M] when the kernel is built with CTA_MAX
   // Optional, for launches with a device table: per CTA {first m-tile, its
@@ -102,7 +114,52 @@ __device__ __forceinline__ int mtile_at_cost(const StreamParams& p, long long co
   return tbl[lo].mt_begin + (within + nch - 1) / nch;
 }
 
-// Position of a warp in its own list of (m-tile, chunk) items.
+// Per-CTA bookkeeping in shared memory.
+// What the kernel needs of a projection, without the tensor map itself.
+struct DescLite {
+  const CUtensorMap* tmap;
+  const std::uint16_t* S;
+  const std::uint16_t* x;
+  std::uint16_t* y;
+  int N, K, M, mt_begin, flags, pad;
+};
+
+struct CtaControl {
+  unsigned long long xbar;  // mbarrier of the activation staging copy
+  int pad;
+  int fill_claim;           // first projection whose activation refill nobody has taken
+  int fill_done;            // every projection before this one has its activations in place
+  int fill_parts;           // warps that have converted their share of the refill under way
+  int cur_desc[kMaxWarps];  // projection each warp is consuming (INT_MAX when done)
+  // The CTA's first projections.  Under load a dependent load from global
+  // memory waits microseconds behind the weight stream, so nothing in the
+  // steady state reads the descriptor table there.
+  DescLite desc[kDescCache];
+};
+
+struct DescSource {
+  const StreamParams* p;
+  const DescLite* cache;
+  int d_first;
+};
+
+static_assert(kMaxWarps * kMaxDepth * 8 + sizeof(CtaControl) <= kHeaderBytes, "header too small");
+
+__device__ __forceinline__ int ld_volatile_s32(const int* p) {
+  return *reinterpret_cast<const volatile int*>(p);
+}
+__device__ __forceinline__ void st_volatile_s32(int* p, int v) {
+  *reinterpret_cast<volatile int*>(p) = v;
+}
+
+__device__ __forceinline__ DescLite get_desc(const DescSource& ds, int d) {
+  if (d - ds.d_first < kDescCache) return ds.cache[d - ds.d_first];
+  const LinearDev* L = desc_table(*ds.p) + d;
+  return DescLite{&L->tmap, L->S, L->x, L->y, L->N, L->K, L->M, L->mt_begin, L->flags, 0};
+}
+
+// Position of a warp in the launch: an m-tile, the chunk inside it and the
+// projection it belongs to.
 template <int CG>
 struct Cursor {
   int d, mt, chunk;
@@ -111,39 +168,26 @@ struct Cursor {
   const std::uint16_t* S;
   bool valid;
 
-  __device__ __forceinline__ void bind(const StreamParams& p, int dd) {
-    const LinearDev* L = desc_table(p) + dd;
+  __device__ __forceinline__ void bind(const DescSource& ds, int dd) {
+    const DescLite L = get_desc(ds, dd);
     d = dd;
-    mt_begin = L->mt_begin;
-    N = L->N;
+    mt_begin = L.mt_begin;
+    N = L.N;
     mt_end = mt_begin + desc_mtiles(N);
-    G = L->K >> 7;
-    flags = L->flags;
-    tmap = &L->tmap;
-    S = L->S;
+    G = L.K >> 7;
+    flags = L.flags;
+    tmap = L.tmap;
+    S = L.S;
     nch = (G + CG - 1) / CG;
   }
-  // d_hint: a projection at or before the one that holds mt0
-  __device__ __forceinline__ void start(const StreamParams& p, int mt0, int mt_hi, int d_hint) {
-    mt = mt0;
+  // Moves to m-tile m, which is at or after the current one; m >= mt_hi ends
+  // the walk.
+  __device__ __forceinline__ void seek(const DescSource& ds, int m, int mt_hi) {
+    mt = m;
     chunk = 0;
-    valid = mt0 < mt_hi;
-    if (valid) {
-      bind(p, d_hint);
-      while (mt >= mt_end) bind(p, d + 1);
-    }
-  }
-  // Next item of this warp: next chunk, else the warp's next m-tile (`stride`
-  // m-tiles further on), moving to a later projection when needed.
-  __device__ __forceinline__ void advance(const StreamParams& p, int stride, int mt_hi) {
-    if (++chunk < nch) return;
-    chunk = 0;
-    mt += stride;
-    if (mt >= mt_hi) {
-      valid = false;
-      return;
-    }
-    while (mt >= mt_end) bind(p, d + 1);
+    valid = m < mt_hi;
+    if (valid)
+      while (mt >= mt_end) bind(ds, d + 1);
   }
 };
 
@@ -178,7 +222,9 @@ __device__ __forceinline__ void issue_item(const Cursor<CG>& c, std::uint8_t* st
       reinterpret_cast<std::uint16_t*>(sdst)[i] = __ldg(ssrc + i);
   }
   // order this warp's earlier reads of the stage before the async writes
+#ifndef CB200_NO_ISSUE_FENCE
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+#endif
   __syncwarp();
   if (lane == 0) {
     mbar_arrive_expect_tx(bar, kBoxBytes + (sbulk ? sbytes : 0u));
@@ -231,22 +277,25 @@ __device__ __forceinline__ void store_x_value(std::uint8_t* xs, int rsx, int n, 
       float_to_bf16_bits(f);
 }
 
+template <int U, bool kFromShared = false>
 __device__ __forceinline__ void fill_x_fragments(std::uint8_t* xs, const std::uint16_t* x,
                                                  int M, int K, int rsx, int tid,
                                                  int nthreads) {
   const int total = M * K;
   if ((reinterpret_cast<std::uintptr_t>(x) & 7u) == 0) {
-    // four values per 8-byte load, four loads in flight per thread
+    // four values per 8-byte load, U loads in flight per thread
     const int quads = total >> 2;
-    for (int q0 = tid; q0 < quads; q0 += 4 * nthreads) {
-      uint2 v[4];
+    for (int q0 = tid; q0 < quads; q0 += U * nthreads) {
+      uint2 v[U];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < U; ++u) {
         const int qi = q0 + u * nthreads;
-        v[u] = qi < quads ? __ldg(reinterpret_cast<const uint2*>(x) + qi) : make_uint2(0u, 0u);
+        v[u] = qi >= quads    ? make_uint2(0u, 0u)
+               : kFromShared ? reinterpret_cast<const uint2*>(x)[qi]
+                             : __ldg(reinterpret_cast<const uint2*>(x) + qi);
       }
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < U; ++u) {
         const int qi = q0 + u * nthreads;
         if (qi < quads) {
           const int idx = qi << 2;
@@ -262,7 +311,7 @@ __device__ __forceinline__ void fill_x_fragments(std::uint8_t* xs, const std::ui
   } else {
     for (int idx = tid; idx < total; idx += nthreads) {
       const int n = idx / K;
-      store_x_value(xs, rsx, n, idx - n * K, __ldg(x + idx));
+      store_x_value(xs, rsx, n, idx - n * K, kFromShared ? x[idx] : __ldg(x + idx));
     }
   }
   for (int idx = tid; idx < K / 2; idx += nthreads)
@@ -409,6 +458,144 @@ __device__ __forceinline__ void consume_chunk(const std::uint8_t* stage, const s
 // the largest bf16-rounded output the CTA produced (used by the vocabulary
 // projection to bound its top-k search): p.cta_max[blockIdx.x * M + m].
 // ---------------------------------------------------------------------------
+
+// Shared-memory address of activation buffer b.  The offset goes through an
+// opaque move so that loads from the buffer cannot be scheduled ahead of the
+// wait that precedes this call.
+__device__ __forceinline__ std::uint8_t* x_buffer(std::uint8_t* xs0, int x_bytes, int b) {
+  int off = b * x_bytes;
+  asm volatile("" : "+r"(off)::"memory");
+  return xs0 + off;
+}
+
+// Barrier-free change of projection (two activation buffers; projection e
+// lives in buffer e & 1).  Refills happen one at a time and in order:
+// fill_claim and fill_done only grow, fill_claim == fill_done + 1 while a refill
+// is under way.  Any warp may start the refill of e once e - 1 is in place and
+// every warp is past e - 2, the buffer's previous tenant: it issues one bulk
+// copy of the raw activations into the staging area.  After the copy has
+// landed every warp, whenever it next looks (once per chunk), converts its
+// share of the quantisation groups into the fragment layout and computes their
+// offset sums; the last one publishes fill_done = e + 1.  No warp waits for
+// another unless it actually needs the activations.
+__device__ __forceinline__ void try_start_fill(const DescSource& ds, CtaControl* ctl,
+                                               std::uint8_t* staging, int e, int d_first,
+                                               int nwarps, int lane) {
+  if (lane == 0 && ld_volatile_s32(&ctl->fill_claim) == e && ld_volatile_s32(&ctl->fill_done) == e) {
+    bool free_now = true;
+    if (e - 2 >= d_first)
+      for (int w = 0; w < nwarps; ++w) free_now &= ld_volatile_s32(&ctl->cur_desc[w]) > e - 2;
+    if (free_now && atomicCAS(&ctl->fill_claim, e, e + 1) == e) {
+      const DescLite L = get_desc(ds, e);
+      const std::uint32_t bytes = static_cast<std::uint32_t>(L.M) * L.K * 2u;
+      std::uint64_t* bar = reinterpret_cast<std::uint64_t*>(&ctl->xbar);
+      if ((reinterpret_cast<std::uintptr_t>(L.x) & 15u) == 0) {
+        // earlier generic reads of the staging area come before the async write
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_arrive_expect_tx(bar, bytes);
+        bulk_g2s(staging, L.x, bytes, bar);
+      } else {
+        mbar_arrive_expect_tx(bar, 0);  // keeps the barrier's phase in step; shares are loaded directly
+      }
+    }
+  }
+  __syncwarp();
+}
+
+struct XFill {
+  int part_done;  // latest projection this warp has converted its share of
+};
+
+// One look at the refill machinery.  Returns true when this warp did some work.
+template <int NT>
+__device__ __forceinline__ bool service_fill(const DescSource& ds, CtaControl* ctl,
+                                             std::uint8_t* xs0, std::uint8_t* staging, XFill& xf,
+                                             int d_own, int d_first, int d_last, int nwarps,
+                                             int warp, int lane) {
+  int dn = 0, c = 0;
+  if (lane == 0) {
+    dn = ld_volatile_s32(&ctl->fill_done);
+    c = ld_volatile_s32(&ctl->fill_claim);
+  }
+  dn = __shfl_sync(0xffffffffu, dn, 0);
+  c = __shfl_sync(0xffffffffu, c, 0);
+  const int e = dn;
+  if (c > dn) {
+    // a refill of e is under way (had it completed between the two reads, this
+    // warp's share would already be done)
+    if (xf.part_done >= e) return false;
+    std::uint64_t* bar = reinterpret_cast<std::uint64_t*>(&ctl->xbar);
+    if (!mbar_try_wait(bar, static_cast<std::uint32_t>(e - d_first - 1) & 1u)) return false;
+    const DescLite L = get_desc(ds, e);
+    const int LK = L.K, LM = L.M, G = LK >> 7;
+    const int rsx = 2 * LK + 32;
+    std::uint8_t* xb = x_buffer(xs0, ds.p->x_bytes, e & 1);
+    const bool staged = (reinterpret_cast<std::uintptr_t>(L.x) & 15u) == 0;
+    for (int g = warp; g < G; g += nwarps) {
+      for (int n = 0; n < LM; ++n) {
+        const int k = g * 128 + lane * 4;
+        if (staged) {
+          const uint2 v = *reinterpret_cast<const uint2*>(staging + (static_cast<std::size_t>(n) * LK + k) * 2);
+          store_x_value(xb, rsx, n, k, static_cast<std::uint16_t>(v.x & 0xFFFFu));
+          store_x_value(xb, rsx, n, k + 1, static_cast<std::uint16_t>(v.x >> 16));
+          store_x_value(xb, rsx, n, k + 2, static_cast<std::uint16_t>(v.y & 0xFFFFu));
+          store_x_value(xb, rsx, n, k + 3, static_cast<std::uint16_t>(v.y >> 16));
+        } else {
+          const std::uint16_t* src = L.x + static_cast<std::size_t>(n) * LK + k;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) store_x_value(xb, rsx, n, k + i, __ldg(src + i));
+        }
+      }
+      // the all-zero row's part of this group
+      *reinterpret_cast<uint2*>(xb + LM * rsx + g * 256 + lane * 8) = make_uint2(0u, 0u);
+    }
+    __syncwarp();
+    build_bias<NT>(xb, reinterpret_cast<float*>(xb + (LM + 1) * rsx), G, rsx, LM, warp, lane, nwarps);
+    __threadfence_block();
+    __syncwarp();
+    xf.part_done = e;
+    if (lane == 0 && atomicAdd(&ctl->fill_parts, 1) == nwarps - 1) {
+      st_volatile_s32(&ctl->fill_parts, 0);
+      __threadfence_block();
+      st_volatile_s32(&ctl->fill_done, e + 1);
+    }
+    return true;
+  }
+  // nothing under way: start the next refill if it is due.  While this warp
+  // itself still reads the buffer's previous tenant there is no point in
+  // looking at the other warps.
+  if (e <= d_last && d_own > e - 2) try_start_fill(ds, ctl, staging, e, d_first, nwarps, lane);
+  return false;
+}
+
+// Works on refills until every projection up to d is in place.  False when a
+// bounded wait ran out.
+template <int NT>
+__device__ __forceinline__ bool wait_x_ready(const DescSource& ds, CtaControl* ctl,
+                                             std::uint8_t* xs0, std::uint8_t* staging, XFill& xf,
+                                             int d, int d_own, int d_first, int d_last,
+                                             int nwarps, int warp, int lane) {
+  unsigned long long t0 = 0;
+  for (int spin = 0;; ++spin) {
+    int done = 0;
+    if (lane == 0) done = ld_volatile_s32(&ctl->fill_done);
+    done = __shfl_sync(0xffffffffu, done, 0);
+    if (done > d) {
+      __threadfence_block();
+      return true;
+    }
+    if (service_fill<NT>(ds, ctl, xs0, staging, xf, d_own, d_first, d_last, nwarps, warp, lane))
+      continue;
+    __nanosleep(64);
+    if ((spin & 1023) == 1023) {
+      unsigned long long t1;
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
+      if (t0 == 0) t0 = t1;
+      else if (t1 - t0 > 2000000000ull) return false;
+    }
+  }
+}
+
 template <int NT, int CG, int NWARPS, bool CTA_MAX>
 __global__ void __launch_bounds__(NWARPS * 32, 1)
 w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
@@ -416,17 +603,19 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
   const int depth = p.depth;
-#ifdef CB200_TIMING2
-  unsigned long long gt_start, gt_wait = 0, gt_first = 0;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt_start));
-#endif
+  const bool async_switch = p.x_buffers == 2;
 
-  // shared memory: [barriers][activations][NWARPS rings of `depth` stages]
+  // shared memory: [barriers, control][activation buffers][NWARPS rings of `depth` stages]
   std::uint64_t* bars = reinterpret_cast<std::uint64_t*>(smem) + warp * kMaxDepth;
-  std::uint8_t* xs = smem + 1024;
-  std::uint8_t* ring = xs + p.x_bytes + static_cast<std::size_t>(warp) * depth * p.stage_bytes;
+  CtaControl* ctl = reinterpret_cast<CtaControl*>(smem + kMaxWarps * kMaxDepth * 8);
+  std::uint8_t* xs0 = smem + kHeaderBytes;
+  // the staging area of the barrier-free change of projection follows the two buffers
+  std::uint8_t* staging = xs0 + 2 * static_cast<std::size_t>(p.x_bytes);
+  std::uint8_t* ring = xs0 + static_cast<std::size_t>(p.x_buffers) * p.x_bytes +
+                       (async_switch ? kAsyncFillMaxValues * 2 : 0) +
+                       static_cast<std::size_t>(warp) * depth * p.stage_bytes;
 
-  // this CTA's contiguous range of m-tiles: an equal share of the launch's chunks
+  // this CTA's contiguous range of m-tiles: an equal share of the launch's work
   int mt_lo, mt_hi, d_first;
   if (p.cta_ranges) {
     const int2 r0 = p.cta_ranges[blockIdx.x], r1 = p.cta_ranges[blockIdx.x + 1];
@@ -444,65 +633,116 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
     for (int s = 0; s < depth; ++s) mbar_init(&bars[s], 1);
     mbar_init_fence();
   }
-  __syncwarp();
+  if (tid == 0) {
+    ctl->fill_claim = ctl->fill_done = d_first;
+    ctl->fill_parts = 0;
+    mbar_init(reinterpret_cast<std::uint64_t*>(&ctl->xbar), 1);
+    mbar_init_fence();
+  }
+  if (tid < NWARPS) ctl->cur_desc[tid] = d_first;
+  if (tid < kDescCache) {
+    // descriptors are written when a launch is set up, never by a kernel, so
+    // they may be read before the wait on the previous grid
+    const int d = d_first + tid;
+    DescLite v{nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0x7fffffff, 0, 0};
+    if (d < p.n_desc) {
+      const LinearDev* L = desc_table(p) + d;
+      v = DescLite{&L->tmap, L->S, L->x, L->y, L->N, L->K, L->M, L->mt_begin, L->flags, 0};
+    }
+    ctl->desc[tid] = v;
+  }
+  __syncthreads();
+  const DescSource ds{&p, ctl->desc, d_first};
 
   const std::uint64_t policy = policy_evict_first();
-#ifdef CB200_TIMING
-  const long long tm_start = clock64();
-#endif
 
-  // Two cursors over this warp's items: `fc` runs ahead issuing copies, `cc`
-  // consumes.  The warp takes m-tiles mt_lo + warp, + NWARPS, ...
+  // Two cursors over this warp's m-tiles (mt_lo + warp, + NWARPS, ...): `fc`
+  // runs ahead issuing copies, `cc` consumes.  (Handing m-tiles out dynamically
+  // from a shared counter was measured slower: the atomic per m-tile costs more
+  // than the better balance brings.)
   Cursor<CG> fc, cc;
-  fc.start(p, mt_lo + warp, mt_hi, d_first);
+  fc.valid = false;
+  if (d_first < p.n_desc) fc.bind(ds, d_first);
   cc = fc;
+  int fc_taken = 0, cc_taken = 0;
+  auto fc_next_mtile = [&]() {
+    const int m = mt_lo + warp + fc_taken * NWARPS;
+    ++fc_taken;
+    fc.seek(ds, m < mt_hi ? m : mt_hi, mt_hi);
+  };
+  auto cc_next_mtile = [&]() {
+    const int m = mt_lo + warp + cc_taken * NWARPS;
+    ++cc_taken;
+    cc.seek(ds, m < mt_hi ? m : mt_hi, mt_hi);
+  };
+  auto fc_advance = [&]() {
+    if (++fc.chunk < fc.nch) return;
+    fc_next_mtile();
+  };
+
   // Weights and scales are constants of the model: their first copies go out
   // before this grid waits for its predecessor in the stream, so they overlap
   // the predecessor's tail.  Activations and outputs are touched only after.
-  int in_flight = 0;          // stages issued and not yet consumed
-  for (int s = 0; s < depth && fc.valid; ++s) {
-    issue_item<CG>(fc, ring + s * p.stage_bytes, &bars[s], lane, policy);
-    fc.advance(p, NWARPS, mt_hi);
-    ++in_flight;
+  int in_flight = 0;  // stages issued and not yet consumed
+  if (d_first < p.n_desc) {
+    fc_next_mtile();
+    for (int s = 0; s < depth && fc.valid; ++s) {
+      issue_item<CG>(fc, ring + s * p.stage_bytes, &bars[s], lane, policy);
+      fc_advance();
+      ++in_flight;
+    }
+    cc_next_mtile();
   }
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
-#ifdef CB200_TIMING
-  long long tm_wait = 0, tm_comp = 0, tm_issue = 0, tm_epi = 0;
-  int tm_chunks = 0;
-#endif
 
-  int slot = 0;               // stage the next item arrives in
-  std::uint32_t parity = 0;   // phase of that stage's barrier
+  int slot = 0;              // stage the next item arrives in
+  std::uint32_t parity = 0;  // phase of that stage's barrier
 
   float vmax[NT][2];
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) vmax[nt][0] = vmax[nt][1] = -INFINITY;
 
-  bool dead = false;  // a wait ran out: stop computing, keep attending barriers
+  bool dead = false;     // a wait ran out: stop computing, keep attending barriers
+  XFill xf{d_first};
+  // last projection of this CTA's range
+  int d_last = d_first;
+  while (d_last + 1 < p.n_desc && get_desc(ds, d_last + 1).mt_begin < mt_hi) ++d_last;
   for (int d = d_first; d < p.n_desc; ++d) {
-    const LinearDev* L = desc_table(p) + d;
-    if (L->mt_begin >= mt_hi) break;
-    const int LN = L->N, LK = L->K, LM = L->M;
+    const DescLite L = get_desc(ds, d);
+    if (L.mt_begin >= mt_hi) break;
+    const int LN = L.N, LK = L.K, LM = L.M;
     const int rsx = 2 * LK + 32;
     const int G = LK >> 7;
-    float* bias = reinterpret_cast<float*>(xs + (LM + 1) * rsx);
-    std::uint16_t* y = L->y;
-#ifdef CB200_TIMING
-    const long long tf0 = clock64();
-#endif
-    __syncthreads();  // every warp is done with the previous activations
-    fill_x_fragments(xs, L->x, LM, LK, rsx, tid, NWARPS * 32);
-    __syncthreads();
-#ifdef CB200_TIMING
-    const long long tf1 = clock64();
-#endif
-    build_bias<NT>(xs, bias, G, rsx, LM, warp, lane, NWARPS);
-    __syncthreads();
-#ifdef CB200_TIMING
-    if (false)
-      printf("  desc %d: start->here %lld, fill %lld, bias %lld\n", d, tf0 - tm_start, tf1 - tf0, clock64() - tf1);
-#endif
+    std::uint16_t* y = L.y;
+    std::uint8_t* xs;
+    if (!async_switch || d == d_first) {
+      // the whole CTA refills the buffer together
+      __syncthreads();  // every warp is done with the previous activations
+      xs = x_buffer(xs0, p.x_bytes, async_switch ? (d & 1) : 0);
+      fill_x_fragments<4>(xs, L.x, LM, LK, rsx, tid, NWARPS * 32);
+      __syncthreads();
+      build_bias<NT>(xs, reinterpret_cast<float*>(xs + (LM + 1) * rsx), G, rsx, LM, warp, lane,
+                     NWARPS);
+      if (async_switch && tid == 0) {
+        ctl->fill_claim = d + 1;
+        ctl->fill_done = d + 1;
+      }
+      __syncthreads();
+    } else {
+      // this warp is past every earlier projection, whether it has work here or not
+      __threadfence_block();  // this warp's reads of the earlier activations come first
+      __syncwarp();
+      if (lane == 0) st_volatile_s32(&ctl->cur_desc[warp], d);
+      if (!(cc.valid && cc.d == d)) continue;
+      if (!dead &&
+          !wait_x_ready<NT>(ds, ctl, xs0, staging, xf, d, d, d_first, d_last, NWARPS, warp, lane)) {
+        dead = true;
+        if (lane == 0) atomicExch(p.status, CUDALM_B200_ERR_TIMEOUT);
+      }
+      xs = x_buffer(xs0, p.x_bytes, d & 1);
+    }
+    const float* bias = reinterpret_cast<const float*>(xs + (LM + 1) * rsx);
 
     while (cc.valid && cc.d == d) {
       float acc[NT][4];
@@ -512,45 +752,30 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
       const int nch = cc.nch;
       for (int ch = 0; ch < nch; ++ch) {
         std::uint8_t* stage = ring + slot * p.stage_bytes;
-#ifdef CB200_TIMING
-        const long long tm0 = clock64();
-#endif
         if (!dead && !wait_stage(&bars[slot], parity)) {
           dead = true;
           if (lane == 0) atomicExch(p.status, CUDALM_B200_ERR_TIMEOUT);
         }
-#ifdef CB200_TIMING
-        const long long tm1 = clock64();
-        tm_wait += tm1 - tm0;
-#endif
         if (!dead) {
           const int g0 = ch * CG;
           consume_chunk<NT, CG>(stage, xs, bias, G, g0, min(CG, G - g0), rsx, LM, lane, acc);
           __syncwarp();
-#ifdef CB200_TIMING
-          const long long tm2 = clock64();
-          tm_comp += tm2 - tm1;
-          ++tm_chunks;
-#endif
           --in_flight;
           if (fc.valid) {
             issue_item<CG>(fc, stage, &bars[slot], lane, policy);
-            fc.advance(p, NWARPS, mt_hi);
+            fc_advance();
             ++in_flight;
           }
-#ifdef CB200_TIMING
-          tm_issue += clock64() - tm2;
-#endif
+          if (async_switch) {
+            (void)service_fill<NT>(ds, ctl, xs0, staging, xf, d, d_first, d_last, NWARPS, warp, lane);
+          }
         }
         if (++slot == depth) {
           slot = 0;
           parity ^= 1u;
         }
-        cc.advance(p, NWARPS, mt_hi);
       }
-#ifdef CB200_TIMING
-      const long long te0 = clock64();
-#endif
+      cc_next_mtile();
       if (!dead) {
         const int r8 = lane >> 2, t = lane & 3;
         const int row_lo = row0 + r8, row_hi = row_lo + 8;
@@ -581,25 +806,19 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
           }
         }
       }
-#ifdef CB200_TIMING
-      tm_epi += clock64() - te0;
-#endif
     }
   }
-
-#ifdef CB200_TIMING  // measurement aid: where one warp's cycles went
-  if (lane == 0 && (blockIdx.x % 6 == 3) && warp == 0)
-    printf("cta %3d mt [%d,%d) d_first %d K %d: chunks %d total %lld; per chunk wait %lld comp %lld issue %lld; epilogues %lld\n",
-           blockIdx.x, mt_lo, mt_hi, d_first, desc_table(p)[d_first < p.n_desc ? d_first : 0].K, tm_chunks, clock64() - tm_start, tm_wait / max(tm_chunks, 1),
-           tm_comp / max(tm_chunks, 1), tm_issue / max(tm_chunks, 1), tm_epi);
-#endif
-#ifdef CB200_TIMING2
-  if (tid == 0) {
-    unsigned long long gt_end;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt_end));
-    printf("CTA %d start %llu afterwait %llu end %llu\n", blockIdx.x, gt_start, gt_wait, gt_end);
+  // done: this warp holds neither activation buffer any more
+  __threadfence_block();
+  __syncwarp();
+  if (lane == 0) st_volatile_s32(&ctl->cur_desc[warp], 0x7fffffff);
+  // the other warps may still need this warp's share of later refills
+  if (async_switch && d_first < p.n_desc && !dead &&
+      !wait_x_ready<NT>(ds, ctl, xs0, staging, xf, d_last, 0x7fffffff, d_first, d_last, NWARPS, warp,
+                        lane)) {
+    dead = true;
+    if (lane == 0) atomicExch(p.status, CUDALM_B200_ERR_TIMEOUT);
   }
-#endif
   if (dead) {
     // Give copies still in flight a bounded chance to land before the CTA's
     // shared memory is released.
@@ -627,7 +846,7 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
       }
     }
     __syncthreads();  // the activation region is free again; reuse it as scratch
-    float* red = reinterpret_cast<float*>(xs);  // [NWARPS][NT*8]
+    float* red = reinterpret_cast<float*>(xs0);  // [NWARPS][NT*8]
     if (lane < 4) {
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
