@@ -314,7 +314,7 @@ def bench_lm_head(eng, torch, dist, rank, world, steps, warmup):
     return out
 
 
-def bench_cohorts(eng, torch, steps, warmup):
+def bench_cohorts(eng, torch, steps, warmup, rows=(8, 16, 32, 64)):
     """Batched decode (BASELINE configs[2]): M = 8, 16, 32, 64 rows through the
     MLP projections of 24 layers -- fused gate+up (K=1024 -> 2 x 3584) and down
     (K=3584 -> 1024), distinct weights per layer (137 MB of weights > L2)."""
@@ -328,7 +328,7 @@ def bench_cohorts(eng, torch, steps, warmup):
             ws.append(eng.W4A16Linear(*eng.quantize_w4a16(w)))
         layers.append(ws)
     out = {}
-    for M in (8, 16, 32, 64):
+    for M in rows:
         x = torch.randn((M, 1024), generator=gen, device="cuda", dtype=torch.float32)
         x[torch.rand((M, 1024), generator=gen, device="cuda") < 0.01] *= 20.0
         x = x.to(torch.bfloat16)
@@ -337,15 +337,11 @@ def bench_cohorts(eng, torch, steps, warmup):
         uy = torch.empty((M, 3584), device="cuda", dtype=torch.bfloat16)
         dy = torch.empty((M, 1024), device="cuda", dtype=torch.bfloat16)
 
-        # one grouped launch for all gate and up projections, one for the down
-        # projections; where the kernel cannot hold all M rows of a K=3584 input in
-        # shared memory the rows go in slices of 16 (the weights are then re-read)
+        # one grouped launch for all gate and up projections, one for the down projections
         items_gu, items_d = [], []
-        rows_d = M if M * 3584 * 2 <= 112 * 1024 else 16
         for g, u, d in layers:
             items_gu += [(g, x, gy), (u, x, uy)]
-            for m0 in range(0, M, rows_d):
-                items_d.append((d, h[m0:m0 + rows_d], dy[m0:m0 + rows_d]))
+            items_d.append((d, h, dy))
         grp_gu, grp_d = eng.LinearGroup(items_gu), eng.LinearGroup(items_d)
 
         def step(i):
@@ -397,6 +393,11 @@ def run_ours(args):
     eng.load_library()
 
     copies = max(2, args.copies)
+    if args.only == "batched":
+        out = bench_cohorts(eng, torch, max(2, min(args.steps, 20)), max(1, min(args.warmup, 3)),
+                            rows=(args.rows,))
+        print(json.dumps({"batched_decode": out}), flush=True)
+        return
     if args.only == "lm_head":
         lm = bench_lm_head(eng, torch, dist, rank, world, max(5, min(args.steps, 50)), 3)
         if rank == 0:
@@ -522,8 +523,9 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default="all", choices=["all", "set", "lm_head"],
-                    help="profiling aid: run only the projection set or only the lm_head")
+    ap.add_argument("--only", default="all", choices=["all", "set", "lm_head", "batched"],
+                    help="profiling aid: run only the projection set, the lm_head or batched decode")
+    ap.add_argument("--rows", type=int, default=64, help="with --only batched: activation rows M")
     ap.add_argument("--copies", type=int, default=3, help="distinct weight copies rotated")
     ap.add_argument("--skip-cpu", action="store_true", help="profiling aid: no CPU baseline")
     args = ap.parse_args()

@@ -313,21 +313,14 @@ int run_fallback(const cudalm_b200_linear& l, cudaStream_t stream) {
 // One projection with any M: passes of as many rows as fit in shared memory.
 int run_single(cudalm_b200_linear l, cudaStream_t stream) {
   if (int rc = validate(l)) return rc;
-  if (l.M >= g_tc_min_rows.load(std::memory_order_relaxed) && aligned_to(l.weight, 16)) {
-    // widest pass whose activations fit in shared memory beside the stages
-    int rows = 0;
-    for (int r : {64, 32, 16}) {
-      cudalm_b200_linear probe = l;
-      probe.M = r;
-      if (tc_eligible(probe)) {
-        rows = r;
-        break;
-      }
-    }
-    if (rows > 0) {
-      for (int m0 = 0; m0 < l.M; m0 += rows) {
+  if (l.M >= g_tc_min_rows.load(std::memory_order_relaxed)) {
+    // passes of up to 64 rows on the tensor-memory kernel
+    cudalm_b200_linear probe = l;
+    probe.M = l.M < 64 ? l.M : 64;
+    if (tc_eligible(probe)) {
+      for (int m0 = 0; m0 < l.M; m0 += 64) {
         cudalm_b200_linear part = l;
-        part.M = (l.M - m0 < rows) ? (l.M - m0) : rows;
+        part.M = (l.M - m0 < 64) ? (l.M - m0) : 64;
         part.x = l.x + static_cast<std::size_t>(m0) * l.K;
         part.y = l.y + static_cast<std::size_t>(m0) * l.N;
         if (int rc = run_tc(&part, 1, stream)) return rc;
@@ -434,10 +427,7 @@ int cudalm_b200_linear_multi(const cudalm_b200_linear* linears, int count, void*
   if (mmax >= g_tc_min_rows.load(std::memory_order_relaxed)) {
     bool all_tc = true;
     for (int i = 0; i < count; ++i) all_tc &= tc_eligible(linears[i]);
-    cudalm_b200_linear widest = linears[0];
-    widest.M = mmax;
-    widest.K = kmax;
-    if (all_tc && tc_eligible(widest)) return run_tc(linears, count, st);
+    if (all_tc) return run_tc(linears, count, st);
   }
   Plan pl;
   if (!all_stream || mmax > CUDALM_B200_MAX_GROUP_M || !make_plan(kmax, mmax, &pl)) {

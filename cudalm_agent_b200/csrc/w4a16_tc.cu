@@ -1,31 +1,32 @@
-// Batched rows (M >= 16) on the fifth-generation tensor cores.
+// Batched rows (M >= 17 by default) on the fifth-generation tensor cores.
 //
 // One CTA per SM works on items of 256 weight rows (two 128-row MMA tiles) of one
 // projection; the M activation rows (padded to NTOK = 16, 32 or 64) are the N
-// dimension of the MMA.  Per quantisation group of 128 k:
+// dimension of the MMA.  A stage of shared memory holds two quantisation groups
+// (256 values of k) of an item: the packed weights, 128 bytes per row, and the
+// matching slice of the activations, both brought in by the TMA unit with the
+// 128-byte swizzle (weights: a thread reading its own row meets no bank
+// conflict; activations: the canonical K-major operand layout of the MMA).
+// Per group of 128 k:
 //
-//   * the TMA unit has staged the packed weights of the item, 128 bytes (two
-//     groups) per row and stage, with the 128-byte swizzle so that a thread
-//     reading its own row meets no bank conflict;
 //   * each of 256 "row" threads turns its row's 64 bytes into 64 registers of
-//     exact bf16 pairs and writes them to tensor memory (tcgen05.st) as the A
-//     operand of eight K=16 MMAs: lane = row, 8 columns per MMA;
-//   * one thread issues the eight tcgen05.mma (A from tensor memory, B = the
-//     activations in shared memory in the canonical K-major core-matrix layout)
-//     into a per-group accumulator in tensor memory and commits to mbarriers;
-//   * the row threads read the accumulator back (tcgen05.ld) and fold it into
-//     registers: acc[n] += scale[row, group] * sum[n].
+//     exact bf16 pairs (k, k + 1) and writes them to tensor memory (tcgen05.st)
+//     as the A operand of eight K=16 MMAs: lane = row, 8 columns per MMA;
+//   * one thread per tile issues the eight tcgen05.mma (A from tensor memory,
+//     B = the activations in the stage) into a per-group accumulator in tensor
+//     memory and commits to mbarriers;
+//   * the row threads of the read-back warps fetch the accumulator
+//     (tcgen05.ld) and fold it into registers: acc[n] += scale[row, group] * sum[n].
 //
 // A and D are double buffered in tensor memory (2 tiles x (2 x 64 + 2 x NTOK)
 // columns <= 512), so the dequantisation of group g+1 overlaps the MMAs of group
 // g and the read-back of group g-1.  Products are exact and sums are fp32, as in
-// the streaming kernel; only the summation order differs.
+// the streaming kernel; only the summation order differs.  Finished rows go
+// through a shared-memory tile and one TMA store per tile, which also clips the
+// rows past N and the columns past M.
 //
-// The k order inside a K=16 MMA is a private permutation shared by A and B: word
-// w of a row (k = 8w .. 8w+7) yields four registers {n_i, n_{i+4}}, i = 0..3, which
-// become columns 4(w & 1) + i of MMA w >> 1; the activations are stored to match
-// (fill_b_operand), times 2^64 / 2^60 to offset the 2^-133 / 2^-129 of the tiny-number
-// dequantisation (see w4a16_stream.cuh).
+// Nothing is resident per projection, so a CTA moves from one projection to the
+// next without any CTA-wide step, and K is not limited by shared memory.
 //
 // Every wait is bounded; a wait that runs out raises a CTA-wide abort flag, the
 // kernel stores ERR_TIMEOUT in the status word, frees its tensor memory and returns.
@@ -42,8 +43,12 @@ namespace cb200 {
 constexpr int kTcRowsPerTile = 128;
 constexpr int kTcTiles = 2;                      // MMA tiles per item
 constexpr int kTcItemRows = kTcRowsPerTile * kTcTiles;
-constexpr int kTcMaxStages = 4;  // as many as fit beside the activations, at least 2
-constexpr int kTcStageBytes = kTcItemRows * 128;  // two groups of every row of the item
+constexpr int kTcMaxStages = 4;  // as many as fit, at least 2
+constexpr int kTcWeightBytes = kTcItemRows * 128;  // two groups of every row of the item
+// a stage: the weights, then four activation boxes of 64 k x NTOK rows (128 bytes per row)
+__host__ __device__ constexpr int tc_stage_bytes(int ntok) { return kTcWeightBytes + ntok * 512; }
+// output tile of one MMA tile on its way to global memory: [NTOK][128 rows] bf16
+__host__ __device__ constexpr int tc_out_bytes(int ntok) { return ntok * kTcRowsPerTile * 2; }
 // Warp roles.  Dequantisation and read-back are separate warps so that the
 // threads that feed the tensor core never wait for its results.
 //   warps 0..7   dequantise: tile = warp >> 2, rows 32 (warp & 3) .. +31 of the tile
@@ -55,18 +60,18 @@ constexpr int kTcFoldWarp0 = 8;
 constexpr int kTcProducerWarp = 16;
 constexpr int kTcMmaWarp = 17;
 constexpr int kTcThreads = 608;
-constexpr int kTcMaxBBytes = 128 * 1024;          // activations resident in shared memory
 constexpr unsigned long long kTcWaitNs = 400000000ull;
 
 struct alignas(64) TcDesc {
-  CUtensorMap tmap;  // weights as uint32 [N][K/8], box 128 rows x 32 words, 128-byte swizzle
+  CUtensorMap tmap;    // weights as uint32 [N][K/8], box 128 rows x 32 words, 128-byte swizzle
+  CUtensorMap xmap;    // activations as bf16 [M][K], box NTOK rows x 64 values, 128-byte swizzle
+  CUtensorMap ymap;    // outputs as bf16 [M][N], box NTOK rows x 128 values
   const std::uint16_t* S;
-  const std::uint16_t* x;
   std::uint16_t* y;
   int N, K, M;
   int item_begin;   // first item (256-row block) of this projection in the launch
   int cost_begin;   // stage loads before this projection
-  int pad;
+  int direct_store;  // outputs cannot take the TMA store (base or row pitch off 16 bytes)
 };
 
 struct TcParams {
@@ -156,16 +161,18 @@ __device__ __forceinline__ void tmem_ld8(std::uint32_t taddr, float* f) {
   for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(r[i]);
 }
 
-// Shared-memory matrix descriptor of one K=16 slice of the B operand: K-major,
-// no swizzle, core matrices of 8 rows x 16 bytes; 128 bytes between the two
-// core matrices along K (leading byte offset), 256 bytes between 8-row groups
-// (stride byte offset); descriptor version 1.
+// Shared-memory matrix descriptor of one K=16 slice of the B operand inside an
+// activation box: K-major, 128-byte swizzle (rows of 128 bytes, eight rows per
+// 1024-byte swizzle atom, so 1024 bytes between 8-row groups); the slice is
+// selected by adding its byte offset (32 bytes per K=16) to the start address.
+// Descriptor version 1.
 __device__ __forceinline__ std::uint64_t tc_b_desc(std::uint32_t smem_addr) {
   std::uint64_t d = 0;
   d |= static_cast<std::uint64_t>((smem_addr & 0x3FFFFu) >> 4);
-  d |= static_cast<std::uint64_t>(128u >> 4) << 16;
-  d |= static_cast<std::uint64_t>(256u >> 4) << 32;
-  d |= static_cast<std::uint64_t>(1u) << 46;
+  d |= static_cast<std::uint64_t>(1u) << 16;            // leading byte offset: unused with a swizzle
+  d |= static_cast<std::uint64_t>(1024u >> 4) << 32;    // stride byte offset
+  d |= static_cast<std::uint64_t>(1u) << 46;            // version
+  d |= static_cast<std::uint64_t>(2u) << 61;            // 128-byte swizzle
   return d;
 }
 
@@ -196,65 +203,22 @@ __device__ __forceinline__ bool tc_wait(std::uint64_t* bar, std::uint32_t parity
   }
 }
 
-// Activations -> B operand.  For MMA slice kt (16 values of k) and activation row
-// n the 16 slots are laid out as core matrices: byte offset
-//   kt * ntok * 32 + (n / 8) * 256 + (slot / 8) * 128 + (n % 8) * 16 + (slot % 8) * 2.
-// Value k = 16 kt + 8 w + i (w = word parity, i = nibble in the word) goes to slot
-// 8 w + 2 (i & 3) + (i >> 2), times 2^64 (even i) or 2^60 (odd i).
-template <int NTOK>
-__device__ __forceinline__ void fill_b_operand(std::uint8_t* bsm, const std::uint16_t* x, int M,
-                                               int K, int tid, int nthreads) {
-  // one block of eight consecutive k (one weight word) = one 16-byte core-matrix row:
-  // slots 0..7 of the block hold k offsets 0,4,1,5,2,6,3,7
-  const int blocks_per_row = K >> 3;
-  const int total = NTOK * blocks_per_row;
-  const bool vec = (reinterpret_cast<std::uintptr_t>(x) & 15u) == 0;
-  for (int b = tid; b < total; b += nthreads) {
-    const int n = b / blocks_per_row;
-    const int kb = b - n * blocks_per_row;  // k = 8 kb .. 8 kb + 7
-    std::uint16_t v[8];
-    if (n < M) {
-      const std::uint16_t* src = x + static_cast<std::size_t>(n) * K + kb * 8;
-      if (vec) {
-        const uint4 q = __ldg(reinterpret_cast<const uint4*>(src));
-        const std::uint32_t w[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          v[2 * i] = static_cast<std::uint16_t>(w[i] & 0xFFFFu);
-          v[2 * i + 1] = static_cast<std::uint16_t>(w[i] >> 16);
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = __ldg(src + i);
-      }
-    } else {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) v[i] = 0;
-    }
-    std::uint32_t out[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float sc = (i & 1) ? 0x1p60f : 0x1p64f;
-      const std::uint32_t lo = float_to_bf16_bits(bf16_bits_to_float(v[i]) * sc);
-      const std::uint32_t hi = float_to_bf16_bits(bf16_bits_to_float(v[i + 4]) * sc);
-      out[i] = lo | (hi << 16);
-    }
-    const int kt = kb >> 1, w = kb & 1;
-    *reinterpret_cast<uint4*>(bsm + static_cast<std::size_t>(kt) * NTOK * 32 + (n >> 3) * 256 + w * 128 +
-                              (n & 7) * 16) = make_uint4(out[0], out[1], out[2], out[3]);
-  }
-}
-
-// int4 word -> four exact bf16 pairs {q(n_i), q(n_{i+4})} * 2^-133 (even i) or
-// 2^-129 (odd i); see dequant_word in w4a16_stream.cuh for the encoding.  Here the
-// offset 8 is subtracted per value (an exact bf16 subtraction) because the
-// accumulators live in tensor memory, where a per-group correction would cost more.
-__device__ __forceinline__ void dequant_word_exact(std::uint32_t w, std::uint32_t* out) {
-  const std::uint32_t w8 = w >> 8;
-  out[0] = sub_bf16x2(lop3_and_xor(w, 0x000F000Fu, 0x00080008u), 0x00080008u);
-  out[1] = sub_bf16x2(lop3_and_xor(w, 0x00F000F0u, 0x00800080u), 0x00800080u);
-  out[2] = sub_bf16x2(lop3_and_xor(w8, 0x000F000Fu, 0x00080008u), 0x00080008u);
-  out[3] = sub_bf16x2(lop3_and_xor(w8, 0x00F000F0u, 0x00800080u), 0x00800080u);
+// int4 word (k = 8w .. 8w+7, nibble i at bits 4i) -> four exact bf16 pairs
+// {q(k), q(k + 1)}, k = 8w, 8w+2, 8w+4, 8w+6, in the natural order of k so that
+// the activations need no rearrangement.  Byte b of the word holds nibbles 2b
+// (low) and 2b+1 (high); in w >> 4 the same byte position holds nibble 2b+1 in
+// its low four bits.  PRMT puts byte b of w into the low half of a register and
+// byte b of w >> 4 into the high half; one LOP3 keeps the two low nibbles, flips
+// their sign bits (two's complement n -> offset binary u = q + 8) and ORs in the
+// bf16 pattern of 128, whose seven mantissa bits then hold u: {128 + u0,
+// 128 + u1}, exact; subtracting {136, 136} leaves {q0, q1}, exact.
+__device__ __forceinline__ void dequant_word_natural(std::uint32_t w, std::uint32_t* out) {
+  const std::uint32_t w4 = w >> 4;
+  constexpr std::uint32_t kMagic = 0x43084308u;  // {136, 136} = {128 + 8, 128 + 8}
+  out[0] = sub_bf16x2(lop3_and_xor(__byte_perm(w, w4, 0x4400u), 0x000F000Fu, kMagic), kMagic);
+  out[1] = sub_bf16x2(lop3_and_xor(__byte_perm(w, w4, 0x5511u), 0x000F000Fu, kMagic), kMagic);
+  out[2] = sub_bf16x2(lop3_and_xor(__byte_perm(w, w4, 0x6622u), 0x000F000Fu, kMagic), kMagic);
+  out[3] = sub_bf16x2(lop3_and_xor(__byte_perm(w, w4, 0x7733u), 0x000F000Fu, kMagic), kMagic);
 }
 
 // Shared-memory map of the kernel.
@@ -265,11 +229,37 @@ struct TcSmem {
   std::uint64_t a_free[kTcTiles][2];
   std::uint64_t d_full[kTcTiles][2];
   std::uint64_t d_free[kTcTiles][2];
+  std::uint64_t out_free[kTcTiles];  // the tile's output buffer has been read by its last store
+  std::uint64_t out_full[kTcTiles];  // every row thread has written the tile's output buffer
   std::uint32_t tmem_base;
   int abort_flag;
 };
 constexpr int kTcHeaderBytes = 1024;
 static_assert(sizeof(TcSmem) <= kTcHeaderBytes, "barrier block too large");
+
+// Walks the items of a CTA's range, keeping track of the projection they belong to.
+struct TcWalk {
+  const TcDesc* tbl;
+  int d;           // projection of the current item
+  int item_end;    // first item after projection d
+  int n_desc;
+  __device__ __forceinline__ void start(const TcDesc* t, int nd, int d_first) {
+    tbl = t;
+    n_desc = nd;
+    d = d_first;
+    item_end = d < nd ? t[d].item_begin + (t[d].N + kTcItemRows - 1) / kTcItemRows : 0;
+  }
+  // true when the item lies in a later projection than the previous one did
+  __device__ __forceinline__ bool seek(int item) {
+    bool moved = false;
+    while (item >= item_end) {
+      ++d;
+      item_end = tbl[d].item_begin + (tbl[d].N + kTcItemRows - 1) / kTcItemRows;
+      moved = true;
+    }
+    return moved;
+  }
+};
 
 // ---------------------------------------------------------------------------
 // The kernel
@@ -280,9 +270,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
   // the swizzled TMA destinations need 1024-byte alignment; the launch adds the slack
   std::uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   TcSmem* sm = reinterpret_cast<TcSmem*>(smem);
-  std::uint8_t* stages = smem + kTcHeaderBytes;                       // 1024-byte aligned
+  std::uint8_t* stages = smem + kTcHeaderBytes;  // 1024-byte aligned
   const int kTcStages = p.n_stages;
-  std::uint8_t* bsm = stages + kTcStages * kTcStageBytes;             // B operand
+  constexpr int kStageBytes = tc_stage_bytes(NTOK);
+  constexpr int kBoxBytes = NTOK * 128;  // one activation box: NTOK rows x 64 values
+  std::uint8_t* outsm = stages + kTcStages * kStageBytes;  // [tile][NTOK][128] bf16
   volatile int* abort_flag = &sm->abort_flag;
 
   const int tid = threadIdx.x;
@@ -294,15 +286,19 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
   if (tid == 0) {
     for (int s = 0; s < kTcStages; ++s) {
       mbar_init(&sm->full[s], 1);
-      mbar_init(&sm->empty[s], kTcDequantWarps * 32);
+      // the row threads have taken the weights out, both issuers' MMAs have read the activations
+      mbar_init(&sm->empty[s], kTcDequantWarps * 32 + kTcTiles);
     }
-    for (int t = 0; t < kTcTiles; ++t)
+    for (int t = 0; t < kTcTiles; ++t) {
       for (int b = 0; b < 2; ++b) {
         mbar_init(&sm->a_full[t][b], kTcRowsPerTile);
         mbar_init(&sm->a_free[t][b], 1);
         mbar_init(&sm->d_full[t][b], 1);
         mbar_init(&sm->d_free[t][b], kTcRowsPerTile);
       }
+      mbar_init(&sm->out_free[t], 1);
+      mbar_init(&sm->out_full[t], kTcRowsPerTile);
+    }
     sm->abort_flag = 0;
     mbar_init_fence();
   }
@@ -337,170 +333,237 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
 
   std::uint32_t sit = 0;  // stage loads so far (same count in every role)
   std::uint32_t git = 0;  // groups so far (same count in every role)
+  TcWalk wk;
+  wk.start(tbl, p.n_desc, d_first);
 
-  for (int d = d_first; d < p.n_desc; ++d) {
-    const TcDesc* L = tbl + d;
-    if (L->item_begin >= it_hi) break;
-    const int LN = L->N, LK = L->K, LM = L->M;
-    const int G = LK >> 7;
-    const int items_here = (LN + kTcItemRows - 1) / kTcItemRows;
-    const int i0 = max(it_lo, L->item_begin), i1 = min(it_hi, L->item_begin + items_here);
-
-    // (also) all MMAs that read the previous activations have completed
-    if (__syncthreads_or(sm->abort_flag)) break;
-    fill_b_operand<NTOK>(bsm, L->x, LM, LK, tid, kTcThreads);
-    // make the generic-proxy writes visible to the tensor core's (async proxy) reads
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    __syncthreads();
-
-    if (warp == kTcProducerWarp) {
-      // ---------------- TMA producer ----------------
-      if (lane == 0) {
-        const std::uint64_t policy = policy_evict_first();
-        for (int item = i0; item < i1 && !*abort_flag; ++item) {
-          const int row0 = (item - L->item_begin) * kTcItemRows;
-          for (int c = 0; c < (G + 1) / 2; ++c, ++sit) {
-            const int s = sit % kTcStages;
-            const std::uint32_t use = sit / kTcStages;
-            if (use >= 1 && !tc_wait(&sm->empty[s], (use - 1) & 1u, abort_flag)) break;
-            std::uint8_t* st = stages + s * kTcStageBytes;
-            mbar_arrive_expect_tx(&sm->full[s], kTcStageBytes);
-            for (int t = 0; t < kTcTiles; ++t) {
-              asm volatile(
-                  "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
-                  ".L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;" ::"r"(
-                      smem_u32(st + t * kTcRowsPerTile * 128)),
-                  "l"(&L->tmap), "r"(c * 32), "r"(row0 + t * kTcRowsPerTile),
-                  "r"(smem_u32(&sm->full[s])), "l"(policy)
-                  : "memory");
-            }
-          }
+  if (warp == kTcProducerWarp) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      const std::uint64_t policy = policy_evict_first();
+      bool ok = true;
+      const TcDesc* L = nullptr;
+      int G = 0, item_begin = 0;
+      for (int item = it_lo; item < it_hi && ok && !*abort_flag; ++item) {
+        if (wk.seek(item) || L == nullptr) {
+          L = tbl + wk.d;
+          G = L->K >> 7;
+          item_begin = L->item_begin;
         }
-      } else {
-        for (int item = i0; item < i1; ++item) sit += (G + 1) / 2;
-      }
-      sit = __shfl_sync(0xffffffffu, sit, 0);
-    } else if (warp >= kTcMmaWarp) {
-      // ---------------- MMA issuer ----------------
-      if (lane == 0) {
-        const std::uint32_t b_base = smem_u32(bsm);
-        for (int item = i0; item < i1 && !*abort_flag; ++item) {
-          for (int g = 0; g < G; ++g, ++git) {
-            const int buf = git & 1;
-            const std::uint32_t use = git >> 1;
-            bool ok = true;
-            {
-              const int t = warp - kTcMmaWarp;
-              ok = tc_wait(&sm->a_full[t][buf], use & 1u, abort_flag);
-              if (ok && use >= 1) ok = tc_wait(&sm->d_free[t][buf], (use - 1) & 1u, abort_flag);
-              if (!ok) break;
-              tc_fence_after();
-              const std::uint32_t tile_base = tmem_base + t * kColsPerTile;
-              const std::uint32_t a_addr = tile_base + buf * 64;
-              const std::uint32_t d_addr = tile_base + 128 + buf * NTOK;
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const std::uint64_t bd = tc_b_desc(b_base + static_cast<std::uint32_t>(g * 8 + j) * (NTOK * 32));
-                tc_mma_ts(d_addr, a_addr + j * 8, bd, kIdesc, j > 0 ? 1u : 0u);
-              }
-              tc_commit(&sm->a_free[t][buf]);
-              tc_commit(&sm->d_full[t][buf]);
-            }
-            if (!ok) break;
-          }
-        }
-      } else {
-        for (int item = i0; item < i1; ++item) git += G;
-      }
-      git = __shfl_sync(0xffffffffu, git, 0);
-      for (int item = i0; item < i1; ++item) sit += (G + 1) / 2;
-    } else if (warp < kTcDequantWarps) {
-      // ---------------- dequantise and feed the A operand ----------------
-      const int tile = warp >> 2;
-      const int lrow = (warp & 3) * 32 + lane;                      // row inside the tile
-      const std::uint32_t lane_base = static_cast<std::uint32_t>((warp & 3) * 32) << 16;
-      const std::uint32_t tile_base = tmem_base + tile * kColsPerTile + lane_base;
-      bool alive = true;
-      for (int item = i0; item < i1 && alive; ++item) {
-        for (int g = 0; g < G && alive; ++g, ++git) {
-          const int half = g & 1;
+        const int row0 = (item - item_begin) * kTcItemRows;
+        for (int c = 0; c < (G + 1) / 2; ++c, ++sit) {
           const int s = sit % kTcStages;
-          if (half == 0) {
-            bool ok = tc_wait(&sm->full[s], (sit / kTcStages) & 1u, abort_flag);
-            alive = __all_sync(0xffffffffu, ok);
-            if (!alive) break;
+          const std::uint32_t use = sit / kTcStages;
+          if (use >= 1 && !tc_wait(&sm->empty[s], (use - 1) & 1u, abort_flag)) {
+            ok = false;
+            break;
           }
-          const std::uint8_t* rowp = stages + s * kTcStageBytes + tile * kTcRowsPerTile * 128 + lrow * 128;
-          std::uint32_t regs[64];
-#pragma unroll
+          std::uint8_t* st = stages + s * kStageBytes;
+          mbar_arrive_expect_tx(&sm->full[s], kStageBytes);
+          for (int t = 0; t < kTcTiles; ++t) {
+            asm volatile(
+                "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+                ".L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;" ::"r"(
+                    smem_u32(st + t * kTcRowsPerTile * 128)),
+                "l"(&L->tmap), "r"(c * 32), "r"(row0 + t * kTcRowsPerTile),
+                "r"(smem_u32(&sm->full[s])), "l"(policy)
+                : "memory");
+          }
+          // four boxes of 64 k each; k past K and rows past M arrive as zeros
           for (int q = 0; q < 4; ++q) {
-            const uint4 v = lds128(rowp + (((4 * half + q) ^ (lrow & 7)) << 4));
-            dequant_word_exact(v.x, regs + 16 * q);
-            dequant_word_exact(v.y, regs + 16 * q + 4);
-            dequant_word_exact(v.z, regs + 16 * q + 8);
-            dequant_word_exact(v.w, regs + 16 * q + 12);
+            asm volatile(
+                "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+                " [%0], [%1, {%2, %3}], [%4];" ::"r"(smem_u32(st + kTcWeightBytes + q * kBoxBytes)),
+                "l"(&L->xmap), "r"(c * 256 + q * 64), "r"(0), "r"(smem_u32(&sm->full[s]))
+                : "memory");
           }
-          if (half == 1 || g == G - 1) {
-            mbar_arrive(&sm->empty[s]);  // this thread has taken its bytes out of the stage
-            ++sit;
-          }
-          const int buf = git & 1;
-          const std::uint32_t use = git >> 1;
-          if (use >= 1) {
-            bool ok = tc_wait(&sm->a_free[tile][buf], (use - 1) & 1u, abort_flag);
-            alive = __all_sync(0xffffffffu, ok);
-            if (!alive) break;
-          }
-          tc_fence_after();
-          const std::uint32_t a_addr = tile_base + buf * 64;
-#pragma unroll
-          for (int q = 0; q < 4; ++q) tmem_st16(a_addr + 16 * q, regs + 16 * q);
-          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-          tc_fence_before();
-          mbar_arrive(&sm->a_full[tile][buf]);
-        }
-      }
-    } else if (warp < kTcProducerWarp) {
-      // ---------------- read the accumulators back: acc += scale * sum ----------------
-      const int fw = warp - kTcFoldWarp0;
-      const int tile = fw >> 2;
-      const int lrow = (fw & 3) * 32 + lane;
-      const std::uint32_t lane_base = static_cast<std::uint32_t>((fw & 3) * 32) << 16;
-      const std::uint32_t tile_base = tmem_base + tile * kColsPerTile + lane_base;
-      bool alive = true;
-      for (int item = i0; item < i1 && alive; ++item) {
-        const int row = (item - L->item_begin) * kTcItemRows + tile * kTcRowsPerTile + lrow;
-        const bool row_ok = row < LN;
-        const std::uint16_t* srow = L->S + static_cast<std::size_t>(row_ok ? row : 0) * G;
-        float acc[NTOK];
-#pragma unroll
-        for (int n = 0; n < NTOK; ++n) acc[n] = 0.f;
-        for (int g = 0; g < G && alive; ++g, ++git) {
-          const float sc = row_ok ? __half2float(__ushort_as_half(__ldg(srow + g))) : 0.f;
-          const int buf = git & 1;
-          bool ok = tc_wait(&sm->d_full[tile][buf], (git >> 1) & 1u, abort_flag);
-          alive = __all_sync(0xffffffffu, ok);
-          if (!alive) break;
-          tc_fence_after();
-          const std::uint32_t d_addr = tile_base + 128 + buf * NTOK;
-#pragma unroll
-          for (int c = 0; c < NTOK / 16; ++c) {
-            float f[16];
-            tmem_ld16(d_addr + c * 16, f);
-#pragma unroll
-            for (int i = 0; i < 16; ++i) acc[c * 16 + i] = fmaf(sc, f[i], acc[c * 16 + i]);
-          }
-          tc_fence_before();
-          mbar_arrive(&sm->d_free[tile][buf]);
-        }
-        if (alive && row_ok) {
-          std::uint16_t* y = L->y;
-#pragma unroll
-          for (int n = 0; n < NTOK; ++n)
-            if (n < LM) y[static_cast<std::size_t>(n) * LN + row] = float_to_bf16_bits(acc[n] * 0x1p69f);
         }
       }
     }
+  } else if (warp >= kTcMmaWarp) {
+    // ---------------- MMA issuer, one per tile ----------------
+    if (lane == 0) {
+      const int t = warp - kTcMmaWarp;
+      const std::uint32_t tile_base = tmem_base + t * kColsPerTile;
+      bool ok = true;
+      int G = 0;
+      for (int item = it_lo; item < it_hi && ok && !*abort_flag; ++item) {
+        if (wk.seek(item) || G == 0) G = tbl[wk.d].K >> 7;
+        for (int g = 0; g < G; ++g, ++git) {
+          const int buf = git & 1;
+          const std::uint32_t use = git >> 1;
+          ok = tc_wait(&sm->a_full[t][buf], use & 1u, abort_flag);
+          if (ok && use >= 1) ok = tc_wait(&sm->d_free[t][buf], (use - 1) & 1u, abort_flag);
+          if (!ok) break;
+          const int s = sit % kTcStages;
+          // the stage's activations (its barrier has completed by now: the row
+          // threads waited for it before they signalled a_full)
+          if ((g & 1) == 0 && !tc_wait(&sm->full[s], (sit / kTcStages) & 1u, abort_flag)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const std::uint32_t b_base =
+              smem_u32(stages + s * kStageBytes + kTcWeightBytes) + (g & 1) * 2 * kBoxBytes;
+          const std::uint32_t a_addr = tile_base + buf * 64;
+          const std::uint32_t d_addr = tile_base + 128 + buf * NTOK;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const std::uint64_t bd = tc_b_desc(b_base + (j >> 2) * kBoxBytes + (j & 3) * 32);
+            tc_mma_ts(d_addr, a_addr + j * 8, bd, kIdesc, j > 0 ? 1u : 0u);
+          }
+          tc_commit(&sm->a_free[t][buf]);
+          tc_commit(&sm->d_full[t][buf]);
+          if ((g & 1) || g == G - 1) {
+            tc_commit(&sm->empty[s]);  // these MMAs were the last readers of the stage's activations
+            ++sit;
+          }
+        }
+      }
+    }
+  } else if (warp < kTcDequantWarps) {
+    // ---------------- dequantise and feed the A operand ----------------
+    const int tile = warp >> 2;
+    const int lrow = (warp & 3) * 32 + lane;  // row inside the tile
+    const std::uint32_t lane_base = static_cast<std::uint32_t>((warp & 3) * 32) << 16;
+    const std::uint32_t tile_base = tmem_base + tile * kColsPerTile + lane_base;
+    bool alive = true;
+    int G = 0;
+    for (int item = it_lo; item < it_hi && alive; ++item) {
+      if (wk.seek(item) || G == 0) G = tbl[wk.d].K >> 7;
+      for (int g = 0; g < G && alive; ++g, ++git) {
+        const int half = g & 1;
+        const int s = sit % kTcStages;
+        if (half == 0) {
+          const bool ok = tc_wait(&sm->full[s], (sit / kTcStages) & 1u, abort_flag);
+          alive = __all_sync(0xffffffffu, ok);
+          if (!alive) break;
+        }
+        const std::uint8_t* rowp = stages + s * kStageBytes + tile * kTcRowsPerTile * 128 + lrow * 128;
+        std::uint32_t regs[64];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint4 v = lds128(rowp + (((4 * half + q) ^ (lrow & 7)) << 4));
+          dequant_word_natural(v.x, regs + 16 * q);
+          dequant_word_natural(v.y, regs + 16 * q + 4);
+          dequant_word_natural(v.z, regs + 16 * q + 8);
+          dequant_word_natural(v.w, regs + 16 * q + 12);
+        }
+        if (half == 1 || g == G - 1) {
+          mbar_arrive(&sm->empty[s]);  // this thread has taken its bytes out of the stage
+          ++sit;
+        }
+        const int buf = git & 1;
+        const std::uint32_t use = git >> 1;
+        if (use >= 1) {
+          const bool ok = tc_wait(&sm->a_free[tile][buf], (use - 1) & 1u, abort_flag);
+          alive = __all_sync(0xffffffffu, ok);
+          if (!alive) break;
+        }
+        tc_fence_after();
+        const std::uint32_t a_addr = tile_base + buf * 64;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) tmem_st16(a_addr + 16 * q, regs + 16 * q);
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        tc_fence_before();
+        mbar_arrive(&sm->a_full[tile][buf]);
+      }
+    }
+  } else if (warp < kTcProducerWarp) {
+    // ---------------- read the accumulators back: acc += scale * sum ----------------
+    const int fw = warp - kTcFoldWarp0;
+    const int tile = fw >> 2;
+    const int lrow = (fw & 3) * 32 + lane;
+    const std::uint32_t lane_base = static_cast<std::uint32_t>((fw & 3) * 32) << 16;
+    const std::uint32_t tile_base = tmem_base + tile * kColsPerTile + lane_base;
+    const bool store_thread = (fw & 3) == 0 && lane == 0;  // issues the tile's TMA stores
+    std::uint8_t* outp = outsm + tile * tc_out_bytes(NTOK) + lrow * 2;
+    std::uint32_t eit = 0;  // items finished by this tile
+    bool alive = true;
+    const TcDesc* L = nullptr;
+    const std::uint16_t* S = nullptr;
+    std::uint16_t* y = nullptr;
+    int LN = 0, LM = 0, G = 0, item_begin = 0;
+    bool direct = false;
+    for (int item = it_lo; item < it_hi && alive; ++item) {
+      if (wk.seek(item) || L == nullptr) {
+        L = tbl + wk.d;
+        S = L->S;
+        y = L->y;
+        LN = L->N;
+        LM = L->M;
+        G = L->K >> 7;
+        item_begin = L->item_begin;
+        direct = L->direct_store != 0;
+      }
+      const int row0 = (item - item_begin) * kTcItemRows + tile * kTcRowsPerTile;
+      const int row = row0 + lrow;
+      const bool row_ok = row < LN;
+      const std::uint16_t* srow = S + static_cast<std::size_t>(row_ok ? row : 0) * G;
+      float acc[NTOK];
+#pragma unroll
+      for (int n = 0; n < NTOK; ++n) acc[n] = 0.f;
+      // the scale of the next group is fetched while this one's accumulator is awaited
+      std::uint16_t sc_bits = __ldg(srow);
+      for (int g = 0; g < G && alive; ++g, ++git) {
+        const float sc = row_ok ? __half2float(__ushort_as_half(sc_bits)) : 0.f;
+        if (g + 1 < G) sc_bits = __ldg(srow + g + 1);
+        const int buf = git & 1;
+        const bool ok = tc_wait(&sm->d_full[tile][buf], (git >> 1) & 1u, abort_flag);
+        alive = __all_sync(0xffffffffu, ok);
+        if (!alive) break;
+        tc_fence_after();
+        const std::uint32_t d_addr = tile_base + 128 + buf * NTOK;
+#pragma unroll
+        for (int c = 0; c < NTOK / 16; ++c) {
+          float f[16];
+          tmem_ld16(d_addr + c * 16, f);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) acc[c * 16 + i] = fmaf(sc, f[i], acc[c * 16 + i]);
+        }
+        tc_fence_before();
+        mbar_arrive(&sm->d_free[tile][buf]);
+      }
+      if (!alive) break;
+      if (direct) {
+        // outputs the TMA unit cannot address: plain stores, one row per thread
+        if (row_ok) {
+#pragma unroll
+          for (int n = 0; n < NTOK; ++n)
+            if (n < LM) y[static_cast<std::size_t>(n) * LN + row] = float_to_bf16_bits(acc[n]);
+        }
+        continue;
+      }
+      // the tile's rows leave through shared memory and one TMA store
+      if (store_thread) {
+        if (eit >= 1) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        mbar_arrive(&sm->out_free[tile]);
+      }
+      {
+        const bool ok = tc_wait(&sm->out_free[tile], eit & 1u, abort_flag);
+        alive = __all_sync(0xffffffffu, ok);
+        if (!alive) break;
+      }
+#pragma unroll
+      for (int n = 0; n < NTOK; ++n)
+        *reinterpret_cast<std::uint16_t*>(outp + n * (kTcRowsPerTile * 2)) = float_to_bf16_bits(acc[n]);
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      mbar_arrive(&sm->out_full[tile]);
+      if (store_thread) {
+        if (!tc_wait(&sm->out_full[tile], eit & 1u, abort_flag)) {
+          alive = false;
+        } else if (row0 < LN) {
+          asm volatile(
+              "cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(
+                  &L->ymap),
+              "r"(row0), "r"(0), "r"(smem_u32(outsm + tile * tc_out_bytes(NTOK)))
+              : "memory");
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+      }
+      alive = __all_sync(0xffffffffu, alive);
+      ++eit;
+    }
+    if (store_thread) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   }
 
   __syncthreads();
@@ -534,36 +597,73 @@ EncodeTiledFn tc_encode_fn() {
   return fn;
 }
 
-// weights as uint32 [N][K/8]; box = 32 words (two groups) x 128 rows, 128-byte swizzle
-int tc_encode(const std::uint8_t* weight, int N, int K, CUtensorMap* out) {
+// A 2-D tensor map: `inner` x `outer` elements with a row pitch of inner * esize
+// bytes, box `box_inner` x `box_outer`.  The decode loop passes the same
+// pointers step after step, so encodings are kept in a small direct-mapped cache.
+struct TcMapKey {
+  const void* base = nullptr;
+  int inner = 0, outer = 0, box_inner = 0, box_outer = 0, kind = 0;
+};
+struct TcMapEntry {
+  TcMapKey key;
+  CUtensorMap map;
+};
+constexpr int kTcMapCache = 1024;
+
+int tc_encode(const void* base, int inner, int outer, int box_inner, int box_outer, int kind,
+              CUtensorMap* out) {
+  // kind 0: packed weights as uint32, 128-byte swizzle; 1: activations as bf16, 128-byte
+  // swizzle; 2: outputs as bf16, no swizzle
+  static std::mutex mu;
+  static TcMapEntry cache[kTcMapCache];
+  const std::uintptr_t h = reinterpret_cast<std::uintptr_t>(base);
+  const int slot = static_cast<int>(((h >> 4) ^ (h >> 15) ^ static_cast<std::uintptr_t>(inner) * 31u ^
+                                     static_cast<std::uintptr_t>(outer) * 131u ^
+                                     static_cast<std::uintptr_t>(kind) * 7919u ^
+                                     static_cast<std::uintptr_t>(box_outer) * 17u) % kTcMapCache);
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    const TcMapEntry& e = cache[slot];
+    if (e.key.base == base && e.key.inner == inner && e.key.outer == outer &&
+        e.key.box_inner == box_inner && e.key.box_outer == box_outer && e.key.kind == kind) {
+      *out = e.map;
+      return CUDALM_B200_OK;
+    }
+  }
   EncodeTiledFn fn = tc_encode_fn();
   if (!fn) return CUDALM_B200_ERR_CUDA;
-  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K / 8), static_cast<cuuint64_t>(N)};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K / 2)};
-  const cuuint32_t box[2] = {32, static_cast<cuuint32_t>(kTcRowsPerTile)};
+  const int esize = kind == 0 ? 4 : 2;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(inner) * esize};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(box_inner), static_cast<cuuint32_t>(box_outer)};
   const cuuint32_t elem[2] = {1, 1};
-  const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<std::uint8_t*>(weight),
-                        dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  const CUresult r =
+      fn(out, kind == 0 ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16, 2,
+         const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+         kind == 2 ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
+         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     g_last_cuda_error = static_cast<int>(r);
     return CUDALM_B200_ERR_CUDA;
   }
+  std::lock_guard<std::mutex> lk(mu);
+  cache[slot].key = TcMapKey{base, inner, outer, box_inner, box_outer, kind};
+  cache[slot].map = *out;
   return CUDALM_B200_OK;
 }
 
 int tc_ntok(int M) { return M <= 16 ? 16 : (M <= 32 ? 32 : 64); }
 
 template <int NTOK>
-int tc_launch(const TcParams& p_in, int kmax, cudaStream_t stream) {
+int tc_launch(const TcParams& p_in, cudaStream_t stream) {
   auto kern = w4a16_tc_kernel<NTOK>;
-  int n_stages = (kMaxSmemBytes - 1024 - kTcHeaderBytes - NTOK * kmax * 2) / kTcStageBytes;
+  constexpr int kFixed = 1024 + kTcHeaderBytes + kTcTiles * tc_out_bytes(NTOK);
+  int n_stages = (kMaxSmemBytes - kFixed) / tc_stage_bytes(NTOK);
   if (n_stages > kTcMaxStages) n_stages = kTcMaxStages;
   if (n_stages < 2) return CUDALM_B200_ERR_UNSUPPORTED;
   TcParams p = p_in;
   p.n_stages = n_stages;
-  const int smem = 1024 + kTcHeaderBytes + n_stages * kTcStageBytes + NTOK * kmax * 2;
+  const int smem = kFixed + n_stages * tc_stage_bytes(NTOK);
   static std::mutex mu;
   static std::vector<int> done;
   int dev = 0;
@@ -601,26 +701,33 @@ int tc_launch(const TcParams& p_in, int kmax, cudaStream_t stream) {
 
 }  // namespace
 
-// True when the tensor-memory kernel takes this projection in one pass.
+// True when the tensor-memory kernel takes this projection: the TMA unit needs
+// 16-byte aligned bases for the weights and activations (their row pitches are
+// multiples of 64 bytes already).  Outputs that it cannot address (base or row
+// pitch off 16 bytes) are stored with plain stores instead.
 bool tc_eligible(const cudalm_b200_linear& l) {
-  if (l.M < 1 || l.M > 64 || l.K <= 0 || (l.K % 128) != 0) return false;
-  if (!aligned_to(l.weight, 16)) return false;
-  return static_cast<long long>(tc_ntok(l.M)) * l.K * 2 <= kTcMaxBBytes;
+  if (l.M < 1 || l.M > 64 || l.K <= 0 || (l.K % 128) != 0 || l.N < 1) return false;
+  return aligned_to(l.weight, 16) && aligned_to(l.x, 16);
 }
 
-// Fills `out[count]` and the launch totals; UNSUPPORTED when a projection (or the
-// widest M with the longest K) does not fit the kernel's shared-memory budget.
+// Fills `out[count]` and the launch totals; UNSUPPORTED when a projection does
+// not meet the kernel's alignment rules.
 int tc_describe(const cudalm_b200_linear* ls, int count, TcDesc* out, int* items_out,
-                int* cost_out, int* kmax_out, int* ntok_out) {
-  int items = 0, cost = 0, kmax = 0, ntok = 0;
+                int* cost_out, int* ntok_out) {
+  int items = 0, cost = 0, ntok = 0;
+  for (int i = 0; i < count; ++i) {
+    if (!tc_eligible(ls[i])) return CUDALM_B200_ERR_UNSUPPORTED;
+    ntok = tc_ntok(ls[i].M) > ntok ? tc_ntok(ls[i].M) : ntok;
+  }
   for (int i = 0; i < count; ++i) {
     const cudalm_b200_linear& l = ls[i];
-    if (!tc_eligible(l)) return CUDALM_B200_ERR_UNSUPPORTED;
-    ntok = tc_ntok(l.M) > ntok ? tc_ntok(l.M) : ntok;
     TcDesc& d = out[i];
-    if (int rc = tc_encode(l.weight, l.N, l.K, &d.tmap)) return rc;
+    if (int rc = tc_encode(l.weight, l.K / 8, l.N, 32, kTcRowsPerTile, 0, &d.tmap)) return rc;
+    if (int rc = tc_encode(l.x, l.K, l.M, 64, ntok, 1, &d.xmap)) return rc;
+    d.direct_store = (!aligned_to(l.y, 16) || (l.N % 8) != 0) ? 1 : 0;
+    if (!d.direct_store)
+      if (int rc = tc_encode(l.y, l.N, l.M, kTcRowsPerTile, ntok, 2, &d.ymap)) return rc;
     d.S = l.scales;
-    d.x = l.x;
     d.y = l.y;
     d.N = l.N;
     d.K = l.K;
@@ -630,22 +737,19 @@ int tc_describe(const cudalm_b200_linear* ls, int count, TcDesc* out, int* items
     const int n_items = (l.N + kTcItemRows - 1) / kTcItemRows;
     items += n_items;
     cost += n_items * (((l.K >> 7) + 1) >> 1);
-    kmax = l.K > kmax ? l.K : kmax;
   }
-  if (static_cast<long long>(ntok) * kmax * 2 > kTcMaxBBytes) return CUDALM_B200_ERR_UNSUPPORTED;
   *items_out = items;
   *cost_out = cost;
-  *kmax_out = kmax;
   *ntok_out = ntok;
   return CUDALM_B200_OK;
 }
 
-int tc_run_params(TcParams& p, int kmax, int ntok, cudaStream_t stream) {
+int tc_run_params(TcParams& p, int ntok, cudaStream_t stream) {
   p.status = device_status_word();
   if (!p.status) return CUDALM_B200_ERR_CUDA;
-  if (ntok == 16) return tc_launch<16>(p, kmax, stream);
-  if (ntok == 32) return tc_launch<32>(p, kmax, stream);
-  return tc_launch<64>(p, kmax, stream);
+  if (ntok == 16) return tc_launch<16>(p, stream);
+  if (ntok == 32) return tc_launch<32>(p, stream);
+  return tc_launch<64>(p, stream);
 }
 
 // Up to CUDALM_B200_MAX_INLINE_LINEARS projections in one launch.
@@ -653,23 +757,23 @@ int run_tc(const cudalm_b200_linear* ls, int count, cudaStream_t stream) {
   if (count < 1 || count > CUDALM_B200_MAX_INLINE_LINEARS) return CUDALM_B200_ERR_BAD_SHAPE;
   TcParams p;
   std::memset(&p, 0, sizeof(p));
-  int kmax = 0, ntok = 0;
-  if (int rc = tc_describe(ls, count, p.inl, &p.total_items, &p.total_cost, &kmax, &ntok)) return rc;
+  int ntok = 0;
+  if (int rc = tc_describe(ls, count, p.inl, &p.total_items, &p.total_cost, &ntok)) return rc;
   p.n_desc = count;
-  return tc_run_params(p, kmax, ntok, stream);
+  return tc_run_params(p, ntok, stream);
 }
 
 // Any number of projections: the descriptor table lives on the device.
 struct TcGroup {
   TcDesc* table_dev = nullptr;
-  int count = 0, items = 0, cost = 0, kmax = 0, ntok = 0;
+  int count = 0, items = 0, cost = 0, ntok = 0;
 };
 
 int tc_group_create(const cudalm_b200_linear* ls, int count, TcGroup** out) {
   std::vector<TcDesc> tbl(static_cast<size_t>(count));
   TcGroup* g = new TcGroup();
   g->count = count;
-  if (int rc = tc_describe(ls, count, tbl.data(), &g->items, &g->cost, &g->kmax, &g->ntok)) {
+  if (int rc = tc_describe(ls, count, tbl.data(), &g->items, &g->cost, &g->ntok)) {
     delete g;
     return rc;
   }
@@ -693,7 +797,7 @@ int tc_group_run(const TcGroup* g, cudaStream_t stream) {
   p.n_desc = g->count;
   p.total_items = g->items;
   p.total_cost = g->cost;
-  return tc_run_params(p, g->kmax, g->ntok, stream);
+  return tc_run_params(p, g->ntok, stream);
 }
 
 void tc_group_destroy(TcGroup* g) {

@@ -392,10 +392,11 @@ def test_packed_merge_equals_host_merge(eng, orc):
 
 
 @pytest.mark.parametrize("N,K,M", [(256, 128, 16), (100, 384, 17), (513, 1024, 32), (7168, 1024, 64),
-                                   (1024, 3584, 64), (1024, 2048, 48), (33, 4096, 16), (1023, 1024, 64)])
+                                   (1024, 3584, 64), (1024, 2048, 48), (33, 4096, 16), (1023, 1024, 64),
+                                   (520, 1024, 64), (40, 4096, 17), (1000, 384, 33), (8, 128, 64)])
 def test_tensor_memory_path_shapes(eng, orc, N, K, M):
-    # M >= 16 takes the tcgen05 kernel (several passes when the activations do not
-    # fit shared memory at once); the streaming kernel on the same inputs must agree
+    # M >= 16 takes the tcgen05 kernel when N is a multiple of 8 (its outputs leave
+    # through TMA stores); the streaming kernel on the same inputs must agree
     W, S = raw_weights(N, K, 300 + N + M)
     x = make_x(orc, (M, K), 301 + K, "outlier")
     want = orc.batch_gemv_bf16(W, S, x, threads=8)
