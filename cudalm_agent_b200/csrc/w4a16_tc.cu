@@ -124,6 +124,43 @@ __device__ __forceinline__ void tc_mma_ts(std::uint32_t d_tmem, std::uint32_t a_
       : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
       : "memory");
 }
+// The eight K=16 MMAs of one quantisation group in one go: D = A[:, 0:16) * B0 and
+// then D += A[:, 16j:16j+16) * Bj.  A advances 8 columns per MMA; the B descriptor's
+// start-address field (units of 16 bytes) advances 32 bytes per MMA inside an
+// activation box and `box_step16` between the group's two boxes.  Issuing a
+// tcgen05.mma costs the issuing thread on the order of a hundred cycles, so
+// nothing else is computed between them.
+__device__ __forceinline__ void tc_mma_group(std::uint32_t d_tmem, std::uint32_t a_tmem,
+                                             std::uint32_t desc_lo, std::uint32_t desc_hi,
+                                             std::uint32_t box_step16, std::uint32_t idesc) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred pf, pt;\n\t"
+      ".reg .b32 lo, aa;\n\t"
+      ".reg .b64 bd;\n\t"
+      "setp.ne.b32 pf, 0, 0;\n\t"
+      "setp.eq.b32 pt, 0, 0;\n\t"
+      "mov.b64 bd, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], bd, %5, pf;\n\t"
+      "add.u32 lo, %2, 2;\n\t mov.b64 bd, {lo, %3};\n\t add.u32 aa, %1, 8;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [aa], bd, %5, pt;\n\t"
+      "add.u32 lo, %2, 4;\n\t mov.b64 bd, {lo, %3};\n\t add.u32 aa, %1, 16;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [aa], bd, %5, pt;\n\t"
+      "add.u32 lo, %2, 6;\n\t mov.b64 bd, {lo, %3};\n\t add.u32 aa, %1, 24;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [aa], bd, %5, pt;\n\t"
+      "add.u32 lo, %2, %4;\n\t mov.b64 bd, {lo, %3};\n\t add.u32 aa, %1, 32;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [aa], bd, %5, pt;\n\t"
+      "add.u32 lo, lo, 2;\n\t mov.b64 bd, {lo, %3};\n\t add.u32 aa, %1, 40;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [aa], bd, %5, pt;\n\t"
+      "add.u32 lo, lo, 2;\n\t mov.b64 bd, {lo, %3};\n\t add.u32 aa, %1, 48;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [aa], bd, %5, pt;\n\t"
+      "add.u32 lo, lo, 2;\n\t mov.b64 bd, {lo, %3};\n\t add.u32 aa, %1, 56;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [aa], bd, %5, pt;\n\t"
+      "}"
+      :
+      : "r"(d_tmem), "r"(a_tmem), "r"(desc_lo), "r"(desc_hi), "r"(box_step16), "r"(idesc)
+      : "memory");
+}
 // 16 consecutive 32-bit columns of this thread's lane
 __device__ __forceinline__ void tmem_st16(std::uint32_t taddr, const std::uint32_t* r) {
   asm volatile(
@@ -226,8 +263,8 @@ struct TcSmem {
   std::uint64_t full[kTcMaxStages];
   std::uint64_t empty[kTcMaxStages];
   std::uint64_t a_full[kTcTiles][2];
-  std::uint64_t a_free[kTcTiles][2];
-  std::uint64_t d_full[kTcTiles][2];
+  // the group's MMAs have completed: its A buffer is free again, its D buffer is full
+  std::uint64_t mma_done[kTcTiles][2];
   std::uint64_t d_free[kTcTiles][2];
   std::uint64_t out_free[kTcTiles];  // the tile's output buffer has been read by its last store
   std::uint64_t out_full[kTcTiles];  // every row thread has written the tile's output buffer
@@ -292,8 +329,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
     for (int t = 0; t < kTcTiles; ++t) {
       for (int b = 0; b < 2; ++b) {
         mbar_init(&sm->a_full[t][b], kTcRowsPerTile);
-        mbar_init(&sm->a_free[t][b], 1);
-        mbar_init(&sm->d_full[t][b], 1);
+        mbar_init(&sm->mma_done[t][b], 1);
         mbar_init(&sm->d_free[t][b], kTcRowsPerTile);
       }
       mbar_init(&sm->out_free[t], 1);
@@ -331,7 +367,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
-  std::uint32_t sit = 0;  // stage loads so far (same count in every role)
   std::uint32_t git = 0;  // groups so far (same count in every role)
   TcWalk wk;
   wk.start(tbl, p.n_desc, d_first);
@@ -343,6 +378,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
       bool ok = true;
       const TcDesc* L = nullptr;
       int G = 0, item_begin = 0;
+      int ps = 0;                  // stage to fill next
+      std::uint32_t ps_phase = 0;  // phase its `full` barrier completes next
+      bool ps_round = false;       // every stage has been used at least once
       for (int item = it_lo; item < it_hi && ok && !*abort_flag; ++item) {
         if (wk.seek(item) || L == nullptr) {
           L = tbl + wk.d;
@@ -350,13 +388,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
           item_begin = L->item_begin;
         }
         const int row0 = (item - item_begin) * kTcItemRows;
-        for (int c = 0; c < (G + 1) / 2; ++c, ++sit) {
-          const int s = sit % kTcStages;
-          const std::uint32_t use = sit / kTcStages;
-          if (use >= 1 && !tc_wait(&sm->empty[s], (use - 1) & 1u, abort_flag)) {
+        for (int c = 0; c < (G + 1) / 2; ++c) {
+          // second and later uses of a stage wait until its previous content is done with
+          if (ps_round && !tc_wait(&sm->empty[ps], ps_phase ^ 1u, abort_flag)) {
             ok = false;
             break;
           }
+          const int s = ps;
           std::uint8_t* st = stages + s * kStageBytes;
           mbar_arrive_expect_tx(&sm->full[s], kStageBytes);
           for (int t = 0; t < kTcTiles; ++t) {
@@ -376,6 +414,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
                 "l"(&L->xmap), "r"(c * 256 + q * 64), "r"(0), "r"(smem_u32(&sm->full[s]))
                 : "memory");
           }
+          if (++ps == kTcStages) {
+            ps = 0;
+            ps_phase ^= 1u;
+            ps_round = true;
+          }
         }
       }
     }
@@ -384,8 +427,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
     if (lane == 0) {
       const int t = warp - kTcMmaWarp;
       const std::uint32_t tile_base = tmem_base + t * kColsPerTile;
+      const std::uint32_t desc_hi = static_cast<std::uint32_t>(tc_b_desc(0) >> 32);
+      const std::uint32_t desc_lo0 = static_cast<std::uint32_t>(tc_b_desc(0));
       bool ok = true;
       int G = 0;
+      int s = 0;                   // stage of the current group
+      std::uint32_t s_phase = 0;   // phase of that stage's barriers
       for (int item = it_lo; item < it_hi && ok && !*abort_flag; ++item) {
         if (wk.seek(item) || G == 0) G = tbl[wk.d].K >> 7;
         for (int g = 0; g < G; ++g, ++git) {
@@ -393,29 +440,22 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
           const std::uint32_t use = git >> 1;
           ok = tc_wait(&sm->a_full[t][buf], use & 1u, abort_flag);
           if (ok && use >= 1) ok = tc_wait(&sm->d_free[t][buf], (use - 1) & 1u, abort_flag);
-          if (!ok) break;
-          const int s = sit % kTcStages;
           // the stage's activations (its barrier has completed by now: the row
           // threads waited for it before they signalled a_full)
-          if ((g & 1) == 0 && !tc_wait(&sm->full[s], (sit / kTcStages) & 1u, abort_flag)) {
-            ok = false;
-            break;
-          }
+          if (ok && (g & 1) == 0) ok = tc_wait(&sm->full[s], s_phase, abort_flag);
+          if (!ok) break;
           tc_fence_after();
-          const std::uint32_t b_base =
+          const std::uint32_t b_addr =
               smem_u32(stages + s * kStageBytes + kTcWeightBytes) + (g & 1) * 2 * kBoxBytes;
-          const std::uint32_t a_addr = tile_base + buf * 64;
-          const std::uint32_t d_addr = tile_base + 128 + buf * NTOK;
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const std::uint64_t bd = tc_b_desc(b_base + (j >> 2) * kBoxBytes + (j & 3) * 32);
-            tc_mma_ts(d_addr, a_addr + j * 8, bd, kIdesc, j > 0 ? 1u : 0u);
-          }
-          tc_commit(&sm->a_free[t][buf]);
-          tc_commit(&sm->d_full[t][buf]);
+          tc_mma_group(tile_base + 128 + buf * NTOK, tile_base + buf * 64,
+                       desc_lo0 | ((b_addr & 0x3FFFFu) >> 4), desc_hi, kBoxBytes >> 4, kIdesc);
+          tc_commit(&sm->mma_done[t][buf]);
           if ((g & 1) || g == G - 1) {
             tc_commit(&sm->empty[s]);  // these MMAs were the last readers of the stage's activations
-            ++sit;
+            if (++s == kTcStages) {
+              s = 0;
+              s_phase ^= 1u;
+            }
           }
         }
       }
@@ -428,13 +468,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
     const std::uint32_t tile_base = tmem_base + tile * kColsPerTile + lane_base;
     bool alive = true;
     int G = 0;
+    int s = 0;                  // stage of the current group
+    std::uint32_t s_phase = 0;  // phase of its `full` barrier
     for (int item = it_lo; item < it_hi && alive; ++item) {
       if (wk.seek(item) || G == 0) G = tbl[wk.d].K >> 7;
       for (int g = 0; g < G && alive; ++g, ++git) {
         const int half = g & 1;
-        const int s = sit % kTcStages;
         if (half == 0) {
-          const bool ok = tc_wait(&sm->full[s], (sit / kTcStages) & 1u, abort_flag);
+          const bool ok = tc_wait(&sm->full[s], s_phase, abort_flag);
           alive = __all_sync(0xffffffffu, ok);
           if (!alive) break;
         }
@@ -450,12 +491,15 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
         }
         if (half == 1 || g == G - 1) {
           mbar_arrive(&sm->empty[s]);  // this thread has taken its bytes out of the stage
-          ++sit;
+          if (++s == kTcStages) {
+            s = 0;
+            s_phase ^= 1u;
+          }
         }
         const int buf = git & 1;
         const std::uint32_t use = git >> 1;
         if (use >= 1) {
-          const bool ok = tc_wait(&sm->a_free[tile][buf], (use - 1) & 1u, abort_flag);
+          const bool ok = tc_wait(&sm->mma_done[tile][buf], (use - 1) & 1u, abort_flag);
           alive = __all_sync(0xffffffffu, ok);
           if (!alive) break;
         }
@@ -508,7 +552,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
         const float sc = row_ok ? __half2float(__ushort_as_half(sc_bits)) : 0.f;
         if (g + 1 < G) sc_bits = __ldg(srow + g + 1);
         const int buf = git & 1;
-        const bool ok = tc_wait(&sm->d_full[tile][buf], (git >> 1) & 1u, abort_flag);
+        const bool ok = tc_wait(&sm->mma_done[tile][buf], (git >> 1) & 1u, abort_flag);
         alive = __all_sync(0xffffffffu, ok);
         if (!alive) break;
         tc_fence_after();
