@@ -384,6 +384,8 @@ using namespace cb200;
 
 struct cudalm_b200_group {
   cb200::TcGroup* tc = nullptr;  // set when the group runs on the tensor-memory kernel
+  // set when no single launch takes the whole group: the projections run one by one
+  std::vector<cudalm_b200_linear> singles;
   LinearDev* table_dev = nullptr;
   int2* ranges_dev = nullptr;  // per-CTA {first m-tile, projection}, grid + 1 entries
   int grid = 0;
@@ -510,12 +512,15 @@ int cudalm_b200_group_create(const cudalm_b200_linear* linears, int count,
   std::vector<LinearDev> tbl(static_cast<size_t>(count));
   int mt = 0, kmax = 0, mmax = 0;
   long long bytes = 0, cost = 0;
+  bool one_by_one = false;
   for (int i = 0; i < count; ++i) {
     const cudalm_b200_linear& l = linears[i];
     if (int rc = validate(l)) return rc;
     if (l.reserved != 0) return CUDALM_B200_ERR_BAD_SHAPE;
-    if (!aligned_to(l.weight, 16)) return CUDALM_B200_ERR_MISALIGNED;
-    if (l.K > kMaxStreamK || l.M > CUDALM_B200_MAX_GROUP_M) return CUDALM_B200_ERR_UNSUPPORTED;
+    if (!aligned_to(l.weight, 16) || l.K > kMaxStreamK || l.M > CUDALM_B200_MAX_GROUP_M) {
+      one_by_one = true;
+      break;
+    }
     if (int rc = to_dev(l, mt, static_cast<int>(cost), &tbl[static_cast<size_t>(i)])) return rc;
     mt += mtiles(l.N);
     cost += static_cast<long long>(mtiles(l.N)) * chunks_per_mtile(l.K);
@@ -526,7 +531,21 @@ int cudalm_b200_group_create(const cudalm_b200_linear* linears, int count,
              static_cast<long long>(l.M) * l.K * 2 + static_cast<long long>(l.M) * l.N * 2;
   }
   Plan pl;
-  if (!make_plan(kmax, mmax, &pl, count > 1)) return CUDALM_B200_ERR_UNSUPPORTED;
+  if (!one_by_one && !make_plan(kmax, mmax, &pl, count > 1)) one_by_one = true;
+  if (one_by_one) {
+    // a projection that only the slow kernel takes, or rows that do not fit one
+    // staged launch: same results, one launch (or several passes) per projection
+    cudalm_b200_group* g = new cudalm_b200_group();
+    g->count = count;
+    g->singles.assign(linears, linears + count);
+    for (int i = 0; i < count; ++i) {
+      const cudalm_b200_linear& l = linears[i];
+      g->bytes += static_cast<long long>(l.N) * (l.K / 2) + static_cast<long long>(l.N) * (l.K / 128) * 2 +
+                  static_cast<long long>(l.M) * l.K * 2 + static_cast<long long>(l.M) * l.N * 2;
+    }
+    *group_out = g;
+    return CUDALM_B200_OK;
+  }
   cudalm_b200_group* g = new cudalm_b200_group();
   g->count = count;
   g->total_mt = mt;
@@ -618,6 +637,11 @@ int cudalm_b200_group_create(const cudalm_b200_linear* linears, int count,
 int cudalm_b200_group_run(const cudalm_b200_group* group, void* stream) {
   if (!group) return CUDALM_B200_ERR_NULL;
   if (group->tc) return tc_group_run(group->tc, static_cast<cudaStream_t>(stream));
+  if (!group->singles.empty()) {
+    for (const cudalm_b200_linear& l : group->singles)
+      if (int rc = run_linear_any(l, static_cast<cudaStream_t>(stream))) return rc;
+    return CUDALM_B200_OK;
+  }
   StreamParams p;
   std::memset(&p, 0, sizeof(p));
   p.table = group->table_dev;
@@ -633,6 +657,10 @@ int cudalm_b200_group_destroy(cudalm_b200_group* group) {
   if (!group) return CUDALM_B200_OK;
   if (group->tc) {
     tc_group_destroy(group->tc);
+    delete group;
+    return CUDALM_B200_OK;
+  }
+  if (!group->singles.empty()) {
     delete group;
     return CUDALM_B200_OK;
   }
