@@ -49,7 +49,7 @@ METRIC = "w4a16_gemv_hbm_gbps_m1_projection_set"
 UNIT = "GB/s"
 # dram__bytes_read.sum + dram__bytes_write.sum of one grouped launch, from the
 # ncu capture summarised in profiles/ (None until a capture exists)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 241_422_336  # profiles/w4a16_stream_kernel_m1_projection_set.md
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 242_899_968  # profiles/w4a16_stream_kernel_m1_projection_set.md
 
 
 def set_bytes(M: int = 1) -> int:
@@ -398,6 +398,10 @@ def run_ours(args):
                             rows=(args.rows,))
         print(json.dumps({"batched_decode": out}), flush=True)
         return
+    if args.only == "quantize":
+        print(json.dumps({"quantize": bench_quantize(eng, torch, max(2, min(args.steps, 20)),
+                                                     max(1, min(args.warmup, 3)))}), flush=True)
+        return
     if args.only == "lm_head":
         lm = bench_lm_head(eng, torch, dist, rank, world, max(5, min(args.steps, 50)), 3)
         if rank == 0:
@@ -523,8 +527,9 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default="all", choices=["all", "set", "lm_head", "batched"],
-                    help="profiling aid: run only the projection set, the lm_head or batched decode")
+    ap.add_argument("--only", default="all", choices=["all", "set", "lm_head", "batched", "quantize"],
+                    help="profiling aid: run only the projection set, the lm_head, batched decode "
+                         "or the quantizer")
     ap.add_argument("--rows", type=int, default=64, help="with --only batched: activation rows M")
     ap.add_argument("--copies", type=int, default=3, help="distinct weight copies rotated")
     ap.add_argument("--skip-cpu", action="store_true", help="profiling aid: no CPU baseline")
