@@ -78,6 +78,9 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(std::uint64_t* bar,
       "r"(tx_bytes)
       : "memory");
 }
+__device__ __forceinline__ void mbar_arrive(std::uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait(std::uint64_t* bar,
                                               std::uint32_t parity) {
   std::uint32_t ok;

@@ -76,7 +76,7 @@ inline int round_up(int v, int a) { return (v + a - 1) / a * a; }
 
 struct Plan {
   int nt;       // MMA column tiles: activations rows per pass = 8 * nt
-  int nwarps;   // 16 or 8
+  int nwarps;   // consumer warps: 12 or 8
   int depth;
   int stage_bytes;
   int x_bytes;
@@ -97,7 +97,7 @@ bool make_plan(int kmax, int mmax, Plan* out, bool several = false) {
 #ifdef CB200_WARPS
   for (int nwarps : {CB200_WARPS}) {
 #else
-  for (int nwarps : {16, 12, 8}) {
+  for (int nwarps : {12, 8}) {
 #endif
     if (nt == 8 && nwarps != 8) continue;  // 32 accumulators per lane need the larger register budget
     // a launch of several projections with few rows keeps two activation
@@ -126,9 +126,15 @@ int max_rows_per_pass(int k) {
   return best;
 }
 
+#ifndef CB200_PRODUCERS
+#define CB200_PRODUCERS 1  // producer warps for the 8-consumer form
+#endif
+
 template <int NT, int NWARPS, bool CTA_MAX>
 int launch_instance(const StreamParams& p, const Plan& pl, int grid, cudaStream_t stream) {
-  auto kern = w4a16_stream_kernel<NT, kCG, NWARPS, CTA_MAX>;
+  // producer warps need registers: only the 8-consumer form has room for them
+  constexpr int kProd = (CB200_PRODUCERS && NWARPS == 8) ? NWARPS / 4 : 0;
+  auto kern = w4a16_stream_kernel<NT, kCG, NWARPS, CTA_MAX, kProd>;
   // the attribute is per device; set it on every device this process uses
   static std::mutex mu;
   static std::vector<int> done_devices;
@@ -155,7 +161,7 @@ int launch_instance(const StreamParams& p, const Plan& pl, int grid, cudaStream_
   // (activations, outputs) before its griddepcontrol.wait.
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(grid));
-  cfg.blockDim = dim3(NWARPS * 32);
+  cfg.blockDim = dim3((NWARPS + kProd) * 32);
   cfg.dynamicSmemBytes = static_cast<size_t>(pl.smem_bytes);
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -192,7 +198,6 @@ int launch_stream(StreamParams& p, int kmax, int mmax, cudaStream_t stream,
   if (pl.nt == NT_ && pl.nwarps == NW_)                                             \
     return want_max ? launch_instance<NT_, NW_, true>(p, pl, grid, stream)          \
                     : launch_instance<NT_, NW_, false>(p, pl, grid, stream);
-  CB200_CASE(1, 16) CB200_CASE(2, 16) CB200_CASE(4, 16)
   CB200_CASE(1, 12) CB200_CASE(2, 12) CB200_CASE(4, 12)
   CB200_CASE(1, 8) CB200_CASE(2, 8) CB200_CASE(4, 8) CB200_CASE(8, 8)
 #undef CB200_CASE
@@ -689,8 +694,8 @@ int cudalm_b200_kernel_regs(const char* kernel_name) {
   const void* fn = nullptr;
 #define CB200_NAME(NT_, NW_)                                                     \
   if (std::strcmp(kernel_name, "w4a16_stream_nt" #NT_ "_w" #NW_) == 0)           \
-    fn = reinterpret_cast<const void*>(&w4a16_stream_kernel<NT_, kCG, NW_, false>);
-  CB200_NAME(1, 16) CB200_NAME(2, 16) CB200_NAME(4, 16)
+    fn = reinterpret_cast<const void*>(                                           \
+        &w4a16_stream_kernel<NT_, kCG, NW_, false, (CB200_PRODUCERS && NW_ == 8) ? 2 : 0>);
   CB200_NAME(1, 12) CB200_NAME(2, 12) CB200_NAME(4, 12)
   CB200_NAME(1, 8) CB200_NAME(2, 8) CB200_NAME(4, 8) CB200_NAME(8, 8)
 #undef CB200_NAME

@@ -39,8 +39,9 @@ namespace cb200 {
 constexpr int kMTileRows = 16;
 constexpr int kMaxDepth = 4;
 constexpr int kMaxWarps = 16;
-// shared-memory header: mbarriers [kMaxWarps][kMaxDepth], then CtaControl
-constexpr int kHeaderBytes = 1152;
+// shared-memory header: "full" mbarriers [kMaxWarps][kMaxDepth], CtaControl, and in
+// its last 512 bytes the "empty" mbarriers [kMaxWarps][kMaxDepth] of the producer form
+constexpr int kHeaderBytes = 1664;
 // projections of a CTA's range whose descriptors are kept in shared memory
 constexpr int kDescCache = 8;
 // largest M*K one warp refills on its own (the barrier-free change of projection)
@@ -130,6 +131,8 @@ struct CtaControl {
   int fill_claim;           // first projection whose activation refill nobody has taken
   int fill_done;            // every projection before this one has its activations in place
   int fill_parts;           // warps that have converted their share of the refill under way
+  int abort;                // a bounded wait ran out somewhere in the CTA
+  int issued[kMaxWarps];    // producer form: stages issued so far for each consumer warp
   int cur_desc[kMaxWarps];  // projection each warp is consuming (INT_MAX when done)
   // The CTA's first projections.  Under load a dependent load from global
   // memory waits microseconds behind the weight stream, so nothing in the
@@ -143,7 +146,7 @@ struct DescSource {
   int d_first;
 };
 
-static_assert(kMaxWarps * kMaxDepth * 8 + sizeof(CtaControl) <= kHeaderBytes, "header too small");
+static_assert(2 * kMaxWarps * kMaxDepth * 8 + sizeof(CtaControl) <= kHeaderBytes, "header too small");
 
 __device__ __forceinline__ int ld_volatile_s32(const int* p) {
   return *reinterpret_cast<const volatile int*>(p);
@@ -231,6 +234,29 @@ __device__ __forceinline__ void issue_item(const Cursor<CG>& c, std::uint8_t* st
     tma_box_2d(stage, c.tmap, c.chunk * (CG * 16), row0, bar, policy);
     if (sbulk) bulk_g2s(sdst, ssrc, sbytes, bar);
   }
+}
+
+// The same from a single thread that is not the stage's reader (producer form): the
+// reader released the stage through an mbarrier, which orders its reads before these
+// copies.  A ragged or unaligned scale block is left to the reader (stage_scales_bulk).
+template <int CG>
+__device__ __forceinline__ bool stage_scales_bulk(const Cursor<CG>& c) {
+  const int row0 = (c.mt - c.mt_begin) * kMTileRows;
+  const int rows = min(kMTileRows, c.N - row0);
+  return (c.flags & kFlagScalesBulk) && (((rows * c.G * 2) & 15) == 0);
+}
+template <int CG>
+__device__ __forceinline__ void issue_item_single(const Cursor<CG>& c, std::uint8_t* stage,
+                                                  std::uint64_t* bar, std::uint64_t policy) {
+  constexpr int RS = CG * 64;
+  constexpr std::uint32_t kBoxBytes = kMTileRows * RS;
+  const int row0 = (c.mt - c.mt_begin) * kMTileRows;
+  const int rows = min(kMTileRows, c.N - row0);
+  const std::uint32_t sbytes = static_cast<std::uint32_t>(rows * c.G) * 2u;
+  const bool sbulk = stage_scales_bulk<CG>(c);
+  mbar_arrive_expect_tx(bar, kBoxBytes + (sbulk ? sbytes : 0u));
+  tma_box_2d(stage, c.tmap, c.chunk * (CG * 16), row0, bar, policy);
+  if (sbulk) bulk_g2s(stage + kBoxBytes, c.S + static_cast<std::size_t>(row0) * c.G, sbytes, bar);
 }
 
 // Bounded wait on a stage; false when it ran out (about two seconds).
@@ -343,6 +369,26 @@ __device__ __forceinline__ void dequant_word(std::uint32_t w, std::uint32_t (&ou
   out[3] = lop3_and_xor(w8, 0x00F000F0u, kBiasOdd);
 }
 
+// The eight MMAs of a group are spread over kC independent accumulation chains;
+// the group sum is the chains' sum in a fixed order, the same in build_bias and
+// consume_chunk.  Measured on the M=1 set: 2 chains 49.0 us, 4 chains 52.0 us,
+// 8 chains 54.9 us per launch (the extra adds and registers cost more than the
+// shorter dependency chains bring).
+#ifndef CB200_CHAINS
+#define CB200_CHAINS 2
+#endif
+__host__ __device__ constexpr int chains_per_group(int nt) { return nt <= 2 ? CB200_CHAINS : 2; }
+__device__ __forceinline__ constexpr int chain_of(int kc, int w, int h) {
+  return kc == 2 ? h : (kc == 4 ? (w & 1) * 2 + h : 2 * w + h);
+}
+template <int kC>
+__device__ __forceinline__ float chain_sum(const float (*part)[4], int e) {
+  if (kC == 2) return part[0][e] + part[1][e];
+  if (kC == 4) return (part[0][e] + part[1][e]) + (part[2][e] + part[3][e]);
+  return ((part[0][e] + part[1][e]) + (part[2][e] + part[3][e])) +
+         ((part[4][e] + part[5][e]) + (part[6][e] + part[7][e]));
+}
+
 // Offset sums: bias[g][n] = (sum over group g of 8 * x[n][k]) * 2^-69, for the
 // 8*NT MMA columns n, written by the lanes that own row 0 of the fragment.
 // The instruction sequence mirrors one_group() in consume_chunk exactly.
@@ -357,11 +403,12 @@ __device__ __forceinline__ void build_bias(const std::uint8_t* xs, float* bias, 
     xrow[nt] = xs + (n < M ? n : M) * rsx + t * 8;
   }
   for (int g = warp; g < G; g += nwarps) {
-    float part[NT][2][4];
+    constexpr int kC = chains_per_group(NT);
+    float part[NT][kC][4];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-      for (int c = 0; c < 2; ++c)
+      for (int c = 0; c < kC; ++c)
         part[nt][c][0] = part[nt][c][1] = part[nt][c][2] = part[nt][c][3] = 0.f;
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
@@ -371,15 +418,16 @@ __device__ __forceinline__ void build_bias(const std::uint8_t* xs, float* bias, 
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
           const uint2 b = lds64(xrow[nt] + g * 256 + j * 32);
-          mma_m16n8k16_bf16(part[nt][h], kBiasEven, kBiasEven, kBiasOdd, kBiasOdd, b.x, b.y);
+          mma_m16n8k16_bf16(part[nt][chain_of(kC, w, h)], kBiasEven, kBiasEven, kBiasOdd, kBiasOdd,
+                            b.x, b.y);
         }
       }
     }
     if (r8 == 0) {
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
-        bias[g * (NT * 8) + nt * 8 + 2 * t] = part[nt][0][0] + part[nt][1][0];
-        bias[g * (NT * 8) + nt * 8 + 2 * t + 1] = part[nt][0][1] + part[nt][1][1];
+        bias[g * (NT * 8) + nt * 8 + 2 * t] = chain_sum<kC>(part[nt], 0);
+        bias[g * (NT * 8) + nt * 8 + 2 * t + 1] = chain_sum<kC>(part[nt], 1);
       }
     }
   }
@@ -412,12 +460,13 @@ __device__ __forceinline__ void consume_chunk(const std::uint8_t* stage, const s
     const float s_hi = __half2float(__ushort_as_half(lds16(sb + 2 * g)));
     const std::uint32_t wordA[4] = {qa.x, qa.y, qa.z, qa.w};
     const std::uint32_t wordB[4] = {qb.x, qb.y, qb.z, qb.w};
-    // two accumulation chains per column tile halve the MMA dependency depth
-    float part[NT][2][4];
+    // several accumulation chains per column tile cut the MMA dependency depth
+    constexpr int kC = chains_per_group(NT);
+    float part[NT][kC][4];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-      for (int c = 0; c < 2; ++c)
+      for (int c = 0; c < kC; ++c)
         part[nt][c][0] = part[nt][c][1] = part[nt][c][2] = part[nt][c][3] = 0.f;
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
@@ -430,17 +479,18 @@ __device__ __forceinline__ void consume_chunk(const std::uint8_t* stage, const s
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
           const uint2 b = lds64(xrow[nt] + g * 256 + j * 32);
-          mma_m16n8k16_bf16(part[nt][h], A[2 * h], B[2 * h], A[2 * h + 1], B[2 * h + 1], b.x, b.y);
+          mma_m16n8k16_bf16(part[nt][chain_of(kC, w, h)], A[2 * h], B[2 * h], A[2 * h + 1],
+                            B[2 * h + 1], b.x, b.y);
         }
       }
     }
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
       const float2 b8 = *reinterpret_cast<const float2*>(brow + g * (NT * 8) + nt * 8);
-      acc[nt][0] = fmaf(s_lo, (part[nt][0][0] + part[nt][1][0]) - b8.x, acc[nt][0]);
-      acc[nt][1] = fmaf(s_lo, (part[nt][0][1] + part[nt][1][1]) - b8.y, acc[nt][1]);
-      acc[nt][2] = fmaf(s_hi, (part[nt][0][2] + part[nt][1][2]) - b8.x, acc[nt][2]);
-      acc[nt][3] = fmaf(s_hi, (part[nt][0][3] + part[nt][1][3]) - b8.y, acc[nt][3]);
+      acc[nt][0] = fmaf(s_lo, chain_sum<kC>(part[nt], 0) - b8.x, acc[nt][0]);
+      acc[nt][1] = fmaf(s_lo, chain_sum<kC>(part[nt], 1) - b8.y, acc[nt][1]);
+      acc[nt][2] = fmaf(s_hi, chain_sum<kC>(part[nt], 2) - b8.x, acc[nt][2]);
+      acc[nt][3] = fmaf(s_hi, chain_sum<kC>(part[nt], 3) - b8.y, acc[nt][3]);
     }
   };
   if (cg == CG) {
@@ -596,24 +646,36 @@ __device__ __forceinline__ bool wait_x_ready(const DescSource& ds, CtaControl* c
   }
 }
 
-template <int NT, int CG, int NWARPS, bool CTA_MAX>
-__global__ void __launch_bounds__(NWARPS * 32, 1)
+// NPROD = 0: every warp feeds itself.  NPROD > 0 (= NWARPS / 4): the NWARPS
+// consumer warps only compute; NPROD further warps issue the copies, one thread
+// each for four consumers, as soon as a consumer hands a stage back through its
+// "empty" mbarrier (issuing a chunk's copies costs a warp several hundred cycles).
+template <int NT, int CG, int NWARPS, bool CTA_MAX, int NPROD>
+__global__ void __launch_bounds__((NWARPS + NPROD) * 32, 1)
 w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
   extern __shared__ __align__(128) std::uint8_t smem[];
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
   const int depth = p.depth;
   const bool async_switch = p.x_buffers == 2;
+  // barrier over the consumer warps only
+  auto consumer_sync = [&]() {
+    if (NPROD == 0) __syncthreads();
+    else asm volatile("bar.sync 1, %0;" ::"r"(NWARPS * 32) : "memory");
+  };
 
   // shared memory: [barriers, control][activation buffers][NWARPS rings of `depth` stages]
-  std::uint64_t* bars = reinterpret_cast<std::uint64_t*>(smem) + warp * kMaxDepth;
+  std::uint64_t* all_full = reinterpret_cast<std::uint64_t*>(smem);
+  std::uint64_t* all_empty = reinterpret_cast<std::uint64_t*>(smem + kHeaderBytes - kMaxWarps * kMaxDepth * 8);
+  std::uint64_t* bars = all_full + (warp < NWARPS ? warp : 0) * kMaxDepth;
+  std::uint64_t* ebars = all_empty + (warp < NWARPS ? warp : 0) * kMaxDepth;
   CtaControl* ctl = reinterpret_cast<CtaControl*>(smem + kMaxWarps * kMaxDepth * 8);
   std::uint8_t* xs0 = smem + kHeaderBytes;
   // the staging area of the barrier-free change of projection follows the two buffers
   std::uint8_t* staging = xs0 + 2 * static_cast<std::size_t>(p.x_bytes);
-  std::uint8_t* ring = xs0 + static_cast<std::size_t>(p.x_buffers) * p.x_bytes +
-                       (async_switch ? kAsyncFillMaxValues * 2 : 0) +
-                       static_cast<std::size_t>(warp) * depth * p.stage_bytes;
+  std::uint8_t* rings = xs0 + static_cast<std::size_t>(p.x_buffers) * p.x_bytes +
+                        (async_switch ? kAsyncFillMaxValues * 2 : 0);
+  std::uint8_t* ring = rings + static_cast<std::size_t>(warp < NWARPS ? warp : 0) * depth * p.stage_bytes;
 
   // this CTA's contiguous range of m-tiles: an equal share of the launch's work
   int mt_lo, mt_hi, d_first;
@@ -629,13 +691,18 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
   }
   if (mt_lo >= mt_hi) d_first = p.n_desc;
 
-  if (lane == 0) {
-    for (int s = 0; s < depth; ++s) mbar_init(&bars[s], 1);
+  if (lane == 0 && warp < NWARPS) {
+    for (int s = 0; s < depth; ++s) {
+      mbar_init(&bars[s], 1);
+      if (NPROD > 0) mbar_init(&ebars[s], 1);
+    }
     mbar_init_fence();
   }
+  if (tid < NWARPS) ctl->issued[tid] = 0;
   if (tid == 0) {
     ctl->fill_claim = ctl->fill_done = d_first;
     ctl->fill_parts = 0;
+    ctl->abort = 0;
     mbar_init(reinterpret_cast<std::uint64_t*>(&ctl->xbar), 1);
     mbar_init_fence();
   }
@@ -655,6 +722,75 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
   const DescSource ds{&p, ctl->desc, d_first};
 
   const std::uint64_t policy = policy_evict_first();
+
+  if (NPROD > 0 && warp >= NWARPS) {
+    // ---------------- producer: one thread feeds four consumer warps ----------------
+    // It touches only weights and scales, constants of the model, so it does not
+    // wait for the previous grid either.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (lane != 0 || d_first >= p.n_desc) return;
+    const int w0 = (warp - NWARPS) * 4;
+    Cursor<CG> pc[4];
+    int taken[4], pslot[4], nissued[4];
+    std::uint32_t pphase[4];
+    int live = 0;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      pc[c].valid = false;
+      pc[c].bind(ds, d_first);
+      taken[c] = 1;
+      pslot[c] = 0;
+      pphase[c] = 1;  // a fresh barrier reads as "phase 1 complete": the first round does not wait
+      nissued[c] = 0;
+      const int m = mt_lo + w0 + c;
+      pc[c].seek(ds, m < mt_hi ? m : mt_hi, mt_hi);
+      live += pc[c].valid ? 1 : 0;
+    }
+    unsigned long long t0 = 0;
+    int idle = 0;
+    while (live > 0) {
+      bool progressed = false;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        if (!pc[c].valid) continue;
+        std::uint64_t* eb = all_empty + (w0 + c) * kMaxDepth + pslot[c];
+        if (!mbar_try_wait(eb, pphase[c])) continue;
+        std::uint8_t* st = rings + (static_cast<std::size_t>(w0 + c) * depth + pslot[c]) * p.stage_bytes;
+        issue_item_single<CG>(pc[c], st, all_full + (w0 + c) * kMaxDepth + pslot[c], policy);
+        st_volatile_s32(&ctl->issued[w0 + c], ++nissued[c]);
+        if (++pslot[c] == depth) {
+          pslot[c] = 0;
+          pphase[c] ^= 1u;
+        }
+        if (++pc[c].chunk >= pc[c].nch) {
+          const int m = mt_lo + w0 + c + taken[c] * NWARPS;
+          ++taken[c];
+          pc[c].seek(ds, m < mt_hi ? m : mt_hi, mt_hi);
+          if (!pc[c].valid) --live;
+        }
+        progressed = true;
+      }
+      if (progressed) {
+        idle = 0;
+        t0 = 0;
+        continue;
+      }
+      // nothing to do: a bounded, abort-aware pause
+      if (++idle >= 64) {
+        idle = 0;
+        if (ld_volatile_s32(&ctl->abort)) return;
+        unsigned long long t1;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
+        if (t0 == 0) t0 = t1;
+        else if (t1 - t0 > 4000000000ull) {
+          atomicExch(p.status, CUDALM_B200_ERR_TIMEOUT);
+          return;
+        }
+        __nanosleep(32);
+      }
+    }
+    return;
+  }
 
   // Two cursors over this warp's m-tiles (mt_lo + warp, + NWARPS, ...): `fc`
   // runs ahead issuing copies, `cc` consumes.  (Handing m-tiles out dynamically
@@ -683,13 +819,16 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
   // Weights and scales are constants of the model: their first copies go out
   // before this grid waits for its predecessor in the stream, so they overlap
   // the predecessor's tail.  Activations and outputs are touched only after.
-  int in_flight = 0;  // stages issued and not yet consumed
+  int in_flight = 0;  // self-feeding form: stages issued and not yet consumed
+  int consumed = 0;   // producer form: stages consumed so far
   if (d_first < p.n_desc) {
-    fc_next_mtile();
-    for (int s = 0; s < depth && fc.valid; ++s) {
-      issue_item<CG>(fc, ring + s * p.stage_bytes, &bars[s], lane, policy);
-      fc_advance();
-      ++in_flight;
+    if (NPROD == 0) {
+      fc_next_mtile();
+      for (int s = 0; s < depth && fc.valid; ++s) {
+        issue_item<CG>(fc, ring + s * p.stage_bytes, &bars[s], lane, policy);
+        fc_advance();
+        ++in_flight;
+      }
     }
     cc_next_mtile();
   }
@@ -718,17 +857,17 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
     std::uint8_t* xs;
     if (!async_switch || d == d_first) {
       // the whole CTA refills the buffer together
-      __syncthreads();  // every warp is done with the previous activations
+      consumer_sync();  // every warp is done with the previous activations
       xs = x_buffer(xs0, p.x_bytes, async_switch ? (d & 1) : 0);
       fill_x_fragments<4>(xs, L.x, LM, LK, rsx, tid, NWARPS * 32);
-      __syncthreads();
+      consumer_sync();
       build_bias<NT>(xs, reinterpret_cast<float*>(xs + (LM + 1) * rsx), G, rsx, LM, warp, lane,
                      NWARPS);
       if (async_switch && tid == 0) {
         ctl->fill_claim = d + 1;
         ctl->fill_done = d + 1;
       }
-      __syncthreads();
+      consumer_sync();
     } else {
       // this warp is past every earlier projection, whether it has work here or not
       __threadfence_block();  // this warp's reads of the earlier activations come first
@@ -738,7 +877,10 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
       if (!dead &&
           !wait_x_ready<NT>(ds, ctl, xs0, staging, xf, d, d, d_first, d_last, NWARPS, warp, lane)) {
         dead = true;
-        if (lane == 0) atomicExch(p.status, CUDALM_B200_ERR_TIMEOUT);
+        if (lane == 0) {
+          atomicExch(p.status, CUDALM_B200_ERR_TIMEOUT);
+          st_volatile_s32(&ctl->abort, 1);
+        }
       }
       xs = x_buffer(xs0, p.x_bytes, d & 1);
     }
@@ -754,17 +896,34 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
         std::uint8_t* stage = ring + slot * p.stage_bytes;
         if (!dead && !wait_stage(&bars[slot], parity)) {
           dead = true;
-          if (lane == 0) atomicExch(p.status, CUDALM_B200_ERR_TIMEOUT);
+          if (lane == 0) {
+            atomicExch(p.status, CUDALM_B200_ERR_TIMEOUT);
+            st_volatile_s32(&ctl->abort, 1);
+          }
         }
         if (!dead) {
           const int g0 = ch * CG;
+          if (NPROD > 0 && !stage_scales_bulk<CG>(cc)) {
+            // a ragged or unaligned scale block, which the producer leaves to the reader
+            const int srow0 = (cc.mt - cc.mt_begin) * kMTileRows;
+            const int n_sc = min(kMTileRows, cc.N - srow0) * cc.G;
+            const std::uint16_t* ssrc = cc.S + static_cast<std::size_t>(srow0) * cc.G;
+            std::uint16_t* sdst = reinterpret_cast<std::uint16_t*>(stage + kMTileRows * CG * 64);
+            for (int i = lane; i < n_sc; i += 32) sdst[i] = __ldg(ssrc + i);
+            __syncwarp();
+          }
           consume_chunk<NT, CG>(stage, xs, bias, G, g0, min(CG, G - g0), rsx, LM, lane, acc);
           __syncwarp();
-          --in_flight;
-          if (fc.valid) {
-            issue_item<CG>(fc, stage, &bars[slot], lane, policy);
-            fc_advance();
-            ++in_flight;
+          if (NPROD > 0) {
+            ++consumed;
+            if (lane == 0) mbar_arrive(&ebars[slot]);  // hands the stage back to the producer
+          } else {
+            --in_flight;
+            if (fc.valid) {
+              issue_item<CG>(fc, stage, &bars[slot], lane, policy);
+              fc_advance();
+              ++in_flight;
+            }
           }
           if (async_switch) {
             (void)service_fill<NT>(ds, ctl, xs0, staging, xf, d, d_first, d_last, NWARPS, warp, lane);
@@ -817,11 +976,18 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
       !wait_x_ready<NT>(ds, ctl, xs0, staging, xf, d_last, 0x7fffffff, d_first, d_last, NWARPS, warp,
                         lane)) {
     dead = true;
-    if (lane == 0) atomicExch(p.status, CUDALM_B200_ERR_TIMEOUT);
+    if (lane == 0) {
+      atomicExch(p.status, CUDALM_B200_ERR_TIMEOUT);
+      st_volatile_s32(&ctl->abort, 1);
+    }
   }
   if (dead) {
     // Give copies still in flight a bounded chance to land before the CTA's
     // shared memory is released.
+    if (NPROD > 0) {
+      __nanosleep(2000);  // the producer stops at the abort flag
+      in_flight = ld_volatile_s32(&ctl->issued[warp]) - consumed;
+    }
     for (int i = 0; i < in_flight; ++i) {
       (void)wait_stage(&bars[slot], parity);
       if (++slot == depth) {
@@ -845,7 +1011,7 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
         vmax[nt][c] = v;
       }
     }
-    __syncthreads();  // the activation region is free again; reuse it as scratch
+    consumer_sync();  // the activation region is free again; reuse it as scratch
     float* red = reinterpret_cast<float*>(xs0);  // [NWARPS][NT*8]
     if (lane < 4) {
 #pragma unroll
@@ -854,7 +1020,7 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
         red[warp * (NT * 8) + nt * 8 + 2 * lane + 1] = vmax[nt][1];
       }
     }
-    __syncthreads();
+    consumer_sync();
     if (tid < M && tid < NT * 8) {
       float v = -INFINITY;
       for (int w = 0; w < NWARPS; ++w) v = fmaxf(v, red[w * (NT * 8) + tid]);

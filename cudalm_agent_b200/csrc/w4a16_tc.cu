@@ -109,9 +109,6 @@ __device__ __forceinline__ void tc_commit(std::uint64_t* bar) {
                    smem_u32(bar))
                : "memory");
 }
-__device__ __forceinline__ void mbar_arrive(std::uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
 // D[tmem] (+)= A[tmem] * B[smem]; accumulate = 0 overwrites D.
 __device__ __forceinline__ void tc_mma_ts(std::uint32_t d_tmem, std::uint32_t a_tmem,
                                           std::uint64_t b_desc, std::uint32_t idesc,
