@@ -66,6 +66,8 @@ SIGNATURES = {
     "cudalm_b200_group_destroy": (_ci, [_vp]),
     "cudalm_b200_group_bytes": (ctypes.c_int64, [_vp]),
     "cudalm_b200_gate_up_bf16": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _vp]),
+    "cudalm_b200_gate_up_silu_bf16": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _vp]),
+    "cudalm_b200_linear_residual_bf16": (_ci, [_vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _vp]),
     "cudalm_b200_lm_head_workspace_bytes": (ctypes.c_size_t, [_ci, _ci, _ci, _ci, _ci]),
     "cudalm_b200_lm_head_topk": (_ci, [_vp, _vp, _vp, _ci, _ci, _ci, _ci, _ci, _vp, _vp, _vp,
                                       _vp, _vp, ctypes.c_size_t, _vp]),
@@ -247,6 +249,40 @@ def gate_up_bf16(gate: W4A16Linear, up: W4A16Linear, x: torch.Tensor,
         _ptr(gate_y), _ptr(up_y), gate.N, gate.K, M, _stream())
     _check("gate_up_bf16", st)
     return gate_y, up_y
+
+
+def gate_up_silu_bf16(gate: W4A16Linear, up: W4A16Linear, x: torch.Tensor,
+                      out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """silu(gate(x)) * up(x) in one launch, rounded as CUDALM rounds it
+    (src/kernels/qwen35_kernels.cu:459-476 after the two projections)."""
+    _need(x, torch.bfloat16, "x")
+    if gate.N != up.N or gate.K != up.K:
+        raise ValueError("gate and up must have the same shape")
+    M = 1 if x.dim() == 1 else int(x.shape[0])
+    if out is None:
+        out = torch.empty((gate.N,) if x.dim() == 1 else (M, gate.N), dtype=torch.bfloat16,
+                          device=x.device)
+    st = load_library().cudalm_b200_gate_up_silu_bf16(
+        _ptr(gate.weight), _ptr(gate.scale), _ptr(up.weight), _ptr(up.scale), _ptr(x), _ptr(out),
+        gate.N, gate.K, M, _stream())
+    _check("gate_up_silu_bf16", st)
+    return out
+
+
+def linear_residual_bf16(lin: W4A16Linear, x: torch.Tensor, residual: torch.Tensor,
+                         y: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """residual + lin(x), rounded as CUDALM rounds it (projection to bf16, then
+    src/kernels/qwen35_kernels.cu:442-456)."""
+    _need(x, torch.bfloat16, "x")
+    _need(residual, torch.bfloat16, "residual")
+    M = 1 if x.dim() == 1 else int(x.shape[0])
+    if y is None:
+        y = torch.empty_like(residual)
+    st = load_library().cudalm_b200_linear_residual_bf16(
+        _ptr(lin.weight), _ptr(lin.scale), _ptr(x), _ptr(residual), _ptr(y), lin.N, lin.K, M,
+        _stream())
+    _check("linear_residual_bf16", st)
+    return y
 
 
 class LinearGroup:

@@ -29,34 +29,49 @@ std::atomic<int> g_tc_min_rows{17};
 // calls legal) or K above the staged limit.  One warp per output row, byte
 // loads, fp32 accumulation in a fixed order.
 // ---------------------------------------------------------------------------
+__device__ __forceinline__ float fallback_row_dot(const std::uint8_t* wrow, const std::uint16_t* srow,
+                                                  const std::uint16_t* xm, int K, int lane) {
+  float acc = 0.f;
+  for (int g = 0; g < (K >> 7); ++g) {
+    const float s = __half2float(__ushort_as_half(srow[g]));
+    float part = 0.f;
+    for (int b = lane; b < 64; b += 32) {
+      const std::uint8_t byte = wrow[g * 64 + b];
+      const int lo = static_cast<int>(static_cast<std::int8_t>((byte & 0x0Fu) << 4)) >> 4;
+      const int hi = static_cast<int>(static_cast<std::int8_t>(byte)) >> 4;
+      const int k = g * 128 + 2 * b;
+      part = fmaf(static_cast<float>(lo), bf16_bits_to_float(xm[k]), part);
+      part = fmaf(static_cast<float>(hi), bf16_bits_to_float(xm[k + 1]), part);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
+    acc = fmaf(s, part, acc);
+  }
+  return acc;
+}
+
+// W2/S2 non-null: y = silu(W x) * (W2 x); res non-null: y = res + W x (CUDALM's
+// rounding order, see silu_mul_bits / add_bits).
 __global__ void __launch_bounds__(256)
 w4a16_fallback_kernel(const std::uint8_t* __restrict__ W, const std::uint16_t* __restrict__ S,
                       const std::uint16_t* __restrict__ x, std::uint16_t* __restrict__ y, int N,
-                      int K, int M) {
+                      int K, int M, const std::uint8_t* __restrict__ W2 = nullptr,
+                      const std::uint16_t* __restrict__ S2 = nullptr,
+                      const std::uint16_t* __restrict__ res = nullptr) {
   const int lane = threadIdx.x & 31;
   const long long row = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= N) return;
-  const std::uint8_t* wrow = W + row * (K >> 1);
-  const std::uint16_t* srow = S + row * (K >> 7);
   for (int m = 0; m < M; ++m) {
     const std::uint16_t* xm = x + static_cast<std::size_t>(m) * K;
-    float acc = 0.f;
-    for (int g = 0; g < (K >> 7); ++g) {
-      const float s = __half2float(__ushort_as_half(srow[g]));
-      float part = 0.f;
-      for (int b = lane; b < 64; b += 32) {
-        const std::uint8_t byte = wrow[g * 64 + b];
-        const int lo = static_cast<int>(static_cast<std::int8_t>((byte & 0x0Fu) << 4)) >> 4;
-        const int hi = static_cast<int>(static_cast<std::int8_t>(byte)) >> 4;
-        const int k = g * 128 + 2 * b;
-        part = fmaf(static_cast<float>(lo), bf16_bits_to_float(xm[k]), part);
-        part = fmaf(static_cast<float>(hi), bf16_bits_to_float(xm[k + 1]), part);
-      }
-#pragma unroll
-      for (int off = 16; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
-      acc = fmaf(s, part, acc);
+    std::uint16_t o = float_to_bf16_bits(fallback_row_dot(W + row * (K >> 1), S + row * (K >> 7), xm, K, lane));
+    if (W2) {
+      const std::uint16_t u = float_to_bf16_bits(
+          fallback_row_dot(W2 + row * (K >> 1), S2 + row * (K >> 7), xm, K, lane));
+      o = silu_mul_bits(bf16_bits_to_float(o), u);
+    } else if (res) {
+      o = add_bits(res[static_cast<std::size_t>(m) * N + row], o);
     }
-    if (lane == 0) y[static_cast<std::size_t>(m) * N + row] = float_to_bf16_bits(acc);
+    if (lane == 0) y[static_cast<std::size_t>(m) * N + row] = o;
   }
 }
 
@@ -130,11 +145,11 @@ int max_rows_per_pass(int k) {
 #define CB200_PRODUCERS 1  // producer warps for the 8-consumer form
 #endif
 
-template <int NT, int NWARPS, bool CTA_MAX>
+template <int NT, int NWARPS, bool CTA_MAX, bool EXTRA = false>
 int launch_instance(const StreamParams& p, const Plan& pl, int grid, cudaStream_t stream) {
   // producer warps need registers: only the 8-consumer form has room for them
   constexpr int kProd = (CB200_PRODUCERS && NWARPS == 8) ? NWARPS / 4 : 0;
-  auto kern = w4a16_stream_kernel<NT, kCG, NWARPS, CTA_MAX, kProd>;
+  auto kern = w4a16_stream_kernel<NT, kCG, NWARPS, CTA_MAX, kProd, EXTRA>;
   // the attribute is per device; set it on every device this process uses
   static std::mutex mu;
   static std::vector<int> done_devices;
@@ -179,7 +194,7 @@ int launch_instance(const StreamParams& p, const Plan& pl, int grid, cudaStream_
 }
 
 int launch_stream(StreamParams& p, int kmax, int mmax, cudaStream_t stream,
-                  int* grid_out = nullptr, int forced_grid = 0) {
+                  int* grid_out = nullptr, int forced_grid = 0, bool extra = false) {
   Plan pl;
   if (!make_plan(kmax, mmax, &pl, p.n_desc > 1)) return CUDALM_B200_ERR_UNSUPPORTED;
   p.depth = pl.depth;
@@ -194,6 +209,14 @@ int launch_stream(StreamParams& p, int kmax, int mmax, cudaStream_t stream,
   if (forced_grid > 0) grid = forced_grid;  // a group's per-CTA ranges were cut for this grid
   if (grid_out) *grid_out = grid;
   const bool want_max = p.cta_max != nullptr;
+  if (extra) {
+    // launches with an MLP epilogue: at most 16 rows, no per-CTA maxima
+    if (pl.nt == 1 && pl.nwarps == 12) return launch_instance<1, 12, false, true>(p, pl, grid, stream);
+    if (pl.nt == 2 && pl.nwarps == 12) return launch_instance<2, 12, false, true>(p, pl, grid, stream);
+    if (pl.nt == 1 && pl.nwarps == 8) return launch_instance<1, 8, false, true>(p, pl, grid, stream);
+    if (pl.nt == 2 && pl.nwarps == 8) return launch_instance<2, 8, false, true>(p, pl, grid, stream);
+    return CUDALM_B200_ERR_UNSUPPORTED;
+  }
 #define CB200_CASE(NT_, NW_)                                                        \
   if (pl.nt == NT_ && pl.nwarps == NW_)                                             \
     return want_max ? launch_instance<NT_, NW_, true>(p, pl, grid, stream)          \
@@ -293,8 +316,28 @@ int encode_weight_map_uncached(const std::uint8_t* weight, int N, int K, CUtenso
   return CUDALM_B200_OK;
 }
 
-int to_dev(const cudalm_b200_linear& l, int mt_begin, int cost_begin, LinearDev* d) {
+// What the fused MLP entries add to a projection: a second matrix over the same
+// input (out = silu(W x) * (W2 x)) or a residual (out = residual + W x).
+struct LinearExtra {
+  const std::uint8_t* weight2 = nullptr;
+  const std::uint16_t* scales2 = nullptr;
+  const std::uint16_t* residual = nullptr;
+};
+
+int to_dev(const cudalm_b200_linear& l, int mt_begin, int cost_begin, LinearDev* d,
+           const LinearExtra* ex = nullptr) {
   if (int rc = encode_weight_map(l.weight, l.N, l.K, &d->tmap)) return rc;
+  d->S2 = nullptr;
+  d->res = nullptr;
+  int extra_flags = 0;
+  if (ex && ex->weight2) {
+    if (int rc = encode_weight_map(ex->weight2, l.N, l.K, &d->tmap2)) return rc;
+    d->S2 = ex->scales2;
+    extra_flags |= kFlagPair | (aligned_to(ex->scales2, 16) ? kFlagScales2Bulk : 0);
+  } else if (ex && ex->residual) {
+    d->res = ex->residual;
+    extra_flags |= kFlagResidual;
+  }
   d->S = l.scales;
   d->x = l.x;
   d->y = l.y;
@@ -302,7 +345,7 @@ int to_dev(const cudalm_b200_linear& l, int mt_begin, int cost_begin, LinearDev*
   d->K = l.K;
   d->M = l.M;
   d->mt_begin = mt_begin;
-  d->flags = aligned_to(l.scales, 16) ? kFlagScalesBulk : 0;
+  d->flags = (aligned_to(l.scales, 16) ? kFlagScalesBulk : 0) | extra_flags;
   d->cost_begin = cost_begin;
   return CUDALM_B200_OK;
 }
@@ -350,6 +393,40 @@ int run_single(cudalm_b200_linear l, cudaStream_t stream) {
     p.total_mt = mtiles(l.N);
     p.total_cost = p.total_mt * chunks_per_mtile(l.K);
     if (int rc = launch_stream(p, l.K, part.M, stream)) return rc;
+  }
+  return CUDALM_B200_OK;
+}
+
+// A projection with an MLP epilogue: passes of up to 16 rows on the streaming
+// kernel (the pair keeps its first outputs in registers), or the slow kernel.
+int run_extra(cudalm_b200_linear l, const LinearExtra& ex, cudaStream_t stream) {
+  if (int rc = validate(l)) return rc;
+  const bool pair = ex.weight2 != nullptr;
+  if (pair && !ex.scales2) return CUDALM_B200_ERR_NULL;
+  int per_pass = stream_eligible(l) && (!pair || aligned_to(ex.weight2, 16)) ? max_rows_per_pass(l.K) : 0;
+  if (per_pass > 16) per_pass = 16;
+  if (per_pass == 0) {
+    const int rows_per_block = 8;
+    const int grid = (l.N + rows_per_block - 1) / rows_per_block;
+    w4a16_fallback_kernel<<<grid, rows_per_block * 32, 0, stream>>>(
+        l.weight, l.scales, l.x, l.y, l.N, l.K, l.M, ex.weight2, ex.scales2, ex.residual);
+    return check_launch();
+  }
+  const int M = l.M;
+  for (int m0 = 0; m0 < M; m0 += per_pass) {
+    cudalm_b200_linear part = l;
+    part.M = (M - m0 < per_pass) ? (M - m0) : per_pass;
+    part.x = l.x + static_cast<std::size_t>(m0) * l.K;
+    part.y = l.y + static_cast<std::size_t>(m0) * l.N;
+    LinearExtra pex = ex;
+    if (ex.residual) pex.residual = ex.residual + static_cast<std::size_t>(m0) * l.N;
+    StreamParams p;
+    std::memset(&p, 0, sizeof(p));
+    if (int rc = to_dev(part, 0, 0, &p.inl[0], &pex)) return rc;
+    p.n_desc = 1;
+    p.total_mt = mtiles(l.N);
+    p.total_cost = p.total_mt * chunks_per_mtile(l.K) * (pair ? 2 : 1);
+    if (int rc = launch_stream(p, l.K, part.M, stream, nullptr, 0, true)) return rc;
   }
   return CUDALM_B200_OK;
 }
@@ -476,6 +553,28 @@ int cudalm_b200_gate_up_bf16(const uint8_t* gate_weight, const uint16_t* gate_sc
     if (int rc = cudalm_b200_linear_multi(two, 2, st)) return rc;
   }
   return CUDALM_B200_OK;
+}
+
+int cudalm_b200_gate_up_silu_bf16(const uint8_t* gate_weight, const uint16_t* gate_scales,
+                                  const uint8_t* up_weight, const uint16_t* up_scales,
+                                  const uint16_t* x, uint16_t* out, int N, int K, int M,
+                                  void* stream) {
+  if (!up_weight || !up_scales) return CUDALM_B200_ERR_NULL;
+  cudalm_b200_linear l{gate_weight, gate_scales, x, out, N, K, M, 0};
+  LinearExtra ex;
+  ex.weight2 = up_weight;
+  ex.scales2 = up_scales;
+  return run_extra(l, ex, static_cast<cudaStream_t>(stream));
+}
+
+int cudalm_b200_linear_residual_bf16(const uint8_t* weight, const uint16_t* scales,
+                                     const uint16_t* x, const uint16_t* residual, uint16_t* y,
+                                     int N, int K, int M, void* stream) {
+  if (!residual) return CUDALM_B200_ERR_NULL;
+  cudalm_b200_linear l{weight, scales, x, y, N, K, M, 0};
+  LinearExtra ex;
+  ex.residual = residual;
+  return run_extra(l, ex, static_cast<cudaStream_t>(stream));
 }
 
 int cudalm_b200_group_create(const cudalm_b200_linear* linears, int count,
@@ -695,7 +794,7 @@ int cudalm_b200_kernel_regs(const char* kernel_name) {
 #define CB200_NAME(NT_, NW_)                                                     \
   if (std::strcmp(kernel_name, "w4a16_stream_nt" #NT_ "_w" #NW_) == 0)           \
     fn = reinterpret_cast<const void*>(                                           \
-        &w4a16_stream_kernel<NT_, kCG, NW_, false, (CB200_PRODUCERS && NW_ == 8) ? 2 : 0>);
+        &w4a16_stream_kernel<NT_, kCG, NW_, false, (CB200_PRODUCERS && NW_ == 8) ? 2 : 0, false>);
   CB200_NAME(1, 12) CB200_NAME(2, 12) CB200_NAME(4, 12)
   CB200_NAME(1, 8) CB200_NAME(2, 8) CB200_NAME(4, 8) CB200_NAME(8, 8)
 #undef CB200_NAME

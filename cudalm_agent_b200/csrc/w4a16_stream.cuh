@@ -41,18 +41,26 @@ constexpr int kMaxDepth = 4;
 constexpr int kMaxWarps = 16;
 // shared-memory header: "full" mbarriers [kMaxWarps][kMaxDepth], CtaControl, and in
 // its last 512 bytes the "empty" mbarriers [kMaxWarps][kMaxDepth] of the producer form
-constexpr int kHeaderBytes = 1664;
+constexpr int kHeaderBytes = 1920;
 // projections of a CTA's range whose descriptors are kept in shared memory
 constexpr int kDescCache = 8;
 // largest M*K one warp refills on its own (the barrier-free change of projection)
 constexpr int kAsyncFillMaxValues = 8192;
 
-enum : int { kFlagScalesBulk = 1 };
+enum : int {
+  kFlagScalesBulk = 1,   // the scales' base is 16-byte aligned: bulk copies
+  kFlagPair = 2,         // gate and up matrices over one input: out = silu(gate) * up
+  kFlagScales2Bulk = 4,  // the same for the second matrix of a pair
+  kFlagResidual = 8,     // out = residual + projection
+};
 
 // Device-side projection descriptor.
 struct alignas(64) LinearDev {
-  CUtensorMap tmap;  // weight matrix as uint32 [N][K/8], box 16 rows x CG*16 words
+  CUtensorMap tmap;   // weight matrix as uint32 [N][K/8], box 16 rows x CG*16 words
+  CUtensorMap tmap2;  // second matrix of a pair (kFlagPair)
   const std::uint16_t* S;
+  const std::uint16_t* S2;   // scales of the second matrix
+  const std::uint16_t* res;  // residual [M][N] (kFlagResidual)
   const std::uint16_t* x;
   std::uint16_t* y;
   int N, K, M;
@@ -110,7 +118,7 @@ __device__ __forceinline__ int mtile_at_cost(const StreamParams& p, long long co
     const int mid = (lo + hi + 1) >> 1;
     if (tbl[mid].cost_begin <= cost) lo = mid; else hi = mid - 1;
   }
-  const int nch = ((tbl[lo].K >> 7) + CG - 1) / CG;
+  const int nch = (((tbl[lo].K >> 7) + CG - 1) / CG) * ((tbl[lo].flags & kFlagPair) ? 2 : 1);
   const int within = static_cast<int>(cost) - tbl[lo].cost_begin;
   return tbl[lo].mt_begin + (within + nch - 1) / nch;
 }
@@ -119,7 +127,10 @@ __device__ __forceinline__ int mtile_at_cost(const StreamParams& p, long long co
 // What the kernel needs of a projection, without the tensor map itself.
 struct DescLite {
   const CUtensorMap* tmap;
+  const CUtensorMap* tmap2;
   const std::uint16_t* S;
+  const std::uint16_t* S2;
+  const std::uint16_t* res;
   const std::uint16_t* x;
   std::uint16_t* y;
   int N, K, M, mt_begin, flags, pad;
@@ -158,7 +169,8 @@ __device__ __forceinline__ void st_volatile_s32(int* p, int v) {
 __device__ __forceinline__ DescLite get_desc(const DescSource& ds, int d) {
   if (d - ds.d_first < kDescCache) return ds.cache[d - ds.d_first];
   const LinearDev* L = desc_table(*ds.p) + d;
-  return DescLite{&L->tmap, L->S, L->x, L->y, L->N, L->K, L->M, L->mt_begin, L->flags, 0};
+  return DescLite{&L->tmap, &L->tmap2, L->S, L->S2, L->res, L->x, L->y,
+                  L->N,     L->K,      L->M, L->mt_begin, L->flags, 0};
 }
 
 // Position of a warp in the launch: an m-tile, the chunk inside it and the
@@ -166,9 +178,13 @@ __device__ __forceinline__ DescLite get_desc(const DescSource& ds, int d) {
 template <int CG>
 struct Cursor {
   int d, mt, chunk;
-  int mt_begin, mt_end, nch, N, G, flags;
+  int mt_begin, mt_end, N, G, flags;
+  int nch;        // chunks of one matrix per m-tile
+  int nch_total;  // chunks per m-tile: twice nch for a pair (first matrix, then second)
   const CUtensorMap* tmap;
+  const CUtensorMap* tmap2;
   const std::uint16_t* S;
+  const std::uint16_t* S2;
   bool valid;
 
   __device__ __forceinline__ void bind(const DescSource& ds, int dd) {
@@ -180,8 +196,20 @@ struct Cursor {
     G = L.K >> 7;
     flags = L.flags;
     tmap = L.tmap;
+    tmap2 = L.tmap2;
     S = L.S;
+    S2 = L.S2;
     nch = (G + CG - 1) / CG;
+    nch_total = (flags & kFlagPair) ? 2 * nch : nch;
+  }
+  // The current chunk's matrix (a pair: first all chunks of the gate matrix,
+  // then all chunks of the up matrix) and its index inside that matrix.
+  __device__ __forceinline__ bool second() const { return chunk >= nch; }
+  __device__ __forceinline__ int chunk_in() const { return chunk >= nch ? chunk - nch : chunk; }
+  __device__ __forceinline__ const CUtensorMap* cur_map() const { return chunk >= nch ? tmap2 : tmap; }
+  __device__ __forceinline__ const std::uint16_t* cur_scales() const { return chunk >= nch ? S2 : S; }
+  __device__ __forceinline__ bool cur_scales_aligned() const {
+    return (flags & (chunk >= nch ? kFlagScales2Bulk : kFlagScalesBulk)) != 0;
   }
   // Moves to m-tile m, which is at or after the current one; m >= mt_hi ends
   // the walk.
@@ -207,7 +235,7 @@ __device__ __forceinline__ void tma_box_2d(void* smem_dst, const CUtensorMap* tm
 }
 
 // Starts the copies that fill `stage` with the cursor's item.
-template <int CG>
+template <int CG, bool EXTRA>
 __device__ __forceinline__ void issue_item(const Cursor<CG>& c, std::uint8_t* stage,
                                            std::uint64_t* bar, int lane,
                                            std::uint64_t policy) {
@@ -216,8 +244,9 @@ __device__ __forceinline__ void issue_item(const Cursor<CG>& c, std::uint8_t* st
   const int row0 = (c.mt - c.mt_begin) * kMTileRows;
   const int rows = min(kMTileRows, c.N - row0);
   const std::uint32_t sbytes = static_cast<std::uint32_t>(rows * c.G) * 2u;
-  const std::uint16_t* ssrc = c.S + static_cast<std::size_t>(row0) * c.G;
-  const bool sbulk = (c.flags & kFlagScalesBulk) && ((sbytes & 15u) == 0u);
+  const std::uint16_t* ssrc = (EXTRA ? c.cur_scales() : c.S) + static_cast<std::size_t>(row0) * c.G;
+  const bool sbulk = (EXTRA ? c.cur_scales_aligned() : (c.flags & kFlagScalesBulk) != 0) &&
+                     ((sbytes & 15u) == 0u);
   std::uint8_t* sdst = stage + kBoxBytes;
   if (!sbulk) {
     // ragged scale block (or an unaligned scale base): plain loads
@@ -231,7 +260,8 @@ __device__ __forceinline__ void issue_item(const Cursor<CG>& c, std::uint8_t* st
   __syncwarp();
   if (lane == 0) {
     mbar_arrive_expect_tx(bar, kBoxBytes + (sbulk ? sbytes : 0u));
-    tma_box_2d(stage, c.tmap, c.chunk * (CG * 16), row0, bar, policy);
+    tma_box_2d(stage, EXTRA ? c.cur_map() : c.tmap, (EXTRA ? c.chunk_in() : c.chunk) * (CG * 16), row0,
+               bar, policy);
     if (sbulk) bulk_g2s(sdst, ssrc, sbytes, bar);
   }
 }
@@ -239,13 +269,14 @@ __device__ __forceinline__ void issue_item(const Cursor<CG>& c, std::uint8_t* st
 // The same from a single thread that is not the stage's reader (producer form): the
 // reader released the stage through an mbarrier, which orders its reads before these
 // copies.  A ragged or unaligned scale block is left to the reader (stage_scales_bulk).
-template <int CG>
+template <int CG, bool EXTRA>
 __device__ __forceinline__ bool stage_scales_bulk(const Cursor<CG>& c) {
   const int row0 = (c.mt - c.mt_begin) * kMTileRows;
   const int rows = min(kMTileRows, c.N - row0);
-  return (c.flags & kFlagScalesBulk) && (((rows * c.G * 2) & 15) == 0);
+  return (EXTRA ? c.cur_scales_aligned() : (c.flags & kFlagScalesBulk) != 0) &&
+         (((rows * c.G * 2) & 15) == 0);
 }
-template <int CG>
+template <int CG, bool EXTRA>
 __device__ __forceinline__ void issue_item_single(const Cursor<CG>& c, std::uint8_t* stage,
                                                   std::uint64_t* bar, std::uint64_t policy) {
   constexpr int RS = CG * 64;
@@ -253,10 +284,13 @@ __device__ __forceinline__ void issue_item_single(const Cursor<CG>& c, std::uint
   const int row0 = (c.mt - c.mt_begin) * kMTileRows;
   const int rows = min(kMTileRows, c.N - row0);
   const std::uint32_t sbytes = static_cast<std::uint32_t>(rows * c.G) * 2u;
-  const bool sbulk = stage_scales_bulk<CG>(c);
+  const bool sbulk = stage_scales_bulk<CG, EXTRA>(c);
   mbar_arrive_expect_tx(bar, kBoxBytes + (sbulk ? sbytes : 0u));
-  tma_box_2d(stage, c.tmap, c.chunk * (CG * 16), row0, bar, policy);
-  if (sbulk) bulk_g2s(stage + kBoxBytes, c.S + static_cast<std::size_t>(row0) * c.G, sbytes, bar);
+  tma_box_2d(stage, EXTRA ? c.cur_map() : c.tmap, (EXTRA ? c.chunk_in() : c.chunk) * (CG * 16), row0,
+             bar, policy);
+  if (sbulk)
+    bulk_g2s(stage + kBoxBytes, (EXTRA ? c.cur_scales() : c.S) + static_cast<std::size_t>(row0) * c.G,
+             sbytes, bar);
 }
 
 // Bounded wait on a stage; false when it ran out (about two seconds).
@@ -503,6 +537,15 @@ __device__ __forceinline__ void consume_chunk(const std::uint8_t* stage, const s
   }
 }
 
+// Epilogues of the MLP, in CUDALM's rounding order.
+__device__ __forceinline__ std::uint16_t silu_mul_bits(float g, std::uint16_t up_bits) {
+  const float s = bf16_bits_to_float(float_to_bf16_bits(__fdiv_rn(g, 1.0f + expf(-g))));
+  return float_to_bf16_bits(s * bf16_bits_to_float(up_bits));
+}
+__device__ __forceinline__ std::uint16_t add_bits(std::uint16_t a, std::uint16_t b) {
+  return float_to_bf16_bits(bf16_bits_to_float(a) + bf16_bits_to_float(b));
+}
+
 // ---------------------------------------------------------------------------
 // Streaming kernel.  CTA_MAX additionally records, per CTA and activation row,
 // the largest bf16-rounded output the CTA produced (used by the vocabulary
@@ -650,7 +693,9 @@ __device__ __forceinline__ bool wait_x_ready(const DescSource& ds, CtaControl* c
 // consumer warps only compute; NPROD further warps issue the copies, one thread
 // each for four consumers, as soon as a consumer hands a stage back through its
 // "empty" mbarrier (issuing a chunk's copies costs a warp several hundred cycles).
-template <int NT, int CG, int NWARPS, bool CTA_MAX, int NPROD>
+// EXTRA: the launch may hold a pair (silu(gate) * up) or a projection with a
+// residual; plain launches are compiled without any of that.
+template <int NT, int CG, int NWARPS, bool CTA_MAX, int NPROD, bool EXTRA>
 __global__ void __launch_bounds__((NWARPS + NPROD) * 32, 1)
 w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
   extern __shared__ __align__(128) std::uint8_t smem[];
@@ -711,10 +756,11 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
     // descriptors are written when a launch is set up, never by a kernel, so
     // they may be read before the wait on the previous grid
     const int d = d_first + tid;
-    DescLite v{nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0x7fffffff, 0, 0};
+    DescLite v{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0x7fffffff, 0, 0};
     if (d < p.n_desc) {
       const LinearDev* L = desc_table(p) + d;
-      v = DescLite{&L->tmap, L->S, L->x, L->y, L->N, L->K, L->M, L->mt_begin, L->flags, 0};
+      v = DescLite{&L->tmap, &L->tmap2, L->S, L->S2, L->res, L->x, L->y,
+                   L->N,     L->K,      L->M, L->mt_begin, L->flags, 0};
     }
     ctl->desc[tid] = v;
   }
@@ -756,13 +802,13 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
         std::uint64_t* eb = all_empty + (w0 + c) * kMaxDepth + pslot[c];
         if (!mbar_try_wait(eb, pphase[c])) continue;
         std::uint8_t* st = rings + (static_cast<std::size_t>(w0 + c) * depth + pslot[c]) * p.stage_bytes;
-        issue_item_single<CG>(pc[c], st, all_full + (w0 + c) * kMaxDepth + pslot[c], policy);
+        issue_item_single<CG, EXTRA>(pc[c], st, all_full + (w0 + c) * kMaxDepth + pslot[c], policy);
         st_volatile_s32(&ctl->issued[w0 + c], ++nissued[c]);
         if (++pslot[c] == depth) {
           pslot[c] = 0;
           pphase[c] ^= 1u;
         }
-        if (++pc[c].chunk >= pc[c].nch) {
+        if (++pc[c].chunk >= (EXTRA ? pc[c].nch_total : pc[c].nch)) {
           const int m = mt_lo + w0 + c + taken[c] * NWARPS;
           ++taken[c];
           pc[c].seek(ds, m < mt_hi ? m : mt_hi, mt_hi);
@@ -812,7 +858,7 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
     cc.seek(ds, m < mt_hi ? m : mt_hi, mt_hi);
   };
   auto fc_advance = [&]() {
-    if (++fc.chunk < fc.nch) return;
+    if (++fc.chunk < (EXTRA ? fc.nch_total : fc.nch)) return;
     fc_next_mtile();
   };
 
@@ -825,7 +871,7 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
     if (NPROD == 0) {
       fc_next_mtile();
       for (int s = 0; s < depth && fc.valid; ++s) {
-        issue_item<CG>(fc, ring + s * p.stage_bytes, &bars[s], lane, policy);
+        issue_item<CG, EXTRA>(fc, ring + s * p.stage_bytes, &bars[s], lane, policy);
         fc_advance();
         ++in_flight;
       }
@@ -891,8 +937,22 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
       const int row0 = (cc.mt - cc.mt_begin) * kMTileRows;
-      const int nch = cc.nch;
-      for (int ch = 0; ch < nch; ++ch) {
+      const int nch = cc.nch, nch_total = EXTRA ? cc.nch_total : cc.nch;
+      // a pair's first (gate) outputs, rounded to bf16, while the second matrix streams
+      constexpr int kGateTiles = (EXTRA && NT <= 2) ? NT : 1;
+      float gate[kGateTiles][4];
+      for (int chunk = 0; chunk < nch_total; ++chunk) {
+        if (EXTRA) cc.chunk = chunk;
+        const int ch = (EXTRA && chunk >= nch) ? chunk - nch : chunk;
+        if (EXTRA && NT <= 2 && chunk == nch) {
+#pragma unroll
+          for (int nt = 0; nt < kGateTiles; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              gate[nt][i] = bf16_bits_to_float(float_to_bf16_bits(acc[nt][i] * CB200_OUT_SCALE));
+              acc[nt][i] = 0.f;
+            }
+        }
         std::uint8_t* stage = ring + slot * p.stage_bytes;
         if (!dead && !wait_stage(&bars[slot], parity)) {
           dead = true;
@@ -903,11 +963,11 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
         }
         if (!dead) {
           const int g0 = ch * CG;
-          if (NPROD > 0 && !stage_scales_bulk<CG>(cc)) {
+          if (NPROD > 0 && !stage_scales_bulk<CG, EXTRA>(cc)) {
             // a ragged or unaligned scale block, which the producer leaves to the reader
             const int srow0 = (cc.mt - cc.mt_begin) * kMTileRows;
             const int n_sc = min(kMTileRows, cc.N - srow0) * cc.G;
-            const std::uint16_t* ssrc = cc.S + static_cast<std::size_t>(srow0) * cc.G;
+            const std::uint16_t* ssrc = (EXTRA ? cc.cur_scales() : cc.S) + static_cast<std::size_t>(srow0) * cc.G;
             std::uint16_t* sdst = reinterpret_cast<std::uint16_t*>(stage + kMTileRows * CG * 64);
             for (int i = lane; i < n_sc; i += 32) sdst[i] = __ldg(ssrc + i);
             __syncwarp();
@@ -920,7 +980,7 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
           } else {
             --in_flight;
             if (fc.valid) {
-              issue_item<CG>(fc, stage, &bars[slot], lane, policy);
+              issue_item<CG, EXTRA>(fc, stage, &bars[slot], lane, policy);
               fc_advance();
               ++in_flight;
             }
@@ -941,10 +1001,30 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
           const int col = nt * 8 + 2 * t;
-          const std::uint16_t o0 = float_to_bf16_bits(acc[nt][0] * CB200_OUT_SCALE);
-          const std::uint16_t o1 = float_to_bf16_bits(acc[nt][1] * CB200_OUT_SCALE);
-          const std::uint16_t o2 = float_to_bf16_bits(acc[nt][2] * CB200_OUT_SCALE);
-          const std::uint16_t o3 = float_to_bf16_bits(acc[nt][3] * CB200_OUT_SCALE);
+          std::uint16_t o0 = float_to_bf16_bits(acc[nt][0] * CB200_OUT_SCALE);
+          std::uint16_t o1 = float_to_bf16_bits(acc[nt][1] * CB200_OUT_SCALE);
+          std::uint16_t o2 = float_to_bf16_bits(acc[nt][2] * CB200_OUT_SCALE);
+          std::uint16_t o3 = float_to_bf16_bits(acc[nt][3] * CB200_OUT_SCALE);
+          if (EXTRA && NT <= 2 && (L.flags & kFlagPair)) {
+            // CUDALM's rounding order (src/kernels/qwen35_kernels.cu:459-476):
+            // s = bf16(g / (1 + exp(-g))), then bf16(float(s) * float(u))
+            const int gi = nt < kGateTiles ? nt : 0;
+            o0 = silu_mul_bits(gate[gi][0], o0);
+            o1 = silu_mul_bits(gate[gi][1], o1);
+            o2 = silu_mul_bits(gate[gi][2], o2);
+            o3 = silu_mul_bits(gate[gi][3], o3);
+          } else if (EXTRA && (L.flags & kFlagResidual)) {
+            // bf16(float(residual) + float(projection)) (src/kernels/qwen35_kernels.cu:442-456)
+            const std::uint16_t* res = L.res;
+            if (col < LM) {
+              if (row_lo < LN) o0 = add_bits(res[static_cast<std::size_t>(col) * LN + row_lo], o0);
+              if (row_hi < LN) o2 = add_bits(res[static_cast<std::size_t>(col) * LN + row_hi], o2);
+            }
+            if (col + 1 < LM) {
+              if (row_lo < LN) o1 = add_bits(res[static_cast<std::size_t>(col + 1) * LN + row_lo], o1);
+              if (row_hi < LN) o3 = add_bits(res[static_cast<std::size_t>(col + 1) * LN + row_hi], o3);
+            }
+          }
           if (col < LM) {
             if (row_lo < LN) y[static_cast<std::size_t>(col) * LN + row_lo] = o0;
             if (row_hi < LN) y[static_cast<std::size_t>(col) * LN + row_hi] = o2;

@@ -129,6 +129,28 @@ CUDALM_B200_API int cudalm_b200_gate_up_bf16(const uint8_t* gate_weight,
                              const uint16_t* x, uint16_t* gate_y, uint16_t* up_y,
                              int N, int K, int M, void* stream);
 
+/* ---- MLP epilogues fused into the projection ----------------------------------
+ * gate_up_silu: out[m][n] = bf16(float(bf16(silu(g))) * float(u)) with g, u the
+ * bf16 outputs of the gate and up projections of x [M, K]; replaces the two
+ * projections and qwen35_silu_mul (CUDALM include/cudalm/kernels/qwen35_kernels.h:137-155,
+ * src/kernels/qwen35_kernels.cu:459-476; call sites src/runtime/qwen35_deltanet.cpp:236-247,
+ * src/runtime/qwen35_full_attention.cpp:317-331) with one launch per 16 rows.
+ * linear_residual: y[m][n] = bf16(float(residual[m][n]) + float(p)) with p the bf16
+ * output of the projection; replaces the down / o_proj / out_proj projection and the
+ * qwen35_add that follows it (src/kernels/qwen35_kernels.cu:442-456;
+ * src/runtime/qwen35_deltanet.cpp:248-252).  y may alias residual.
+ * The intermediate values are rounded exactly where CUDALM rounds them, so the
+ * results equal the unfused sequence on this library's own projections bit for bit. */
+CUDALM_B200_API int cudalm_b200_gate_up_silu_bf16(const uint8_t* gate_weight,
+                             const uint16_t* gate_scales,
+                             const uint8_t* up_weight, const uint16_t* up_scales,
+                             const uint16_t* x, uint16_t* out,
+                             int N, int K, int M, void* stream);
+CUDALM_B200_API int cudalm_b200_linear_residual_bf16(const uint8_t* weight,
+                             const uint16_t* scales, const uint16_t* x,
+                             const uint16_t* residual, uint16_t* y,
+                             int N, int K, int M, void* stream);
+
 /* ---- vocabulary projection with on-device token pick --------------------------
  * Replaces the lm_head call cudalm::bf16_gemv / kernels::batch_bf16_gemv
  * (CUDALM include/cudalm/kernels/bf16_gemv.h:39-40,

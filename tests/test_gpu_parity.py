@@ -10,7 +10,8 @@ lm_head argmax identical.  Shapes follow the reference's kernel tests
 import numpy as np
 import pytest
 
-from helpers import (BASE_SEED, check_close, from_dev, make_weights, make_x, raw_weights, to_dev)
+from helpers import (BASE_SEED, _ordinal, check_close, from_dev, make_weights, make_x, raw_weights,
+                     to_dev)
 
 pytestmark = pytest.mark.gpu
 
@@ -448,3 +449,94 @@ def test_group_on_tensor_memory_path(eng, orc):
     for i, ((lin, _, y), want) in enumerate(zip(items, refs)):
         check_close(orc, from_dev(y), want, f"tc group item {i} {lin.N}x{lin.K}")
     grp.close()
+
+
+# --- MLP epilogues fused into the projection ---------------------------------------
+
+def _ulp_neighbours(a, b):
+    return np.abs(_ordinal(a) - _ordinal(b))
+
+
+@pytest.mark.parametrize("N,K,M", [(3584, 1024, 1), (3584, 1024, 8), (1000, 1024, 3), (520, 384, 16),
+                                   (3584, 1024, 40), (100, 256, 2)])
+def test_gate_up_silu_matches_unfused_sequence(eng, orc, N, K, M):
+    # fused = the reference's sequence (two projections, then silu_mul with its
+    # rounding order) applied to this library's own projection outputs
+    import torch
+    Wg, Sg = raw_weights(N, K, 900 + N)
+    Wu, Su = raw_weights(N, K, 901 + N + M)
+    x = make_x(orc, (M, K), 902 + K, "outlier")
+    gate = eng.W4A16Linear(to_dev(Wg), to_dev(Sg, torch.float16))
+    up = eng.W4A16Linear(to_dev(Wu), to_dev(Su, torch.float16))
+    xd = to_dev(x, torch.bfloat16)
+    # the fused entry runs on the streaming kernel: take the unfused outputs from it too
+    prev = eng.set_tensor_path_min_rows(1 << 30)
+    try:
+        g_y, u_y = eng.gate_up_bf16(gate, up, xd)
+    finally:
+        eng.set_tensor_path_min_rows(prev)
+    fused = from_dev(eng.gate_up_silu_bf16(gate, up, xd))
+    want = orc.silu_mul_bf16(from_dev(g_y), from_dev(u_y))
+    d = _ulp_neighbours(fused, want)
+    # device expf and the host's may differ in the last bit before the bf16 round
+    assert d.max() <= 1 and (d != 0).mean() <= 2e-3, (d.max(), (d != 0).mean())
+    # and against the CPU reference end to end
+    ref = orc.silu_mul_bf16(orc.batch_gemv_bf16(Wg, Sg, x, threads=8),
+                            orc.batch_gemv_bf16(Wu, Su, x, threads=8))
+    # a projection output may be the neighbouring bf16 value (see check_close), so the
+    # product may be up to two bf16 steps away; anything else must be within 1e-2 * RMS
+    a, r = orc.bf16_bits_to_f32(fused), orc.bf16_bits_to_f32(ref)
+    ok = (_ulp_neighbours(fused, ref) <= 2) | (np.abs(a - r) <= 1e-2 * np.sqrt(np.mean(r * r)))
+    assert ok.all(), f"gate_up_silu {N}x{K} M={M}: {np.count_nonzero(~ok)} elements off"
+    assert (fused != ref).mean() <= 2e-2
+
+
+@pytest.mark.parametrize("N,K,M", [(1024, 3584, 1), (1024, 3584, 8), (1024, 2048, 16), (300, 1024, 5),
+                                   (1024, 3584, 24)])
+def test_linear_residual_matches_unfused_sequence(eng, orc, N, K, M):
+    import torch
+    W, S = raw_weights(N, K, 950 + N)
+    x = make_x(orc, (M, K), 951 + K, "outlier")
+    res = make_x(orc, (M, N), 952 + N)
+    lin = eng.W4A16Linear(to_dev(W), to_dev(S, torch.float16))
+    xd, rd = to_dev(x, torch.bfloat16), to_dev(res, torch.bfloat16)
+    y = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    prev = eng.set_tensor_path_min_rows(1 << 30)
+    try:
+        eng.batch_int4_gemv_bf16(lin.weight, lin.scale, xd, y)
+    finally:
+        eng.set_tensor_path_min_rows(prev)
+    want = orc.add_bf16(res, from_dev(y))
+    fused = from_dev(eng.linear_residual_bf16(lin, xd, rd))
+    assert np.array_equal(fused, want)
+    # in place: y aliases the residual
+    eng.linear_residual_bf16(lin, xd, rd, y=rd)
+    assert np.array_equal(from_dev(rd), want)
+
+
+def test_fused_epilogues_on_the_slow_kernel(eng, orc):
+    # a weight base off 16 bytes takes the one-warp-per-row kernel
+    import torch
+    N, K, M = 96, 256, 3
+    Wg, Sg = raw_weights(N, K, 970)
+    Wu, Su = raw_weights(N, K, 971)
+    x = make_x(orc, (M, K), 972)
+    res = make_x(orc, (M, N), 973)
+
+    def off_by_one(a):
+        buf = torch.empty(a.size + 1, dtype=torch.uint8, device="cuda")
+        view = buf[1:].view(a.shape)
+        view.copy_(to_dev(a))
+        return view
+
+    gate = eng.W4A16Linear(off_by_one(Wg), to_dev(Sg, torch.float16))
+    up = eng.W4A16Linear(off_by_one(Wu), to_dev(Su, torch.float16))
+    xd = to_dev(x, torch.bfloat16)
+    g_y, u_y = eng.gate_up_bf16(gate, up, xd)
+    fused = from_dev(eng.gate_up_silu_bf16(gate, up, xd))
+    d = _ulp_neighbours(fused, orc.silu_mul_bf16(from_dev(g_y), from_dev(u_y)))
+    assert d.max() <= 1
+    y = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    eng.batch_int4_gemv_bf16(gate.weight, gate.scale, xd, y)
+    got = from_dev(eng.linear_residual_bf16(gate, xd, to_dev(res, torch.bfloat16)))
+    assert np.array_equal(got, orc.add_bf16(res, from_dev(y)))
