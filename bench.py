@@ -362,6 +362,50 @@ def bench_cohorts(eng, torch, steps, warmup, rows=(8, 16, 32, 64)):
     return out
 
 
+def bench_mlp(eng, torch, steps, warmup):
+    """One layer's MLP at M = 1 and 8: the reference's five launches
+    (gate, up, silu_mul, down, add) as this library's two fused ones, against the same
+    work through the unfused entry points plus torch elementwise kernels."""
+    gen = torch.Generator(device="cuda").manual_seed(SEED + 5)
+    layers = []
+    for _ in range(24):
+        ws = []
+        for N, K in ((3584, 1024), (3584, 1024), (1024, 3584)):
+            w = (torch.randn((N, K), generator=gen, device="cuda", dtype=torch.float32) * 0.02
+                 ).to(torch.bfloat16)
+            ws.append(eng.W4A16Linear(*eng.quantize_w4a16(w)))
+        layers.append(ws)
+    out = {}
+    for M in (1, 8):
+        x = torch.randn((M, 1024), generator=gen, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+        act = torch.empty((M, 3584), device="cuda", dtype=torch.bfloat16)
+        gy, uy = torch.empty_like(act), torch.empty_like(act)
+        h = torch.zeros((M, 1024), device="cuda", dtype=torch.bfloat16)
+        dy = torch.empty_like(h)
+
+        def fused(i):
+            for g, u, d in layers:
+                eng.gate_up_silu_bf16(g, u, x, out=act)
+                eng.linear_residual_bf16(d, act, h, y=h)
+
+        def unfused(i):
+            for g, u, d in layers:
+                eng.gate_up_bf16(g, u, x, gy, uy)
+                torch.mul(torch.nn.functional.silu(gy), uy, out=act)
+                eng.batch_int4_gemv_bf16(d.weight, d.scale, act, dy)
+                h.add_(dy)
+
+        res = {}
+        for name, fn in (("fused", fused), ("unfused", unfused)):
+            total_ms, _ = time_steps(torch, fn, steps, warmup)
+            res[name + "_us_per_layer"] = total_ms * 1e3 / steps / 24
+        nbytes = sum(g.bytes(M) + u.bytes(M) + d.bytes(M) for g, u, d in layers) / 24
+        res["fused_gbps"] = nbytes / (res["fused_us_per_layer"] * 1e-6) / 1e9
+        res["launches_per_layer"] = {"fused": 2, "unfused": 5}
+        out[f"M{M}"] = res
+    return out
+
+
 def bench_quantize(eng, torch, steps, warmup):
     """GPU quantize+pack (BASELINE configs[4]): GB/s of bf16 input consumed."""
     gen = torch.Generator(device="cuda").manual_seed(SEED + 4)
@@ -397,6 +441,10 @@ def run_ours(args):
         out = bench_cohorts(eng, torch, max(2, min(args.steps, 20)), max(1, min(args.warmup, 3)),
                             rows=(args.rows,))
         print(json.dumps({"batched_decode": out}), flush=True)
+        return
+    if args.only == "mlp":
+        print(json.dumps({"mlp": bench_mlp(eng, torch, max(2, min(args.steps, 20)),
+                                           max(1, min(args.warmup, 3)))}), flush=True)
         return
     if args.only == "quantize":
         print(json.dumps({"quantize": bench_quantize(eng, torch, max(2, min(args.steps, 20)),
@@ -469,10 +517,11 @@ def run_ours(args):
     lm = {} if args.only == "set" else bench_lm_head(eng, torch, dist, rank, world,
                                                       max(5, min(args.steps, 50)), 3)
 
-    cohorts, quant = {}, {}
+    cohorts, quant, mlp = {}, {}, {}
     if args.only == "all" and rank == 0:
         cohorts = bench_cohorts(eng, torch, max(5, min(args.steps, 20)), 3)
         quant = bench_quantize(eng, torch, max(5, min(args.steps, 20)), 3)
+        mlp = bench_mlp(eng, torch, max(5, min(args.steps, 20)), 3)
     if dist is not None:
         dist.barrier()
 
@@ -509,6 +558,7 @@ def run_ours(args):
         "batched_decode": {"what": "24 layers x (fused gate+up 1024->2x3584, down 3584->1024), "
                                    "bf16 activations with 1% x20 outliers", **cohorts},
         "quantize": quant,
+        "mlp": mlp,
         "lm_head": {"vocab": VOCAB, "K": HIDDEN, "top_k": TOP_K, "n_gpus": world,
                     "scaling": "strong (vocabulary rows split over ranks, one all-gather of "
                                "candidates)" if world > 1 else "single GPU", **lm},
@@ -527,7 +577,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default="all", choices=["all", "set", "lm_head", "batched", "quantize"],
+    ap.add_argument("--only", default="all", choices=["all", "set", "lm_head", "batched", "quantize", "mlp"],
                     help="profiling aid: run only the projection set, the lm_head, batched decode "
                          "or the quantizer")
     ap.add_argument("--rows", type=int, default=64, help="with --only batched: activation rows M")

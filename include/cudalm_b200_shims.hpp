@@ -69,6 +69,35 @@ inline void gate_up_int4_gemv_bf16(const std::uint8_t* gate_weight, const __half
       "gate_up_int4_gemv_bf16");
 }
 
+// The MLP's gate and up projections with silu(gate) * up applied in the same
+// launch; replaces the two projections and qwen35_silu_mul
+// (include/cudalm/kernels/qwen35_kernels.h:137-155) at
+// src/runtime/qwen35_deltanet.cpp:236-247 and its batched form.
+inline void gate_up_silu_int4_gemv_bf16(const std::uint8_t* gate_weight, const __half* gate_scale,
+                                        const std::uint8_t* up_weight, const __half* up_scale,
+                                        const __nv_bfloat16* x, __nv_bfloat16* act, int N, int K,
+                                        int B, cudaStream_t stream) {
+  b200_detail::check(
+      cudalm_b200_gate_up_silu_bf16(gate_weight, b200_detail::u16(gate_scale), up_weight,
+                                    b200_detail::u16(up_scale), b200_detail::u16(x),
+                                    b200_detail::u16(act), N, K, B, stream),
+      "gate_up_silu_int4_gemv_bf16");
+}
+
+// A projection followed by the residual add (qwen35_add,
+// include/cudalm/kernels/qwen35_kernels.h:137-145) in one launch; `y` may be
+// `residual`.  Replaces src/runtime/qwen35_deltanet.cpp:248-252 and the o_proj /
+// out_proj call sites followed by an add.
+inline void int4_gemv_residual_bf16(const std::uint8_t* weight, const __half* scale,
+                                    const __nv_bfloat16* x, const __nv_bfloat16* residual,
+                                    __nv_bfloat16* y, int N, int K, int B, cudaStream_t stream) {
+  b200_detail::check(
+      cudalm_b200_linear_residual_bf16(weight, b200_detail::u16(scale), b200_detail::u16(x),
+                                       b200_detail::u16(residual), b200_detail::u16(y), N, K, B,
+                                       stream),
+      "int4_gemv_residual_bf16");
+}
+
 // lm_head stored as W4A16 with the token pick on the device; replaces
 // batch_bf16_gemv (include/cudalm/kernels/batch_decode.h:77-79) followed by the
 // host pick (src/runtime/scheduler.cpp:91-108).  `logits` may be null.
