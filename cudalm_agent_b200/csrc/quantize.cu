@@ -25,6 +25,43 @@ __device__ __forceinline__ float quant_round(float w, float s, float inv_s) {
   return r;
 }
 
+// Inserts the low four bits of `v` into `word` at bit position `pos`.
+__device__ __forceinline__ std::uint32_t insert_nibble(std::uint32_t word, std::uint32_t v, int pos) {
+  std::uint32_t r;
+  asm("bfi.b32 %0, %1, %2, %3, 4;" : "=r"(r) : "r"(v), "r"(word), "r"(pos));
+  return r;
+}
+
+// One group's share of a lane: eight values in, one packed word out.
+__device__ __forceinline__ std::uint32_t quantize_eight(const uint4& v, unsigned mask, float* scale_out) {
+  const std::uint32_t words[4] = {v.x, v.y, v.z, v.w};
+  float w[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    w[2 * i] = __uint_as_float(words[i] << 16);
+    w[2 * i + 1] = __uint_as_float(words[i] & 0xFFFF0000u);
+  }
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(w[i]));
+#pragma unroll
+  for (int off = 8; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(mask, amax, off));
+  const float scale32 = __fdiv_rn(amax, 7.0f);
+  *scale_out = scale32;
+  if (scale32 == 0.f) return 0u;  // the whole group (all 16 lanes see the same scale)
+  const float inv = __frcp_rn(scale32);
+  std::uint32_t out = 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    float q = quant_round(w[i], scale32, inv);
+    q = fminf(fmaxf(q, -7.f), 7.f);
+    // q is an integer in [-7, 7]: adding 1.5 * 2^23 leaves it, in two's
+    // complement, in the low mantissa bits
+    out = insert_nibble(out, __float_as_uint(q + 12582912.0f), 4 * i);
+  }
+  return out;
+}
+
 __global__ void __launch_bounds__(256)
 quantize_w4a16_kernel(const uint4* __restrict__ W, std::uint32_t* __restrict__ packed,
                       std::uint16_t* __restrict__ scales, long long n_groups) {
@@ -34,32 +71,24 @@ quantize_w4a16_kernel(const uint4* __restrict__ W, std::uint32_t* __restrict__ p
   // The 16 lanes of a half-warp share `grp`; the two halves of a warp may leave
   // the loop at different times, so the shuffles name only their own half.
   const unsigned mask = (threadIdx.x & 16) ? 0xFFFF0000u : 0x0000FFFFu;
+  // four groups per trip so that four loads are in flight per lane
+  for (; grp + 3 * half_warps < n_groups; grp += 4 * half_warps) {
+    uint4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) v[u] = __ldg(W + (grp + u * half_warps) * 16 + lane16);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      float scale32;
+      const std::uint32_t out = quantize_eight(v[u], mask, &scale32);
+      const long long g = grp + u * half_warps;
+      packed[g * 16 + lane16] = out;
+      if (lane16 == 0) scales[g] = __half_as_ushort(__float2half_rn(scale32));
+    }
+  }
   for (; grp < n_groups; grp += half_warps) {
     const uint4 v = __ldg(W + grp * 16 + lane16);
-    const std::uint32_t words[4] = {v.x, v.y, v.z, v.w};
-    float w[8];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      w[2 * i] = __uint_as_float(words[i] << 16);
-      w[2 * i + 1] = __uint_as_float(words[i] & 0xFFFF0000u);
-    }
-    float amax = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(w[i]));
-#pragma unroll
-    for (int off = 8; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(mask, amax, off));
-    const float scale32 = __fdiv_rn(amax, 7.0f);
-    const bool zero = (scale32 == 0.f);
-    const float safe = zero ? 1.0f : scale32;
-    const float inv = __frcp_rn(safe);
-    std::uint32_t out = 0;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      float q = quant_round(w[i], safe, inv);
-      q = fminf(fmaxf(q, -7.f), 7.f);
-      const int qi = zero ? 0 : static_cast<int>(q);
-      out |= static_cast<std::uint32_t>(qi & 0xF) << (4 * i);
-    }
+    float scale32;
+    const std::uint32_t out = quantize_eight(v, mask, &scale32);
     packed[grp * 16 + lane16] = out;
     if (lane16 == 0) scales[grp] = __half_as_ushort(__float2half_rn(scale32));
   }
@@ -75,9 +104,11 @@ extern "C" int cudalm_b200_quantize_w4a16(const uint16_t* w_bf16, int N, int K, 
   if (!aligned_to(w_bf16, 16) || !aligned_to(packed, 4)) return CUDALM_B200_ERR_MISALIGNED;
   const long long n_groups = static_cast<long long>(N) * (K / 128);
   const int threads = 256;
-  long long blocks = (n_groups * 16 + threads - 1) / threads;
+  // a half-warp takes four groups per trip: size the grid so that it has them
+  long long blocks = (((n_groups + 3) / 4) * 16 + threads - 1) / threads;
   const long long cap = static_cast<long long>(num_sms()) * 8;
   if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
   quantize_w4a16_kernel<<<static_cast<int>(blocks), threads, 0, static_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const uint4*>(w_bf16), reinterpret_cast<std::uint32_t*>(packed), scales,
       n_groups);
