@@ -91,6 +91,10 @@ lm_head_collect_kernel(const std::uint16_t* __restrict__ logits, int N, int rows
                        int* __restrict__ counts, std::uint64_t* __restrict__ cand) {
   __shared__ float smax[kMaxCtas];
   __shared__ float bound;
+  // launched with programmatic stream serialisation: the grid may start while
+  // its predecessor drains, and must wait for it before reading its results
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int m = blockIdx.y;
   const int tid = threadIdx.x;
   for (int i = tid; i < ncta; i += blockDim.x) smax[i] = cta_max[static_cast<size_t>(i) * rows + m];
@@ -189,6 +193,8 @@ lm_head_select_kernel(const SelectArgs a) {
   __shared__ std::uint64_t buf[kCandCap];
   __shared__ int scratch[kSelectThreads / 32];
   __shared__ int s_take;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int m = blockIdx.x;
   const int tid = threadIdx.x;
   int n = 0;
@@ -287,6 +293,33 @@ __global__ void zero_counts_kernel(int* counts, int n) {
 
 using namespace cb200;
 
+namespace cb200 {
+namespace {
+// Launch that may overlap its predecessor's tail (the kernel waits with
+// griddepcontrol.wait before it reads anything).
+template <typename... KArgs, typename... Args>
+int launch_after(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t le = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+  if (le != cudaSuccess) {
+    g_last_cuda_error = static_cast<int>(le);
+    (void)cudaGetLastError();
+    return CUDALM_B200_ERR_CUDA;
+  }
+  return check_launch();
+}
+}  // namespace
+}  // namespace cb200
+
 extern "C" {
 
 size_t cudalm_b200_lm_head_workspace_bytes(int N, int K, int M, int top_k, int need_logits) {
@@ -343,9 +376,11 @@ int cudalm_b200_lm_head_topk(const uint8_t* weight, const uint16_t* scales, cons
     const int cap = num_sms() * 8 / rows > 1 ? num_sms() * 8 / rows : 1;
     if (slices > cap) slices = cap;
     if (slices < 1) slices = 1;
-    lm_head_collect_kernel<<<dim3(slices, rows), 256, 0, st>>>(logits, N, rows, ws.cta_max, ncta,
-                                                               top_k, id_offset, ws.counts, ws.cand);
-    if (int rc = check_launch()) return rc;
+    if (int rc = launch_after(lm_head_collect_kernel, dim3(slices, rows), dim3(256), st,
+                              static_cast<const std::uint16_t*>(logits), N, rows,
+                              static_cast<const float*>(ws.cta_max), ncta, top_k, id_offset, ws.counts,
+                              ws.cand))
+      return rc;
 
     SelectArgs a;
     std::memset(&a, 0, sizeof(a));
@@ -359,8 +394,7 @@ int cudalm_b200_lm_head_topk(const uint8_t* weight, const uint16_t* scales, cons
     a.argmax_out = argmax_out ? argmax_out + m0 : nullptr;
     a.topk_idx = topk_idx + static_cast<size_t>(m0) * top_k;
     a.topk_val = topk_val + static_cast<size_t>(m0) * top_k;
-    lm_head_select_kernel<<<rows, kSelectThreads, 0, st>>>(a);
-    if (int rc = check_launch()) return rc;
+    if (int rc = launch_after(lm_head_select_kernel, dim3(rows), dim3(kSelectThreads), st, a)) return rc;
   }
   return CUDALM_B200_OK;
 }

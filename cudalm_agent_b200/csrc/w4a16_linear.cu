@@ -15,6 +15,8 @@ namespace cb200 {
 // tensor-memory path for batched rows (w4a16_tc.cu)
 bool tc_eligible(const cudalm_b200_linear& l);
 int run_tc(const cudalm_b200_linear* ls, int count, cudaStream_t stream);
+int run_tc_with_cta_max(const cudalm_b200_linear& l, float* cta_max, int* grid_out,
+                        cudaStream_t stream);
 struct TcGroup;
 int tc_group_create(const cudalm_b200_linear* ls, int count, TcGroup** out);
 int tc_group_run(const TcGroup* g, cudaStream_t stream);
@@ -439,6 +441,8 @@ int run_extra(cudalm_b200_linear l, const LinearExtra& ex, cudaStream_t stream) 
 int run_linear_with_cta_max(const cudalm_b200_linear& l, float* cta_max, int* grid_out,
                             cudaStream_t stream) {
   if (int rc = validate(l)) return rc;
+  if (l.M >= g_tc_min_rows.load(std::memory_order_relaxed) && tc_eligible(l))
+    return run_tc_with_cta_max(l, cta_max, grid_out, stream);
   if (!stream_eligible(l)) return CUDALM_B200_ERR_UNSUPPORTED;
   if (max_rows_per_pass(l.K) < l.M) return CUDALM_B200_ERR_UNSUPPORTED;
   StreamParams p;

@@ -82,6 +82,10 @@ struct TcParams {
   int total_items;
   int total_cost;
   int* status;
+  // Optional (vocabulary projection, one projection per launch): per CTA and
+  // activation row the largest bf16-rounded output the CTA produced,
+  // cta_max[blockIdx.x * M + m].
+  float* cta_max;
 };
 
 // ---------------------------------------------------------------------------
@@ -267,8 +271,18 @@ struct TcSmem {
   std::uint64_t out_full[kTcTiles];  // every row thread has written the tile's output buffer
   std::uint32_t tmem_base;
   int abort_flag;
+  std::uint32_t row_max[64];  // per activation row: order-preserving key of the CTA's maximum
 };
 constexpr int kTcHeaderBytes = 1024;
+
+// Order-preserving map float -> uint32 (and back) so that integer max gives the float max.
+__device__ __forceinline__ std::uint32_t float_key(float f) {
+  const std::uint32_t b = __float_as_uint(f);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float key_float(std::uint32_t k) {
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7FFFFFFFu) : ~k);
+}
 static_assert(sizeof(TcSmem) <= kTcHeaderBytes, "barrier block too large");
 
 // Walks the items of a CTA's range, keeping track of the projection they belong to.
@@ -335,6 +349,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
     sm->abort_flag = 0;
     mbar_init_fence();
   }
+  if (tid < 64) sm->row_max[tid] = float_key(-INFINITY);
   if (warp == 0) tmem_alloc(&sm->tmem_base, 512);
   tc_fence_before();
   __syncthreads();
@@ -565,6 +580,15 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
         mbar_arrive(&sm->d_free[tile][buf]);
       }
       if (!alive) break;
+      if (p.cta_max != nullptr) {
+        // one warp-wide integer max per activation row, then one shared-memory atomic
+#pragma unroll
+        for (int n = 0; n < NTOK; ++n) {
+          const float v = row_ok ? bf16_bits_to_float(float_to_bf16_bits(acc[n])) : -INFINITY;
+          const std::uint32_t k = __reduce_max_sync(0xffffffffu, float_key(v));
+          if (lane == 0 && n < LM) atomicMax(&sm->row_max[n], k);
+        }
+      }
       if (direct) {
         // outputs the TMA unit cannot address: plain stores, one row per thread
         if (row_ok) {
@@ -608,6 +632,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
   }
 
   __syncthreads();
+  if (p.cta_max != nullptr && tid < tbl[0].M)
+    p.cta_max[static_cast<std::size_t>(blockIdx.x) * tbl[0].M + tid] = key_float(sm->row_max[tid]);
   if (*abort_flag && tid == 0) atomicExch(p.status, CUDALM_B200_ERR_TIMEOUT);
   tc_fence_after();
   if (warp == 0) tmem_dealloc(tmem_base, 512);
@@ -696,7 +722,7 @@ int tc_encode(const void* base, int inner, int outer, int box_inner, int box_out
 int tc_ntok(int M) { return M <= 16 ? 16 : (M <= 32 ? 32 : 64); }
 
 template <int NTOK>
-int tc_launch(const TcParams& p_in, cudaStream_t stream) {
+int tc_launch(const TcParams& p_in, cudaStream_t stream, int* grid_out = nullptr) {
   auto kern = w4a16_tc_kernel<NTOK>;
   constexpr int kFixed = 1024 + kTcHeaderBytes + kTcTiles * tc_out_bytes(NTOK);
   int n_stages = (kMaxSmemBytes - kFixed) / tc_stage_bytes(NTOK);
@@ -721,6 +747,7 @@ int tc_launch(const TcParams& p_in, cudaStream_t stream) {
   }
   int grid = num_sms();
   if (grid > p.total_items) grid = p.total_items;
+  if (grid_out) *grid_out = grid;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(grid));
   cfg.blockDim = dim3(kTcThreads);
@@ -785,12 +812,24 @@ int tc_describe(const cudalm_b200_linear* ls, int count, TcDesc* out, int* items
   return CUDALM_B200_OK;
 }
 
-int tc_run_params(TcParams& p, int ntok, cudaStream_t stream) {
+int tc_run_params(TcParams& p, int ntok, cudaStream_t stream, int* grid_out = nullptr) {
   p.status = device_status_word();
   if (!p.status) return CUDALM_B200_ERR_CUDA;
-  if (ntok == 16) return tc_launch<16>(p, stream);
-  if (ntok == 32) return tc_launch<32>(p, stream);
-  return tc_launch<64>(p, stream);
+  if (ntok == 16) return tc_launch<16>(p, stream, grid_out);
+  if (ntok == 32) return tc_launch<32>(p, stream, grid_out);
+  return tc_launch<64>(p, stream, grid_out);
+}
+
+// One projection that also records the per-CTA maxima (vocabulary projection).
+int run_tc_with_cta_max(const cudalm_b200_linear& l, float* cta_max, int* grid_out,
+                        cudaStream_t stream) {
+  TcParams p;
+  std::memset(&p, 0, sizeof(p));
+  int ntok = 0;
+  if (int rc = tc_describe(&l, 1, p.inl, &p.total_items, &p.total_cost, &ntok)) return rc;
+  p.n_desc = 1;
+  p.cta_max = cta_max;
+  return tc_run_params(p, ntok, stream, grid_out);
 }
 
 // Up to CUDALM_B200_MAX_INLINE_LINEARS projections in one launch.
