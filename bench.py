@@ -205,7 +205,7 @@ def run_reference_arm(args):
 
 
 def workload_config(n_gpus: int, copies: int = 0):
-    return {"workload": "BASELINE configs[1]: full M=1 projection set of the 24-layer hybrid "
+    return {"workload": "configuration 1 of the benchmark plan: full M=1 projection set of the 24-layer hybrid "
                         "stack (132 projections: 1024->6144 x18, 2048->1024 x24, 1024->4096 x6, "
                         "1024->512 x12, 1024->3584 x48, 3584->1024 x24), G=128 int4 + fp16 scales",
             "bytes_per_step": set_bytes(), "M": 1,
@@ -315,7 +315,7 @@ def bench_lm_head(eng, torch, dist, rank, world, steps, warmup):
 
 
 def bench_cohorts(eng, torch, steps, warmup, rows=(8, 16, 32, 64)):
-    """Batched decode (BASELINE configs[2]): M = 8, 16, 32, 64 rows through the
+    """Batched decode (configuration 2 of the benchmark plan): M = 8, 16, 32, 64 rows through the
     MLP projections of 24 layers -- fused gate+up (K=1024 -> 2 x 3584) and down
     (K=3584 -> 1024), distinct weights per layer (137 MB of weights > L2)."""
     gen = torch.Generator(device="cuda").manual_seed(SEED + 2)
@@ -363,7 +363,7 @@ def bench_cohorts(eng, torch, steps, warmup, rows=(8, 16, 32, 64)):
 
 
 def bench_mlp(eng, torch, steps, warmup):
-    """One layer's MLP at M = 1 and 8: the reference's five launches
+    """One layer's MLP at M = 1 and 8 (the fused-epilogue row of the scope table): the reference's five launches
     (gate, up, silu_mul, down, add) as this library's two fused ones, against the same
     work through the unfused entry points plus torch elementwise kernels."""
     gen = torch.Generator(device="cuda").manual_seed(SEED + 5)
@@ -407,7 +407,7 @@ def bench_mlp(eng, torch, steps, warmup):
 
 
 def bench_quantize(eng, torch, steps, warmup):
-    """GPU quantize+pack (BASELINE configs[4]): GB/s of bf16 input consumed."""
+    """GPU quantize+pack (configuration 4 of the benchmark plan): GB/s of bf16 input consumed."""
     gen = torch.Generator(device="cuda").manual_seed(SEED + 4)
     out = {}
     for N, K in ((248320, 1024), (6144, 1024), (1024, 3584)):

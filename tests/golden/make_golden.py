@@ -2,7 +2,7 @@
 
 Run where the reference tree is mounted (it is not present on GPU boxes):
 
-    python tests/golden/make_golden.py [--ref /root/reference]
+    python tests/golden/make_golden.py [--ref <reference tree>]
 
 What is recorded, and which reference code produced it:
 

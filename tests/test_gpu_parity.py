@@ -323,7 +323,7 @@ def test_topk_merge_equals_host_merge(eng, orc):
 
 
 def test_lm_head_full_vocabulary_argmax(eng, orc):
-    # BASELINE configuration: K=1024 -> N=248320, M=1 and M=32, RMS-normalised x
+    # the benchmark's vocabulary configuration: K=1024 -> N=248320, M=1 and M=32, RMS-normalised x
     import torch
     N, K = 248320, 1024
     threads = orc.lib().orc_max_threads()
