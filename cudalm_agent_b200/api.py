@@ -66,6 +66,8 @@ SIGNATURES = {
     "cudalm_b200_group_destroy": (_ci, [_vp]),
     "cudalm_b200_group_bytes": (ctypes.c_int64, [_vp]),
     "cudalm_b200_gate_up_bf16": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _vp]),
+    "cudalm_b200_sample_topk": (_ci, [_vp, _vp, _ci, _ci, ctypes.c_float, _ci, ctypes.c_float, _vp,
+                                      _vp, _vp]),
     "cudalm_b200_gate_up_silu_bf16": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _vp]),
     "cudalm_b200_linear_residual_bf16": (_ci, [_vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _vp]),
     "cudalm_b200_lm_head_workspace_bytes": (ctypes.c_size_t, [_ci, _ci, _ci, _ci, _ci]),
@@ -249,6 +251,26 @@ def gate_up_bf16(gate: W4A16Linear, up: W4A16Linear, x: torch.Tensor,
         _ptr(gate_y), _ptr(up_y), gate.N, gate.K, M, _stream())
     _check("gate_up_bf16", st)
     return gate_y, up_y
+
+
+def sample_topk(topk_idx: torch.Tensor, topk_val: torch.Tensor, temperature: float, top_k: int,
+                top_p: float, rng_state: Optional[torch.Tensor] = None,
+                token_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """CUDALM's sample_token (include/cudalm/sampling.h:200-234) on the device, over
+    candidate lists [M, list_len] (value descending, tie -> lower id).  rng_state is an
+    int64 tensor [M] holding each row's SplitMix64 state; it is advanced in place."""
+    _need(topk_idx, torch.int32, "topk_idx")
+    _need(topk_val, torch.bfloat16, "topk_val")
+    M, list_len = int(topk_idx.shape[0]), int(topk_idx.shape[1])
+    if rng_state is not None:
+        _need(rng_state, torch.int64, "rng_state")
+    if token_out is None:
+        token_out = torch.empty((M,), dtype=torch.int32, device=topk_idx.device)
+    st = load_library().cudalm_b200_sample_topk(
+        _ptr(topk_idx), _ptr(topk_val), list_len, M, float(temperature), int(top_k), float(top_p),
+        _ptr(rng_state) if rng_state is not None else None, _ptr(token_out), _stream())
+    _check("sample_topk", st)
+    return token_out
 
 
 def gate_up_silu_bf16(gate: W4A16Linear, up: W4A16Linear, x: torch.Tensor,

@@ -220,6 +220,22 @@ CUDALM_B200_API int cudalm_b200_topk_merge_packed(const int32_t* gathered, int n
                                                   int32_t* topk_idx, uint16_t* topk_val,
                                                   void* stream);
 
+/* ---- token sampling over the candidate lists -----------------------------------
+ * CUDALM's sample_token (include/cudalm/sampling.h:131-234; called per row on the
+ * host after a 497 KB copy of the logits, src/runtime/scheduler.cpp:59-108) on the
+ * lists cudalm_b200_lm_head_topk / cudalm_b200_topk_merge return: topk_idx,
+ * topk_val [M, list_len] ordered by value descending, tie -> lower id.
+ * temperature <= 0: the greedy pick (entry 0), no draw, rng_state may be null.
+ * Otherwise 1 <= top_k <= list_len is required (UNSUPPORTED else: with top-k
+ * disabled every token of the vocabulary keeps a probability, which a list cannot
+ * answer), 0 < top_p <= 1, and rng_state [M] (device) holds each row's SplitMix64
+ * state, advanced by one draw.  token_out [M] receives global token ids.  Same
+ * arithmetic as the reference (double precision, its summation orders). */
+CUDALM_B200_API int cudalm_b200_sample_topk(const int32_t* topk_idx, const uint16_t* topk_val,
+                             int list_len, int M, float temperature, int top_k,
+                             float top_p, uint64_t* rng_state, int32_t* token_out,
+                             void* stream);
+
 /* ---- quantize + pack --------------------------------------------------------
  * GPU form of CUDALM's offline quantizer quantize_w4a16
  * (CUDALM tools/common/w4a16_quant.py:25-60): bf16 W [N, K] ->

@@ -114,5 +114,17 @@ inline void lm_head_int4_topk_bf16(const std::uint8_t* weight, const __half* sca
       "lm_head_int4_topk_bf16");
 }
 
+// sample_token (include/cudalm/sampling.h:200-234) for B rows on the device, over
+// the candidate lists lm_head_int4_topk_bf16 returned; rng_state holds one
+// SplitMix64 state per row (device memory) and advances by one draw per row.
+inline void sample_tokens_topk(const std::int32_t* topk_idx, const __nv_bfloat16* topk_val,
+                               int list_len, int B, float temperature, int top_k, float top_p,
+                               std::uint64_t* rng_state, std::int32_t* tokens,
+                               cudaStream_t stream) {
+  b200_detail::check(cudalm_b200_sample_topk(topk_idx, b200_detail::u16(topk_val), list_len, B,
+                                             temperature, top_k, top_p, rng_state, tokens, stream),
+                     "sample_tokens_topk");
+}
+
 }  // namespace kernels
 }  // namespace cudalm

@@ -68,6 +68,9 @@ def lib() -> ctypes.CDLL:
         L.orc_argmax_bf16.argtypes = [_u16p, ctypes.c_int]
         L.orc_topk_bf16.argtypes = [_u16p, ctypes.c_int, ctypes.c_int, _i32p,
                                     _u16p]
+        L.orc_sample_from_topk.argtypes = [_i32p, _u16p, ctypes.c_int, ctypes.c_float, ctypes.c_int,
+                                           ctypes.c_float, ctypes.POINTER(ctypes.c_uint64)]
+        L.orc_sample_from_topk.restype = ctypes.c_int
         L.orc_silu_mul_bf16.argtypes = [_u16p, _u16p, _u16p, ctypes.c_size_t]
         L.orc_silu_mul_bf16.restype = None
         L.orc_add_bf16.argtypes = [_u16p, _u16p, _u16p, ctypes.c_size_t]
@@ -92,6 +95,9 @@ def ref() -> ctypes.CDLL:
         R.ref_cpu_argmax_bf16.argtypes = [_u16p, ctypes.c_int]
         R.ref_cpu_topk_keep.argtypes = [_u16p, ctypes.c_int, ctypes.c_int, _u8p]
         R.ref_cpu_topk_keep.restype = None
+        R.ref_cpu_sample_token.argtypes = [_u16p, ctypes.c_int, ctypes.c_float, ctypes.c_int,
+                                           ctypes.c_float, ctypes.POINTER(ctypes.c_uint64)]
+        R.ref_cpu_sample_token.restype = ctypes.c_int
         R.ref_cpu_compare_bf16_ok.argtypes = [_u16p, _u16p, ctypes.c_size_t]
         for name in ("ref_gpu_int4_gemv_bf16",):
             getattr(R, name).argtypes = [ctypes.c_void_p] * 4 + [
@@ -202,6 +208,18 @@ def topk_bf16(logits: np.ndarray, k: int):
     return idx, val
 
 
+def sample_from_topk(idx: np.ndarray, val: np.ndarray, temperature: float, top_k: int,
+                     top_p: float, state: int):
+    """The reference's sample_token on a candidate list (value descending, tie ->
+    lower id); returns (token, new SplitMix64 state)."""
+    i = np.ascontiguousarray(idx, dtype=np.int32)
+    v = np.ascontiguousarray(val, dtype=np.uint16)
+    st = ctypes.c_uint64(state)
+    tok = lib().orc_sample_from_topk(_p(i, _i32p), _p(v, _u16p), i.size, float(temperature),
+                                     int(top_k), float(top_p), ctypes.byref(st))
+    return int(tok), int(st.value)
+
+
 def silu_mul_bf16(gate: np.ndarray, up: np.ndarray) -> np.ndarray:
     g = _c(gate, np.uint16)
     u = _c(up, np.uint16)
@@ -252,6 +270,15 @@ def ref_topk_keep(logits, k: int) -> np.ndarray:
     keep = np.zeros(l.size, np.uint8)
     ref().ref_cpu_topk_keep(_p(l, _u16p), l.size, k, _p(keep, _u8p))
     return keep.astype(bool)
+
+
+def ref_sample_token(logits, temperature: float, top_k: int, top_p: float, state: int):
+    """The reference's own sample_token on full logits; returns (token, new state)."""
+    l = _c(logits, np.uint16)
+    st = ctypes.c_uint64(state)
+    tok = ref().ref_cpu_sample_token(_p(l, _u16p), l.size, float(temperature), int(top_k),
+                                     float(top_p), ctypes.byref(st))
+    return int(tok), int(st.value)
 
 
 def ref_compare_bf16_ok(ref_bits, act_bits) -> bool:

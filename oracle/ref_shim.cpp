@@ -64,6 +64,20 @@ void ref_cpu_topk_keep(const std::uint16_t* logits, int vocab, int k,
   for (int i = 0; i < vocab; ++i) keep[i] = p[static_cast<std::size_t>(i)] > 0.0f;
 }
 
+// The reference's sample_token (include/cudalm/sampling.h:200-234) on full
+// logits; *state is the SplitMix64 state before the call and after it.
+int ref_cpu_sample_token(const std::uint16_t* logits, int vocab, float temperature, int top_k,
+                         float top_p, std::uint64_t* state) {
+  cudalm::SamplingConfig cfg;
+  cfg.temperature = temperature;
+  cfg.top_k = top_k;
+  cfg.top_p = top_p;
+  cudalm::SplitMix64 rng(*state);
+  const int tok = cudalm::sample_token(reinterpret_cast<const __nv_bfloat16*>(logits), vocab, cfg, &rng);
+  *state = rng.state;
+  return tok;
+}
+
 int ref_cpu_unpack_lo(int b) {
   return cudalm::int4::unpack_lo(static_cast<std::uint8_t>(b));
 }

@@ -368,6 +368,76 @@ int orc_topk_bf16(const uint16_t* logits, int n, int k, int32_t* idx_out,
 /* ------------------------------------------------------------------------ */
 
 /* y = bf16( float(bf16( g / (1 + exp(-g)) )) * float(u) ) */
+/* sample_token (CUDALM include/cudalm/sampling.h:131-234) restated on a
+ * candidate list: the first `list_len` tokens of the row in the reference's
+ * order (logit descending, tie -> lower id), as the vocabulary projection
+ * returns them.  Needs 1 <= top_k <= list_len: then the top-k survivors are the
+ * first top_k entries, the row maximum is entry 0, and nothing outside the list
+ * can have a non-zero probability.  temperature <= 0 is the greedy path: entry
+ * 0, no draw.  Arithmetic as in the reference: logit / T, exp and the sums in
+ * double; top-p accumulates in list order; the normalising sum and the
+ * cumulative walk run in ascending token id; probabilities are rounded to
+ * float before the walk.  *state is the SplitMix64 state (:99-116).
+ * Returns the token id, or -1 when the arguments are outside that domain. */
+int orc_sample_from_topk(const int32_t* idx, const uint16_t* val, int list_len, float temperature,
+                         int top_k, float top_p, uint64_t* state) {
+  if (list_len < 1) return -1;
+  if (!(temperature > 0.0f)) return idx[0];
+  if (top_k < 1 || top_k > list_len || top_k > 64) return -1;
+  double f[64];
+  int ids[64], order[64];
+  const int k = top_k;
+  for (int i = 0; i < k; ++i) {
+    f[i] = (double)orc_bf16_to_f32(val[i]) / (double)temperature;
+    ids[i] = idx[i];
+  }
+  const double max_f = f[0];
+  int kept = k;
+  if (top_p < 1.0f) {
+    double total = 0.0;
+    for (int i = 0; i < k; ++i) total += exp(f[i] - max_f);
+    double cum = 0.0;
+    int cut = k - 1;
+    for (int j = 0; j < k; ++j) {
+      cum += exp(f[j] - max_f);
+      if (cum >= (double)top_p * total || j + 1 == k) {
+        cut = j;
+        break;
+      }
+    }
+    kept = cut + 1;
+  }
+  /* ascending token id over the kept entries */
+  for (int i = 0; i < kept; ++i) order[i] = i;
+  for (int i = 1; i < kept; ++i) {
+    const int o = order[i];
+    int j = i - 1;
+    while (j >= 0 && ids[order[j]] > ids[o]) {
+      order[j + 1] = order[j];
+      --j;
+    }
+    order[j + 1] = o;
+  }
+  double norm = 0.0;
+  for (int i = 0; i < kept; ++i) norm += exp(f[order[i]] - max_f);
+  uint64_t z = (*state += 0x9E3779B97F4A7C15ull);
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  z = z ^ (z >> 31);
+  const double u = (double)(z >> 11) * 0x1.0p-53;
+  double cum = 0.0;
+  int last_kept = -1;
+  for (int i = 0; i < kept; ++i) {
+    const float p = (float)(exp(f[order[i]] - max_f) / norm);
+    if (p > 0.0f) {
+      cum += (double)p;
+      last_kept = ids[order[i]];
+      if (u < cum) return last_kept;
+    }
+  }
+  return last_kept >= 0 ? last_kept : idx[0];
+}
+
 void orc_silu_mul_bf16(const uint16_t* gate, const uint16_t* up, uint16_t* y,
                        size_t n) {
   for (size_t i = 0; i < n; ++i) {

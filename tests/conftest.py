@@ -30,6 +30,7 @@ def golden():
         quantize = np.load(os.path.join(d, "quantize.npz"))
         gemv = np.load(os.path.join(d, "gemv.npz"))
         pick = np.load(os.path.join(d, "pick.npz"))
+        sample = np.load(os.path.join(d, "sample.npz"))
 
         @staticmethod
         def names(npz):

@@ -175,6 +175,41 @@ def pick_cases():
     return cases
 
 
+def sample_cases():
+    """The reference's sample_token on full logits: per case the logits, the
+    configuration, the SplitMix64 state before, and the tokens and states of
+    eight consecutive draws."""
+    cases = {}
+    rng = np.random.default_rng(BASE_SEED + 6)
+    shapes = {
+        "normal_4096": (rng.standard_normal(4096) * 3).astype(np.float32),
+        "ties_2048": rng.integers(-3, 4, size=2048).astype(np.float32) * 0.5,
+        "peaked_1000": np.concatenate([[12.0], rng.standard_normal(999)]).astype(np.float32),
+        "flat_300": np.full(300, 1.25, np.float32),
+        "vocab_248320": (rng.standard_normal(248320) * 2.5).astype(np.float32),
+    }
+    configs = [(1.0, 50, 1.0), (0.7, 50, 0.9), (1.5, 20, 0.5), (0.05, 50, 0.95), (1.0, 1, 1.0),
+               (0.0, 50, 0.9), (2.0, 50, 0.999), (1e-3, 8, 0.3)]
+    for name, vals in shapes.items():
+        bits = orc.f32_to_bf16_bits(vals)
+        cases[f"{name}.logits"] = bits
+        cfgs, toks, states = [], [], []
+        for ci, (t, k, p) in enumerate(configs):
+            state = (0x1234567 * (ci + 1)) ^ (len(name) << 32)
+            row_t, row_s = [], [state]
+            for _ in range(8):
+                tok, state = orc.ref_sample_token(bits, t, k, p, state)
+                row_t.append(tok)
+                row_s.append(state)
+            cfgs.append((t, k, p))
+            toks.append(row_t)
+            states.append(row_s)
+        cases[f"{name}.configs"] = np.array(cfgs, np.float64)
+        cases[f"{name}.tokens"] = np.array(toks, np.int32)
+        cases[f"{name}.states"] = np.array(states, np.uint64)
+    return cases
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default="/root/reference")
@@ -188,7 +223,8 @@ def main():
     np.savez_compressed(os.path.join(HERE, "quantize.npz"), **quant_cases(quantize_w4a16))
     np.savez_compressed(os.path.join(HERE, "gemv.npz"), **gemv_cases())
     np.savez_compressed(os.path.join(HERE, "pick.npz"), **pick_cases())
-    for f in ("quantize.npz", "gemv.npz", "pick.npz"):
+    np.savez_compressed(os.path.join(HERE, "sample.npz"), **sample_cases())
+    for f in ("quantize.npz", "gemv.npz", "pick.npz", "sample.npz"):
         print(f, os.path.getsize(os.path.join(HERE, f)), "bytes")
 
 

@@ -540,3 +540,69 @@ def test_fused_epilogues_on_the_slow_kernel(eng, orc):
     eng.batch_int4_gemv_bf16(gate.weight, gate.scale, xd, y)
     got = from_dev(eng.linear_residual_bf16(gate, xd, to_dev(res, torch.bfloat16)))
     assert np.array_equal(got, orc.add_bf16(res, from_dev(y)))
+
+
+# --- token sampling on the device -----------------------------------------------------
+
+def _u64_to_i64(v):
+    return np.array(v, dtype=np.uint64).astype(np.int64)
+
+
+def test_device_sampling_matches_reference_draws(eng, orc, golden):
+    # candidate lists from the oracle's top-50 of the recorded logits; the device must
+    # reproduce the reference's tokens and SplitMix64 states draw for draw
+    # (CUDALM include/cudalm/sampling.h:200-234; recorded by tests/golden/make_golden.py)
+    import torch
+    for name in sorted({k.split(".")[0] for k in golden.sample.files}):
+        logits = golden.sample[f"{name}.logits"]
+        idx, val = orc.topk_bf16(logits, 50)
+        cfgs = golden.sample[f"{name}.configs"]
+        toks = golden.sample[f"{name}.tokens"]
+        states = golden.sample[f"{name}.states"]
+        for (t, k, p), want_t, want_s in zip(cfgs, toks, states):
+            if int(k) > idx.size:
+                continue
+            # eight rows with the same list: row j starts from the state before draw j
+            M = 8
+            d_idx = to_dev(np.tile(idx, (M, 1)).astype(np.int32))
+            d_val = to_dev(np.tile(val, (M, 1)), torch.bfloat16)
+            st = torch.from_numpy(_u64_to_i64(want_s[:M])).cuda()
+            got = eng.sample_topk(d_idx, d_val, float(np.float32(t)), int(k), float(np.float32(p)), st)
+            assert np.array_equal(from_dev(got), want_t), (name, t, k, p)
+            assert np.array_equal(st.cpu().numpy().astype(np.uint64), want_s[1:M + 1]), (name, t, k, p)
+
+
+def test_device_sampling_after_the_vocabulary_projection(eng, orc):
+    # whole chain on the device: W4A16 lm_head -> top-50 -> sample; against the oracle's
+    # sampler fed the device's own lists
+    import torch
+    N, K, M = 4096, 1024, 5
+    W, S = raw_weights(N, K, 1201)
+    x = make_x(orc, (M, K), 1202)
+    head = eng.LmHead(eng.W4A16Linear(to_dev(W), to_dev(S, torch.float16)), max_rows=M)
+    argmax, idx, val = head.forward(to_dev(x, torch.bfloat16))
+    st0 = np.array([11, 22, 33, 44, 55], np.uint64)
+    st = torch.from_numpy(st0.astype(np.int64)).cuda()
+    got = from_dev(eng.sample_topk(idx, val, 0.8, 40, 0.92, st))
+    h_idx, h_val = from_dev(idx), from_dev(val)
+    for m in range(M):
+        tok, new = orc.sample_from_topk(h_idx[m], h_val[m], 0.8, 40, 0.92, int(st0[m]))
+        assert got[m] == tok and int(st.cpu().numpy().astype(np.uint64)[m]) == new
+    # greedy: the argmax, no state needed
+    g = from_dev(eng.sample_topk(idx, val, 0.0, 0, 1.0))
+    assert np.array_equal(g, from_dev(argmax))
+
+
+def test_device_sampling_rejects_unanswerable_configurations(eng):
+    import torch
+    idx = torch.zeros((2, 50), dtype=torch.int32, device="cuda")
+    val = torch.zeros((2, 50), dtype=torch.bfloat16, device="cuda")
+    st = torch.zeros(2, dtype=torch.int64, device="cuda")
+    for kwargs, code in ((dict(temperature=1.0, top_k=0, top_p=1.0), 6),
+                         (dict(temperature=1.0, top_k=51, top_p=1.0), 6),
+                         (dict(temperature=1.0, top_k=10, top_p=0.0), 1),
+                         (dict(temperature=float("nan"), top_k=10, top_p=0.5), 1),
+                         (dict(temperature=1.0, top_k=-1, top_p=0.5), 1)):
+        with pytest.raises(eng.CudalmB200Error) as ei:
+            eng.sample_topk(idx, val, rng_state=st, **kwargs)
+        assert f"status {code}" in str(ei.value)

@@ -161,6 +161,37 @@ def test_pick_matches_reference(orc, golden):
         assert np.array_equal(val, logits[idx])
 
 
+def sample_case_names(golden):
+    return sorted({k.split(".")[0] for k in golden.sample.files})
+
+
+def test_sampling_on_candidate_list_matches_reference_sample_token(orc, golden):
+    # the reference's sample_token on FULL logits (recorded by make_golden.py) against the
+    # oracle's restatement on the top-50 candidate list: tokens and RNG states, eight
+    # consecutive draws per configuration (CUDALM include/cudalm/sampling.h:131-234)
+    for name in sample_case_names(golden):
+        logits = golden.sample[f"{name}.logits"]
+        idx, val = orc.topk_bf16(logits, 50)
+        for (t, k, p), toks, states in zip(golden.sample[f"{name}.configs"],
+                                           golden.sample[f"{name}.tokens"],
+                                           golden.sample[f"{name}.states"]):
+            state = int(states[0])
+            for j in range(8):
+                tok, state = orc.sample_from_topk(idx, val, float(np.float32(t)), int(k),
+                                                  float(np.float32(p)), state)
+                assert tok == int(toks[j]), (name, t, k, p, j)
+                assert state == int(states[j + 1]), (name, t, k, p, j)
+
+
+def test_sampling_rejects_what_a_candidate_list_cannot_answer(orc):
+    idx = np.arange(10, dtype=np.int32)
+    val = orc.f32_to_bf16_bits(np.linspace(2, 1, 10).astype(np.float32))
+    assert orc.sample_from_topk(idx, val, 1.0, 0, 1.0, 1)[0] == -1    # top-k disabled: whole vocabulary
+    assert orc.sample_from_topk(idx, val, 1.0, 11, 1.0, 1)[0] == -1   # more than the list holds
+    tok, state = orc.sample_from_topk(idx, val, 0.0, 5, 0.5, 77)      # greedy: entry 0, no draw
+    assert (tok, state) == (0, 77)
+
+
 def test_silu_mul_and_add_rounding_order(orc):
     # reference src/kernels/qwen35_kernels.cu:442-476: silu is rounded to bf16
     # first, then multiplied; add rounds once.
