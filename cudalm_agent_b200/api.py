@@ -66,6 +66,16 @@ SIGNATURES = {
     "cudalm_b200_group_destroy": (_ci, [_vp]),
     "cudalm_b200_group_bytes": (ctypes.c_int64, [_vp]),
     "cudalm_b200_gate_up_bf16": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _vp]),
+    "cudalm_b200_v2_open": (_ci, [ctypes.c_char_p, _vp, ctypes.c_char_p, ctypes.c_size_t]),
+    "cudalm_b200_v2_close": (None, [_vp]),
+    "cudalm_b200_v2_num_tensors": (_ci, [_vp]),
+    "cudalm_b200_v2_num_metadata": (_ci, [_vp]),
+    "cudalm_b200_v2_tensor_at": (_ci, [_vp, _ci, _vp]),
+    "cudalm_b200_v2_find": (_ci, [_vp, ctypes.c_char_p]),
+    "cudalm_b200_v2_config_blob": (_ci, [_vp, _vp]),
+    "cudalm_b200_v2_metadata_at": (_ci, [_vp, _ci, _vp, _vp]),
+    "cudalm_b200_v2_upload": (_ci, [_vp, _ci, _vp, ctypes.c_size_t, _vp]),
+    "cudalm_b200_v2_linear": (_ci, [_vp, ctypes.c_char_p, ctypes.c_char_p, _vp, _vp, _vp, _vp]),
     "cudalm_b200_sample_topk": (_ci, [_vp, _vp, _ci, _ci, ctypes.c_float, _ci, ctypes.c_float, _vp,
                                       _vp, _vp]),
     "cudalm_b200_gate_up_silu_bf16": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _vp]),

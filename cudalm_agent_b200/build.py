@@ -17,7 +17,8 @@ CSRC = os.path.join(PKG, "csrc")
 LIB_DIR = os.path.join(PKG, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libcudalm_b200.so")
 
-SOURCES = ["runtime.cu", "w4a16_linear.cu", "w4a16_tc.cu", "quantize.cu", "lm_head.cu", "sample.cu"]
+SOURCES = ["runtime.cu", "w4a16_linear.cu", "w4a16_tc.cu", "quantize.cu", "lm_head.cu", "sample.cu",
+           "weights_v2.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -59,6 +59,7 @@ const char* cudalm_b200_status_string(int status) {
     case CUDALM_B200_ERR_UNSUPPORTED: return "unsupported configuration";
     case CUDALM_B200_ERR_TOO_LARGE: return "size exceeds a fixed capacity";
     case CUDALM_B200_ERR_WORKSPACE: return "workspace missing or too small";
+    case CUDALM_B200_ERR_FILE: return "weight file missing or malformed";
     default: return "unknown status";
   }
 }

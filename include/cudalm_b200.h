@@ -47,7 +47,8 @@ enum {
   CUDALM_B200_ERR_TIMEOUT = 5,     /* a bounded device-side wait ran out    */
   CUDALM_B200_ERR_UNSUPPORTED = 6, /* legal in CUDALM but outside this build */
   CUDALM_B200_ERR_TOO_LARGE = 7,   /* exceeds a stated fixed capacity       */
-  CUDALM_B200_ERR_WORKSPACE = 8    /* workspace missing or too small        */
+  CUDALM_B200_ERR_WORKSPACE = 8,   /* workspace missing or too small        */
+  CUDALM_B200_ERR_FILE = 9         /* a weight file is missing or malformed  */
 };
 
 CUDALM_B200_API const char* cudalm_b200_status_string(int status);
@@ -235,6 +236,51 @@ CUDALM_B200_API int cudalm_b200_sample_topk(const int32_t* topk_idx, const uint1
                              int list_len, int M, float temperature, int top_k,
                              float top_p, uint64_t* rng_state, int32_t* token_out,
                              void* stream);
+
+/* ---- `.cudalm` v2 weight container -----------------------------------------------
+ * Reader of the file CUDALM's converter writes and WeightFileV2::load reads
+ * (CUDALM include/cudalm/weight_format_v2.h:35-190,
+ *  src/runtime/weight_loader_v2.cpp:49-242), with the same validation rules.
+ * open() reads and validates the whole file (CUDALM_B200_ERR_FILE with the
+ * reason in `err`); the handle owns the bytes until close().  Tensor and metadata
+ * strings and host_bytes point into the handle.  upload() enqueues one copy of a
+ * tensor's bytes to device memory.  linear() checks that two tensors form a
+ * W4A16 projection (int4_packed [N, K/2] + fp16_scale [N, K/128]). */
+enum {
+  CUDALM_B200_V2_FP16 = 1,
+  CUDALM_B200_V2_INT4_PACKED = 2,
+  CUDALM_B200_V2_FP16_SCALE = 3,
+  CUDALM_B200_V2_FP32 = 4,
+  CUDALM_B200_V2_BF16 = 5
+};
+typedef struct cudalm_b200_v2_file cudalm_b200_v2_file;
+typedef struct cudalm_b200_v2_tensor {
+  const char* name;
+  int32_t dtype;
+  int32_t ndim;
+  int64_t dims[8];        /* int4_packed: in packed bytes (last dim = K/2) */
+  uint64_t offset;        /* from the start of the payload section */
+  uint64_t byte_size;
+  int32_t align;
+  int32_t reserved;
+  const void* host_bytes; /* the tensor's bytes inside the handle */
+} cudalm_b200_v2_tensor;
+CUDALM_B200_API int cudalm_b200_v2_open(const char* path, cudalm_b200_v2_file** out, char* err,
+                             size_t err_cap);
+CUDALM_B200_API void cudalm_b200_v2_close(cudalm_b200_v2_file* file);
+CUDALM_B200_API int cudalm_b200_v2_num_tensors(const cudalm_b200_v2_file* file);
+CUDALM_B200_API int cudalm_b200_v2_num_metadata(const cudalm_b200_v2_file* file);
+CUDALM_B200_API int cudalm_b200_v2_tensor_at(const cudalm_b200_v2_file* file, int index,
+                             cudalm_b200_v2_tensor* out);
+CUDALM_B200_API int cudalm_b200_v2_find(const cudalm_b200_v2_file* file, const char* name);
+CUDALM_B200_API int cudalm_b200_v2_config_blob(const cudalm_b200_v2_file* file, uint8_t* out88);
+CUDALM_B200_API int cudalm_b200_v2_metadata_at(const cudalm_b200_v2_file* file, int index,
+                             const char** key, const char** value);
+CUDALM_B200_API int cudalm_b200_v2_upload(const cudalm_b200_v2_file* file, int index, void* device_dst,
+                             size_t capacity, void* stream);
+CUDALM_B200_API int cudalm_b200_v2_linear(const cudalm_b200_v2_file* file, const char* weight_name,
+                             const char* scale_name, int* weight_index, int* scale_index,
+                             int* N, int* K);
 
 /* ---- quantize + pack --------------------------------------------------------
  * GPU form of CUDALM's offline quantizer quantize_w4a16

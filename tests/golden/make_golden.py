@@ -210,6 +210,47 @@ def sample_cases():
     return cases
 
 
+def v2_file_case(ref_root, quantize_w4a16):
+    """A small `.cudalm` v2 file written by the reference's own Python writer
+    (tools/common/cudalm_v2.py), and what it holds."""
+    import torch
+    sys.path.insert(0, os.path.join(ref_root, "tools", "common"))
+    import cudalm_v2 as ref_v2  # the reference's writer
+
+    g = torch.Generator().manual_seed(BASE_SEED + 7)
+    w = (torch.randn(16, 256, generator=g) * 0.02).to(torch.bfloat16)
+    packed, scale, _, _ = quantize_w4a16(w)
+    packed = packed.contiguous().numpy().astype(np.uint8)
+    scale = scale.contiguous().view(torch.int16).numpy().astype(np.uint16)
+    norm = torch.randn(24, generator=g).to(torch.bfloat16).view(torch.int16).numpy().astype(np.uint16)
+    a_log = torch.randn(5, generator=g).numpy().astype(np.float32)
+    conv = torch.randn(2, 3, 4, generator=g).to(torch.float16).view(torch.int16).numpy().astype(np.uint16)
+    tensors = [
+        ref_v2.V2Tensor("layers.0.mlp.gate_proj.weight", ref_v2.DT_INT4_PACKED, packed.shape, packed.tobytes()),
+        ref_v2.V2Tensor("layers.0.mlp.gate_proj.scale", ref_v2.DT_FP16_SCALE, scale.shape, scale.tobytes()),
+        ref_v2.V2Tensor("layers.0.input_layernorm.weight", ref_v2.DT_BF16, norm.shape, norm.tobytes(), 2),
+        ref_v2.V2Tensor("layers.0.linear_attn.A_log", ref_v2.DT_FP32, a_log.shape, a_log.tobytes(), 4),
+        ref_v2.V2Tensor("layers.0.linear_attn.conv1d.weight", ref_v2.DT_FP16, conv.shape, conv.tobytes()),
+    ]
+    meta = {"arch": "qwen3_5", "source_dtype": "bfloat16", "generator": "make_golden.py"}
+    obj = ref_v2.V2File(ref_v2.Qwen35Config.qwen35_08b(), meta, tensors)
+    raw = obj.to_bytes()
+    with open(os.path.join(HERE, "tiny_v2.cudalm"), "wb") as f:
+        f.write(raw)
+    back = ref_v2.V2File.from_bytes(raw)  # the reference's reader accepts its writer's file
+    assert [t.name for t in back.tensors] == [t.name for t in tensors]
+    cases = {"config_blob": np.frombuffer(obj.config.to_blob(), np.uint8),
+             "meta_keys": np.array(list(meta.keys())), "meta_values": np.array(list(meta.values())),
+             "names": np.array([t.name for t in tensors]),
+             "dtypes": np.array([t.dtype for t in tensors], np.int32),
+             "aligns": np.array([t.align for t in tensors], np.int32),
+             "w_bf16": w.view(torch.int16).numpy().astype(np.uint16)}
+    for i, t in enumerate(tensors):
+        cases[f"dims{i}"] = np.array(t.dims, np.int64)
+        cases[f"data{i}"] = np.frombuffer(t.data, np.uint8)
+    return cases
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default="/root/reference")
@@ -224,7 +265,8 @@ def main():
     np.savez_compressed(os.path.join(HERE, "gemv.npz"), **gemv_cases())
     np.savez_compressed(os.path.join(HERE, "pick.npz"), **pick_cases())
     np.savez_compressed(os.path.join(HERE, "sample.npz"), **sample_cases())
-    for f in ("quantize.npz", "gemv.npz", "pick.npz", "sample.npz"):
+    np.savez_compressed(os.path.join(HERE, "tiny_v2.npz"), **v2_file_case(args.ref, quantize_w4a16))
+    for f in ("quantize.npz", "gemv.npz", "pick.npz", "sample.npz", "tiny_v2.npz", "tiny_v2.cudalm"):
         print(f, os.path.getsize(os.path.join(HERE, f)), "bytes")
 
 
