@@ -55,11 +55,14 @@ __host__ __device__ constexpr int tc_out_bytes(int ntok) { return ntok * kTcRows
 //   warps 8..15  read the accumulators back and fold them in: same row mapping
 //   warp 16      TMA producer
 //   warps 17,18  MMA issuers, one per tile
+//   warp 19      output stores: lane 0 for tile 0, lane 1 for tile 1 (so that no
+//                read-back thread waits on a store)
 constexpr int kTcDequantWarps = 8;
 constexpr int kTcFoldWarp0 = 8;
 constexpr int kTcProducerWarp = 16;
 constexpr int kTcMmaWarp = 17;
-constexpr int kTcThreads = 608;
+constexpr int kTcStoreWarp = 19;  // lanes 0 and 1 issue the TMA stores of tiles 0 and 1
+constexpr int kTcThreads = 640;   // 20 warps: one more would cut the register budget per thread
 constexpr unsigned long long kTcWaitNs = 400000000ull;
 
 struct alignas(64) TcDesc {
@@ -434,7 +437,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
         }
       }
     }
-  } else if (warp >= kTcMmaWarp) {
+  } else if (warp >= kTcMmaWarp && warp < kTcStoreWarp) {
     // ---------------- MMA issuer, one per tile ----------------
     if (lane == 0) {
       const int t = warp - kTcMmaWarp;
@@ -531,7 +534,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
     const int lrow = (fw & 3) * 32 + lane;
     const std::uint32_t lane_base = static_cast<std::uint32_t>((fw & 3) * 32) << 16;
     const std::uint32_t tile_base = tmem_base + tile * kColsPerTile + lane_base;
-    const bool store_thread = (fw & 3) == 0 && lane == 0;  // issues the tile's TMA stores
     std::uint8_t* outp = outsm + tile * tc_out_bytes(NTOK) + lrow * 2;
     std::uint32_t eit = 0;  // items finished by this tile
     bool alive = true;
@@ -598,13 +600,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
         }
         continue;
       }
-      // the tile's rows leave through shared memory and one TMA store
-      if (store_thread) {
-        if (eit >= 1) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-        mbar_arrive(&sm->out_free[tile]);
-      }
-      {
-        const bool ok = tc_wait(&sm->out_free[tile], eit & 1u, abort_flag);
+      // the tile's rows leave through shared memory and one TMA store, issued by the
+      // tile's store warp; the buffer is free again once the previous store has read it
+      if (eit >= 1) {
+        const bool ok = tc_wait(&sm->out_free[tile], (eit - 1) & 1u, abort_flag);
         alive = __all_sync(0xffffffffu, ok);
         if (!alive) break;
       }
@@ -613,22 +612,44 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
         *reinterpret_cast<std::uint16_t*>(outp + n * (kTcRowsPerTile * 2)) = float_to_bf16_bits(acc[n]);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       mbar_arrive(&sm->out_full[tile]);
-      if (store_thread) {
-        if (!tc_wait(&sm->out_full[tile], eit & 1u, abort_flag)) {
-          alive = false;
-        } else if (row0 < LN) {
+      ++eit;
+    }
+  } else if (warp >= kTcStoreWarp) {
+    // ---------------- output stores, one lane per tile ----------------
+    if (lane < kTcTiles) {
+      const int tile = lane;
+      const TcDesc* L = nullptr;
+      int LN = 0, item_begin = 0;
+      bool direct = false;
+      std::uint32_t n_stores = 0;  // items of this tile that went through the output buffer
+      bool ok = true;
+      for (int item = it_lo; item < it_hi && ok && !*abort_flag; ++item) {
+        if (wk.seek(item) || L == nullptr) {
+          L = tbl + wk.d;
+          LN = L->N;
+          item_begin = L->item_begin;
+          direct = L->direct_store != 0;
+        }
+        if (direct) continue;  // the read-back threads store these rows themselves
+        const int row0 = (item - item_begin) * kTcItemRows + tile * kTcRowsPerTile;
+        if (!tc_wait(&sm->out_full[tile], n_stores & 1u, abort_flag)) {
+          ok = false;
+          break;
+        }
+        if (row0 < LN) {
           asm volatile(
               "cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(
                   &L->ymap),
               "r"(row0), "r"(0), "r"(smem_u32(outsm + tile * tc_out_bytes(NTOK)))
               : "memory");
           asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
         }
+        mbar_arrive(&sm->out_free[tile]);
+        ++n_stores;
       }
-      alive = __all_sync(0xffffffffu, alive);
-      ++eit;
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
-    if (store_thread) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   }
 
   __syncthreads();
