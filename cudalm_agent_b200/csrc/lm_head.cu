@@ -28,7 +28,7 @@
 namespace cb200 {
 
 int run_linear_with_cta_max(const cudalm_b200_linear& l, float* cta_max, int* grid_out,
-                            cudaStream_t stream);
+                            cudaStream_t stream, int* clear_words, int clear_count);
 int stream_rows_per_pass(int K);
 int run_linear_any(const cudalm_b200_linear& l, cudaStream_t stream);
 
@@ -358,16 +358,16 @@ int cudalm_b200_lm_head_topk(const uint8_t* weight, const uint16_t* scales, cons
     uint16_t* logits = logits_out ? logits_out + static_cast<size_t>(m0) * N : ws.logits;
     cudalm_b200_linear l{weight, scales, x + static_cast<size_t>(m0) * K, logits, N, K, rows, 0};
 
-    zero_counts_kernel<<<1, 64, 0, st>>>(ws.counts, kMaxPassRows);
-    if (int rc = check_launch()) return rc;
-
     int ncta = 0;
     if (staged) {
-      if (int rc = run_linear_with_cta_max(l, ws.cta_max, &ncta, st)) return rc;
+      // the projection's first CTA also clears the candidate counters
+      if (int rc = run_linear_with_cta_max(l, ws.cta_max, &ncta, st, ws.counts, kMaxPassRows)) return rc;
       if (ncta > kMaxCtas) return CUDALM_B200_ERR_TOO_LARGE;
     } else {
       // no per-CTA maxima on the slow path: every logit is a candidate, and a
       // row longer than the candidate list takes the exact search
+      zero_counts_kernel<<<1, 64, 0, st>>>(ws.counts, kMaxPassRows);
+      if (int rc = check_launch()) return rc;
       if (int rc = run_linear_any(l, st)) return rc;
       ncta = 0;
     }

@@ -16,7 +16,7 @@ namespace cb200 {
 bool tc_eligible(const cudalm_b200_linear& l);
 int run_tc(const cudalm_b200_linear* ls, int count, cudaStream_t stream);
 int run_tc_with_cta_max(const cudalm_b200_linear& l, float* cta_max, int* grid_out,
-                        cudaStream_t stream);
+                        cudaStream_t stream, int* clear_words, int clear_count);
 struct TcGroup;
 int tc_group_create(const cudalm_b200_linear* ls, int count, TcGroup** out);
 int tc_group_run(const TcGroup* g, cudaStream_t stream);
@@ -439,10 +439,10 @@ int run_extra(cudalm_b200_linear l, const LinearExtra& ex, cudaStream_t stream) 
 // (M rows in one pass) that also records the per-CTA maxima.  Returns
 // ERR_UNSUPPORTED when the projection cannot take the staged path in one pass.
 int run_linear_with_cta_max(const cudalm_b200_linear& l, float* cta_max, int* grid_out,
-                            cudaStream_t stream) {
+                            cudaStream_t stream, int* clear_words, int clear_count) {
   if (int rc = validate(l)) return rc;
   if (l.M >= g_tc_min_rows.load(std::memory_order_relaxed) && tc_eligible(l))
-    return run_tc_with_cta_max(l, cta_max, grid_out, stream);
+    return run_tc_with_cta_max(l, cta_max, grid_out, stream, clear_words, clear_count);
   if (!stream_eligible(l)) return CUDALM_B200_ERR_UNSUPPORTED;
   if (max_rows_per_pass(l.K) < l.M) return CUDALM_B200_ERR_UNSUPPORTED;
   StreamParams p;
@@ -452,6 +452,8 @@ int run_linear_with_cta_max(const cudalm_b200_linear& l, float* cta_max, int* gr
   p.total_mt = mtiles(l.N);
   p.total_cost = p.total_mt * chunks_per_mtile(l.K);
   p.cta_max = cta_max;
+  p.clear_words = clear_words;
+  p.clear_count = clear_count;
   return launch_stream(p, l.K, l.M, stream, grid_out);
 }
 

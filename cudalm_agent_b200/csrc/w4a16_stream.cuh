@@ -81,6 +81,10 @@ struct StreamParams {
   int x_buffers;    // 1, or 2 for the barrier-free change of projection
   int* status;      // device status word
   float* cta_max;   // [gridDim.x][M] when the kernel is built with CTA_MAX
+  // CTA_MAX only: words that CTA 0 clears once it is past the wait on the previous
+  // grid (the candidate counters of the token pick that follows), or nullptr
+  int* clear_words;
+  int clear_count;
   // Optional, for launches with a device table: per CTA {first m-tile, its
   // projection}, gridDim.x + 1 entries, so that a CTA finds its range with two
   // loads instead of a chain of dependent table look-ups.
@@ -1078,6 +1082,8 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
   }
 
   if (CTA_MAX) {
+    if (blockIdx.x == 0 && p.clear_words != nullptr)
+      for (int i = tid; i < p.clear_count; i += NWARPS * 32) p.clear_words[i] = 0;
     // reduce over the eight row-lanes that share a column pair, then over warps
     const int M = desc_table(p)->M;
 #pragma unroll

@@ -89,6 +89,10 @@ struct TcParams {
   // activation row the largest bf16-rounded output the CTA produced,
   // cta_max[blockIdx.x * M + m].
   float* cta_max;
+  // with cta_max: words that CTA 0 clears at its end (the candidate counters of the
+  // token pick that follows), or nullptr
+  int* clear_words;
+  int clear_count;
 };
 
 // ---------------------------------------------------------------------------
@@ -655,6 +659,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
   __syncthreads();
   if (p.cta_max != nullptr && tid < tbl[0].M)
     p.cta_max[static_cast<std::size_t>(blockIdx.x) * tbl[0].M + tid] = key_float(sm->row_max[tid]);
+  if (p.cta_max != nullptr && blockIdx.x == 0 && p.clear_words != nullptr)
+    for (int i = tid; i < p.clear_count; i += kTcThreads) p.clear_words[i] = 0;
   if (*abort_flag && tid == 0) atomicExch(p.status, CUDALM_B200_ERR_TIMEOUT);
   tc_fence_after();
   if (warp == 0) tmem_dealloc(tmem_base, 512);
@@ -843,13 +849,15 @@ int tc_run_params(TcParams& p, int ntok, cudaStream_t stream, int* grid_out = nu
 
 // One projection that also records the per-CTA maxima (vocabulary projection).
 int run_tc_with_cta_max(const cudalm_b200_linear& l, float* cta_max, int* grid_out,
-                        cudaStream_t stream) {
+                        cudaStream_t stream, int* clear_words, int clear_count) {
   TcParams p;
   std::memset(&p, 0, sizeof(p));
   int ntok = 0;
   if (int rc = tc_describe(&l, 1, p.inl, &p.total_items, &p.total_cost, &ntok)) return rc;
   p.n_desc = 1;
   p.cta_max = cta_max;
+  p.clear_words = clear_words;
+  p.clear_count = clear_count;
   return tc_run_params(p, ntok, stream, grid_out);
 }
 
