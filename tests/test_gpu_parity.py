@@ -606,3 +606,34 @@ def test_device_sampling_rejects_unanswerable_configurations(eng):
         with pytest.raises(eng.CudalmB200Error) as ei:
             eng.sample_topk(idx, val, rng_state=st, **kwargs)
         assert f"status {code}" in str(ei.value)
+
+
+def test_group_of_very_many_tiny_projections(eng, orc):
+    # ~10 projections per CTA: more than the kernel's shared-memory descriptor cache
+    # holds, and a chain of barrier-free changes of projection in every CTA
+    import torch
+    rng = np.random.default_rng(77)
+    count, K = 1500, 128
+    items, refs = [], []
+    x_all = make_x(orc, (count, K), 1301)
+    for i in range(count):
+        N = 16 if i % 3 else 24
+        W, S = raw_weights(N, K, 2000 + i % 17)
+        lin = eng.W4A16Linear(to_dev(W), to_dev(S, torch.float16))
+        y = torch.zeros((N,), dtype=torch.bfloat16, device="cuda")
+        items.append((lin, to_dev(x_all[i], torch.bfloat16), y))
+        if i % 50 == 0:
+            refs.append((i, orc.gemv_bf16(W, S, x_all[i])))
+    grp = eng.LinearGroup(items)
+    for _ in range(2):
+        grp.run()
+    torch.cuda.synchronize()
+    assert eng.device_status() == 0
+    for i, want in refs:
+        check_close(orc, from_dev(items[i][2]), want, f"tiny group item {i}")
+    # every output equals the single call's, bit for bit
+    for i in rng.choice(count, size=40, replace=False):
+        lin, x, y = items[int(i)]
+        single = eng.int4_gemv_bf16(lin.weight, lin.scale, x)
+        assert torch.equal(single, y), int(i)
+    grp.close()
