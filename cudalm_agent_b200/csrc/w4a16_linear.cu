@@ -17,6 +17,8 @@ bool tc_eligible(const cudalm_b200_linear& l);
 int run_tc(const cudalm_b200_linear* ls, int count, cudaStream_t stream);
 int run_tc_with_cta_max(const cudalm_b200_linear& l, float* cta_max, int* grid_out,
                         cudaStream_t stream, int* clear_words, int clear_count);
+int run_tc_extra(const cudalm_b200_linear& l, const std::uint8_t* weight2,
+                 const std::uint16_t* scales2, const std::uint16_t* residual, cudaStream_t stream);
 struct TcGroup;
 int tc_group_create(const cudalm_b200_linear* ls, int count, TcGroup** out);
 int tc_group_run(const TcGroup* g, cudaStream_t stream);
@@ -405,6 +407,24 @@ int run_extra(cudalm_b200_linear l, const LinearExtra& ex, cudaStream_t stream) 
   if (int rc = validate(l)) return rc;
   const bool pair = ex.weight2 != nullptr;
   if (pair && !ex.scales2) return CUDALM_B200_ERR_NULL;
+  if (l.M >= g_tc_min_rows.load(std::memory_order_relaxed)) {
+    // passes of up to 64 rows on the tensor-memory kernel, when it takes the call
+    bool done = true;
+    for (int m0 = 0; m0 < l.M && done; m0 += 64) {
+      cudalm_b200_linear part = l;
+      part.M = (l.M - m0 < 64) ? (l.M - m0) : 64;
+      part.x = l.x + static_cast<std::size_t>(m0) * l.K;
+      part.y = l.y + static_cast<std::size_t>(m0) * l.N;
+      const int rc = tc_eligible(part)
+                         ? run_tc_extra(part, ex.weight2, ex.scales2,
+                                        ex.residual ? ex.residual + static_cast<std::size_t>(m0) * l.N : nullptr,
+                                        stream)
+                         : CUDALM_B200_ERR_UNSUPPORTED;
+      if (rc == CUDALM_B200_ERR_UNSUPPORTED && m0 == 0) done = false;  // streaming passes instead
+      else if (rc != CUDALM_B200_OK) return rc;
+    }
+    if (done) return CUDALM_B200_OK;
+  }
   int per_pass = stream_eligible(l) && (!pair || aligned_to(ex.weight2, 16)) ? max_rows_per_pass(l.K) : 0;
   if (per_pass > 16) per_pass = 16;
   if (per_pass == 0) {
@@ -549,6 +569,9 @@ int cudalm_b200_gate_up_bf16(const uint8_t* gate_weight, const uint16_t* gate_sc
   // rows of x beyond what one launch holds go in further passes
   int per_pass = (K > 0 && K % 128 == 0 && K <= kMaxStreamK) ? max_rows_per_pass(K) : 0;
   if (per_pass == 0) per_pass = M;
+  // batched rows go to the tensor-memory kernel in passes of 64 (linear_multi falls
+  // back to the streaming kernel, in its own passes, when that kernel does not take them)
+  if (M >= g_tc_min_rows.load(std::memory_order_relaxed)) per_pass = 64;
   for (int m0 = 0; m0 < M; m0 += per_pass) {
     const int mm = (M - m0 < per_pass) ? (M - m0) : per_pass;
     cudalm_b200_linear two[2] = {

@@ -69,13 +69,24 @@ struct alignas(64) TcDesc {
   CUtensorMap tmap;    // weights as uint32 [N][K/8], box 128 rows x 32 words, 128-byte swizzle
   CUtensorMap xmap;    // activations as bf16 [M][K], box NTOK rows x 64 values, 128-byte swizzle
   CUtensorMap ymap;    // outputs as bf16 [M][N], box NTOK rows x 128 values
+  CUtensorMap tmap2;   // mode kTcPair: the second (up) matrix, same shape as the first (gate)
   const std::uint16_t* S;
+  const std::uint16_t* S2;   // scales of the second matrix
+  const std::uint16_t* res;  // mode kTcResidual: residual [M][N]
   std::uint16_t* y;
   int N, K, M;
-  int item_begin;   // first item (256-row block) of this projection in the launch
+  int item_begin;   // first item of this projection in the launch
   int cost_begin;   // stage loads before this projection
   int direct_store;  // outputs cannot take the TMA store (base or row pitch off 16 bytes)
+  // kTcPlain; kTcPair: out = silu(gate x) * (up x), every 256-row block is two
+  // consecutive items (gate rows, then the same rows of up); kTcResidual: out = res + W x
+  int mode;
 };
+enum : int { kTcPlain = 0, kTcPair = 1, kTcResidual = 2 };
+__host__ __device__ inline int tc_desc_items(const TcDesc& d) {
+  const int blocks = (d.N + kTcItemRows - 1) / kTcItemRows;
+  return d.mode == kTcPair ? 2 * blocks : blocks;
+}
 
 struct TcParams {
   TcDesc inl[CUDALM_B200_MAX_INLINE_LINEARS];
@@ -302,14 +313,14 @@ struct TcWalk {
     tbl = t;
     n_desc = nd;
     d = d_first;
-    item_end = d < nd ? t[d].item_begin + (t[d].N + kTcItemRows - 1) / kTcItemRows : 0;
+    item_end = d < nd ? t[d].item_begin + tc_desc_items(t[d]) : 0;
   }
   // true when the item lies in a later projection than the previous one did
   __device__ __forceinline__ bool seek(int item) {
     bool moved = false;
     while (item >= item_end) {
       ++d;
-      item_end = tbl[d].item_begin + (tbl[d].N + kTcItemRows - 1) / kTcItemRows;
+      item_end = tbl[d].item_begin + tc_desc_items(tbl[d]);
       moved = true;
     }
     return moved;
@@ -319,7 +330,9 @@ struct TcWalk {
 // ---------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------
-template <int NTOK>
+// EXTRA: the launch holds a pair (silu(gate) * up) or a projection with a residual;
+// plain launches are compiled without that code (it is large: 64 unrolled epilogues).
+template <int NTOK, bool EXTRA>
 __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_constant__ TcParams p) {
   extern __shared__ __align__(1024) std::uint8_t smem_raw[];
   // the swizzled TMA destinations need 1024-byte alignment; the launch adds the slack
@@ -374,7 +387,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
         if (tbl[mid].cost_begin <= cost) lo = mid; else hi = mid - 1;
       }
       const int per_item = ((tbl[lo].K >> 7) + 1) >> 1;
-      return tbl[lo].item_begin + static_cast<int>((cost - tbl[lo].cost_begin + per_item - 1) / per_item);
+      int within = static_cast<int>((cost - tbl[lo].cost_begin + per_item - 1) / per_item);
+      if (tbl[lo].mode == kTcPair) within = (within + 1) & ~1;  // a block's two items stay together
+      return tbl[lo].item_begin + within;
     };
     it_lo = item_at(static_cast<long long>(blockIdx.x) * p.total_cost / gridDim.x);
     it_hi = item_at(static_cast<long long>(blockIdx.x + 1) * p.total_cost / gridDim.x);
@@ -397,6 +412,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
       bool ok = true;
       const TcDesc* L = nullptr;
       int G = 0, item_begin = 0;
+      bool pair = false;
       int ps = 0;                  // stage to fill next
       std::uint32_t ps_phase = 0;  // phase its `full` barrier completes next
       bool ps_round = false;       // every stage has been used at least once
@@ -405,8 +421,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
           L = tbl + wk.d;
           G = L->K >> 7;
           item_begin = L->item_begin;
+          pair = L->mode == kTcPair;
         }
-        const int row0 = (item - item_begin) * kTcItemRows;
+        const int j = item - item_begin;
+        const int row0 = (pair ? (j >> 1) : j) * kTcItemRows;
+        const CUtensorMap* wmap = (pair && (j & 1)) ? &L->tmap2 : &L->tmap;
         for (int c = 0; c < (G + 1) / 2; ++c) {
           // second and later uses of a stage wait until its previous content is done with
           if (ps_round && !tc_wait(&sm->empty[ps], ps_phase ^ 1u, abort_flag)) {
@@ -421,7 +440,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
                 "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
                 ".L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;" ::"r"(
                     smem_u32(st + t * kTcRowsPerTile * 128)),
-                "l"(&L->tmap), "r"(c * 32), "r"(row0 + t * kTcRowsPerTile),
+                "l"(wmap), "r"(c * 32), "r"(row0 + t * kTcRowsPerTile),
                 "r"(smem_u32(&sm->full[s])), "l"(policy)
                 : "memory");
           }
@@ -542,22 +561,25 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
     std::uint32_t eit = 0;  // items finished by this tile
     bool alive = true;
     const TcDesc* L = nullptr;
-    const std::uint16_t* S = nullptr;
     std::uint16_t* y = nullptr;
-    int LN = 0, LM = 0, G = 0, item_begin = 0;
+    int LN = 0, LM = 0, G = 0, item_begin = 0, mode = kTcPlain;
     bool direct = false;
     for (int item = it_lo; item < it_hi && alive; ++item) {
       if (wk.seek(item) || L == nullptr) {
         L = tbl + wk.d;
-        S = L->S;
         y = L->y;
         LN = L->N;
         LM = L->M;
         G = L->K >> 7;
         item_begin = L->item_begin;
         direct = L->direct_store != 0;
+        mode = L->mode;
       }
-      const int row0 = (item - item_begin) * kTcItemRows + tile * kTcRowsPerTile;
+      const int j = item - item_begin;
+      const bool second = EXTRA && mode == kTcPair && (j & 1);        // the up matrix of a pair
+      const bool first_of_pair = EXTRA && mode == kTcPair && !(j & 1);  // the gate matrix of a pair
+      const std::uint16_t* S = second ? L->S2 : L->S;
+      const int row0 = ((EXTRA && mode == kTcPair) ? (j >> 1) : j) * kTcItemRows + tile * kTcRowsPerTile;
       const int row = row0 + lrow;
       const bool row_ok = row < LN;
       const std::uint16_t* srow = S + static_cast<std::size_t>(row_ok ? row : 0) * G;
@@ -606,14 +628,29 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
       }
       // the tile's rows leave through shared memory and one TMA store, issued by the
       // tile's store warp; the buffer is free again once the previous store has read it
-      if (eit >= 1) {
+      if (eit >= 1 && !second) {
         const bool ok = tc_wait(&sm->out_free[tile], (eit - 1) & 1u, abort_flag);
         alive = __all_sync(0xffffffffu, ok);
         if (!alive) break;
       }
+      if (first_of_pair) {
+        // the gate outputs wait in the tile's buffer, each at its own thread's slots
 #pragma unroll
-      for (int n = 0; n < NTOK; ++n)
-        *reinterpret_cast<std::uint16_t*>(outp + n * (kTcRowsPerTile * 2)) = float_to_bf16_bits(acc[n]);
+        for (int n = 0; n < NTOK; ++n)
+          *reinterpret_cast<std::uint16_t*>(outp + n * (kTcRowsPerTile * 2)) = float_to_bf16_bits(acc[n]);
+        continue;
+      }
+#pragma unroll
+      for (int n = 0; n < NTOK; ++n) {
+        std::uint16_t* slot = reinterpret_cast<std::uint16_t*>(outp + n * (kTcRowsPerTile * 2));
+        std::uint16_t o = float_to_bf16_bits(acc[n]);
+        if (EXTRA && second) {
+          o = silu_mul_bits(bf16_bits_to_float(*slot), o);
+        } else if (EXTRA && mode == kTcResidual) {
+          if (row_ok && n < LM) o = add_bits(__ldg(L->res + static_cast<std::size_t>(n) * LN + row), o);
+        }
+        *slot = o;
+      }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       mbar_arrive(&sm->out_full[tile]);
       ++eit;
@@ -624,7 +661,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
       const int tile = lane;
       const TcDesc* L = nullptr;
       int LN = 0, item_begin = 0;
-      bool direct = false;
+      bool direct = false, pair = false;
       std::uint32_t n_stores = 0;  // items of this tile that went through the output buffer
       bool ok = true;
       for (int item = it_lo; item < it_hi && ok && !*abort_flag; ++item) {
@@ -633,9 +670,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
           LN = L->N;
           item_begin = L->item_begin;
           direct = L->direct_store != 0;
+          pair = L->mode == kTcPair;
         }
         if (direct) continue;  // the read-back threads store these rows themselves
-        const int row0 = (item - item_begin) * kTcItemRows + tile * kTcRowsPerTile;
+        const int j = item - item_begin;
+        if (pair && !(j & 1)) continue;  // a pair's first item leaves nothing to store yet
+        const int row0 = (pair ? (j >> 1) : j) * kTcItemRows + tile * kTcRowsPerTile;
         if (!tc_wait(&sm->out_full[tile], n_stores & 1u, abort_flag)) {
           ok = false;
           break;
@@ -748,9 +788,9 @@ int tc_encode(const void* base, int inner, int outer, int box_inner, int box_out
 
 int tc_ntok(int M) { return M <= 16 ? 16 : (M <= 32 ? 32 : 64); }
 
-template <int NTOK>
+template <int NTOK, bool EXTRA = false>
 int tc_launch(const TcParams& p_in, cudaStream_t stream, int* grid_out = nullptr) {
-  auto kern = w4a16_tc_kernel<NTOK>;
+  auto kern = w4a16_tc_kernel<NTOK, EXTRA>;
   constexpr int kFixed = 1024 + kTcHeaderBytes + kTcTiles * tc_out_bytes(NTOK);
   int n_stages = (kMaxSmemBytes - kFixed) / tc_stage_bytes(NTOK);
   if (n_stages > kTcMaxStages) n_stages = kTcMaxStages;
@@ -823,6 +863,9 @@ int tc_describe(const cudalm_b200_linear* ls, int count, TcDesc* out, int* items
     if (!d.direct_store)
       if (int rc = tc_encode(l.y, l.N, l.M, kTcRowsPerTile, ntok, 2, &d.ymap)) return rc;
     d.S = l.scales;
+    d.S2 = nullptr;
+    d.res = nullptr;
+    d.mode = kTcPlain;
     d.y = l.y;
     d.N = l.N;
     d.K = l.K;
@@ -845,6 +888,36 @@ int tc_run_params(TcParams& p, int ntok, cudaStream_t stream, int* grid_out = nu
   if (ntok == 16) return tc_launch<16>(p, stream, grid_out);
   if (ntok == 32) return tc_launch<32>(p, stream, grid_out);
   return tc_launch<64>(p, stream, grid_out);
+}
+
+// One projection with an MLP epilogue: weight2/scales2 non-null -> out = silu(W x) * (W2 x),
+// residual non-null -> out = residual + W x.  UNSUPPORTED unless the outputs can take
+// the TMA store and the second matrix is 16-byte aligned.
+int run_tc_extra(const cudalm_b200_linear& l, const std::uint8_t* weight2,
+                 const std::uint16_t* scales2, const std::uint16_t* residual, cudaStream_t stream) {
+  TcParams p;
+  std::memset(&p, 0, sizeof(p));
+  int ntok = 0;
+  if (int rc = tc_describe(&l, 1, p.inl, &p.total_items, &p.total_cost, &ntok)) return rc;
+  TcDesc& d = p.inl[0];
+  if (d.direct_store) return CUDALM_B200_ERR_UNSUPPORTED;
+  if (weight2) {
+    if (!aligned_to(weight2, 16) || !scales2) return CUDALM_B200_ERR_UNSUPPORTED;
+    if (int rc = tc_encode(weight2, l.K / 8, l.N, 32, kTcRowsPerTile, 0, &d.tmap2)) return rc;
+    d.S2 = scales2;
+    d.mode = kTcPair;
+    p.total_items *= 2;
+    p.total_cost *= 2;
+  } else if (residual) {
+    d.res = residual;
+    d.mode = kTcResidual;
+  }
+  p.n_desc = 1;
+  p.status = device_status_word();
+  if (!p.status) return CUDALM_B200_ERR_CUDA;
+  if (ntok == 16) return tc_launch<16, true>(p, stream);
+  if (ntok == 32) return tc_launch<32, true>(p, stream);
+  return tc_launch<64, true>(p, stream);
 }
 
 // One projection that also records the per-CTA maxima (vocabulary projection).

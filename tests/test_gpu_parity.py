@@ -458,7 +458,8 @@ def _ulp_neighbours(a, b):
 
 
 @pytest.mark.parametrize("N,K,M", [(3584, 1024, 1), (3584, 1024, 8), (1000, 1024, 3), (520, 384, 16),
-                                   (3584, 1024, 40), (100, 256, 2)])
+                                   (3584, 1024, 40), (100, 256, 2), (7168, 1024, 64), (520, 3584, 17),
+                                   (1000, 384, 100), (300, 1024, 33), (36, 256, 20)])
 def test_gate_up_silu_matches_unfused_sequence(eng, orc, N, K, M):
     # fused = the reference's sequence (two projections, then silu_mul with its
     # rounding order) applied to this library's own projection outputs
@@ -469,8 +470,9 @@ def test_gate_up_silu_matches_unfused_sequence(eng, orc, N, K, M):
     gate = eng.W4A16Linear(to_dev(Wg), to_dev(Sg, torch.float16))
     up = eng.W4A16Linear(to_dev(Wu), to_dev(Su, torch.float16))
     xd = to_dev(x, torch.bfloat16)
-    # the fused entry runs on the streaming kernel: take the unfused outputs from it too
-    prev = eng.set_tensor_path_min_rows(1 << 30)
+    # the fused call runs on the tensor-memory kernel from 17 rows when N is a multiple of
+    # 8 (TMA stores), else on the streaming kernel: take the unfused outputs from the same
+    prev = eng.set_tensor_path_min_rows(17 if N % 8 == 0 else 1 << 30)
     try:
         g_y, u_y = eng.gate_up_bf16(gate, up, xd)
     finally:
@@ -492,7 +494,8 @@ def test_gate_up_silu_matches_unfused_sequence(eng, orc, N, K, M):
 
 
 @pytest.mark.parametrize("N,K,M", [(1024, 3584, 1), (1024, 3584, 8), (1024, 2048, 16), (300, 1024, 5),
-                                   (1024, 3584, 24)])
+                                   (1024, 3584, 24), (1024, 3584, 64), (520, 1024, 33), (1000, 384, 130),
+                                   (300, 1024, 40)])
 def test_linear_residual_matches_unfused_sequence(eng, orc, N, K, M):
     import torch
     W, S = raw_weights(N, K, 950 + N)
@@ -501,7 +504,7 @@ def test_linear_residual_matches_unfused_sequence(eng, orc, N, K, M):
     lin = eng.W4A16Linear(to_dev(W), to_dev(S, torch.float16))
     xd, rd = to_dev(x, torch.bfloat16), to_dev(res, torch.bfloat16)
     y = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
-    prev = eng.set_tensor_path_min_rows(1 << 30)
+    prev = eng.set_tensor_path_min_rows(17 if N % 8 == 0 else 1 << 30)
     try:
         eng.batch_int4_gemv_bf16(lin.weight, lin.scale, xd, y)
     finally:
