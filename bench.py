@@ -363,7 +363,7 @@ def bench_cohorts(eng, torch, steps, warmup, rows=(8, 16, 32, 64)):
 
 
 def bench_mlp(eng, torch, steps, warmup):
-    """One layer's MLP at M = 1 and 8 (the fused-epilogue row of the scope table): the reference's five launches
+    """One layer's MLP at M = 1, 8, 32 and 64 (the fused-epilogue row of the scope table): the reference's five launches
     (gate, up, silu_mul, down, add) as this library's two fused ones, against the same
     work through the unfused entry points plus torch elementwise kernels."""
     gen = torch.Generator(device="cuda").manual_seed(SEED + 5)
@@ -376,7 +376,7 @@ def bench_mlp(eng, torch, steps, warmup):
             ws.append(eng.W4A16Linear(*eng.quantize_w4a16(w)))
         layers.append(ws)
     out = {}
-    for M in (1, 8):
+    for M in (1, 8, 32, 64):
         x = torch.randn((M, 1024), generator=gen, device="cuda", dtype=torch.float32).to(torch.bfloat16)
         act = torch.empty((M, 3584), device="cuda", dtype=torch.bfloat16)
         gy, uy = torch.empty_like(act), torch.empty_like(act)

@@ -70,6 +70,7 @@ struct alignas(64) TcDesc {
   CUtensorMap xmap;    // activations as bf16 [M][K], box NTOK rows x 64 values, 128-byte swizzle
   CUtensorMap ymap;    // outputs as bf16 [M][N], box NTOK rows x 128 values
   CUtensorMap tmap2;   // mode kTcPair: the second (up) matrix, same shape as the first (gate)
+  CUtensorMap rmap;    // mode kTcResidual: the residual as bf16 [M][N], box as ymap
   const std::uint16_t* S;
   const std::uint16_t* S2;   // scales of the second matrix
   const std::uint16_t* res;  // mode kTcResidual: residual [M][N]
@@ -78,14 +79,15 @@ struct alignas(64) TcDesc {
   int item_begin;   // first item of this projection in the launch
   int cost_begin;   // stage loads before this projection
   int direct_store;  // outputs cannot take the TMA store (base or row pitch off 16 bytes)
-  // kTcPlain; kTcPair: out = silu(gate x) * (up x), every 256-row block is two
-  // consecutive items (gate rows, then the same rows of up); kTcResidual: out = res + W x
+  // kTcPlain; kTcPair: out = silu(gate x) * (up x): an item is 128 rows, tile 0 works
+  // on the gate matrix and tile 1 on the same rows of the up matrix;
+  // kTcResidual: out = res + W x
   int mode;
 };
 enum : int { kTcPlain = 0, kTcPair = 1, kTcResidual = 2 };
 __host__ __device__ inline int tc_desc_items(const TcDesc& d) {
-  const int blocks = (d.N + kTcItemRows - 1) / kTcItemRows;
-  return d.mode == kTcPair ? 2 * blocks : blocks;
+  return d.mode == kTcPair ? (d.N + kTcRowsPerTile - 1) / kTcRowsPerTile
+                           : (d.N + kTcItemRows - 1) / kTcItemRows;
 }
 
 struct TcParams {
@@ -285,6 +287,9 @@ struct TcSmem {
   // the group's MMAs have completed: its A buffer is free again, its D buffer is full
   std::uint64_t mma_done[kTcTiles][2];
   std::uint64_t d_free[kTcTiles][2];
+  std::uint64_t g_full;   // pair: tile 0's gate outputs are in its buffer
+  std::uint64_t g_free;   // pair: tile 1 has taken them
+  std::uint64_t res_full[kTcTiles];  // residual: the tile's residual values are in its buffer
   std::uint64_t out_free[kTcTiles];  // the tile's output buffer has been read by its last store
   std::uint64_t out_full[kTcTiles];  // every row thread has written the tile's output buffer
   std::uint32_t tmem_base;
@@ -363,6 +368,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
         mbar_init(&sm->mma_done[t][b], 1);
         mbar_init(&sm->d_free[t][b], kTcRowsPerTile);
       }
+      if (t == 0) {
+        mbar_init(&sm->g_full, kTcRowsPerTile);
+        mbar_init(&sm->g_free, kTcRowsPerTile);
+      }
+      mbar_init(&sm->res_full[t], 1);
       mbar_init(&sm->out_free[t], 1);
       mbar_init(&sm->out_full[t], kTcRowsPerTile);
     }
@@ -387,9 +397,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
         if (tbl[mid].cost_begin <= cost) lo = mid; else hi = mid - 1;
       }
       const int per_item = ((tbl[lo].K >> 7) + 1) >> 1;
-      int within = static_cast<int>((cost - tbl[lo].cost_begin + per_item - 1) / per_item);
-      if (tbl[lo].mode == kTcPair) within = (within + 1) & ~1;  // a block's two items stay together
-      return tbl[lo].item_begin + within;
+      return tbl[lo].item_begin + static_cast<int>((cost - tbl[lo].cost_begin + per_item - 1) / per_item);
     };
     it_lo = item_at(static_cast<long long>(blockIdx.x) * p.total_cost / gridDim.x);
     it_hi = item_at(static_cast<long long>(blockIdx.x + 1) * p.total_cost / gridDim.x);
@@ -424,8 +432,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
           pair = L->mode == kTcPair;
         }
         const int j = item - item_begin;
-        const int row0 = (pair ? (j >> 1) : j) * kTcItemRows;
-        const CUtensorMap* wmap = (pair && (j & 1)) ? &L->tmap2 : &L->tmap;
+        // plain: tiles are consecutive 128-row blocks of one matrix; pair: the same
+        // 128 rows of the gate (tile 0) and up (tile 1) matrices
+        const int row0 = pair ? j * kTcRowsPerTile : j * kTcItemRows;
+        const int tile_step = pair ? 0 : kTcRowsPerTile;
         for (int c = 0; c < (G + 1) / 2; ++c) {
           // second and later uses of a stage wait until its previous content is done with
           if (ps_round && !tc_wait(&sm->empty[ps], ps_phase ^ 1u, abort_flag)) {
@@ -440,7 +450,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
                 "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
                 ".L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;" ::"r"(
                     smem_u32(st + t * kTcRowsPerTile * 128)),
-                "l"(wmap), "r"(c * 32), "r"(row0 + t * kTcRowsPerTile),
+                "l"((pair && t == 1) ? &L->tmap2 : &L->tmap), "r"(c * 32), "r"(row0 + t * tile_step),
                 "r"(smem_u32(&sm->full[s])), "l"(policy)
                 : "memory");
           }
@@ -558,7 +568,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
     const std::uint32_t lane_base = static_cast<std::uint32_t>((fw & 3) * 32) << 16;
     const std::uint32_t tile_base = tmem_base + tile * kColsPerTile + lane_base;
     std::uint8_t* outp = outsm + tile * tc_out_bytes(NTOK) + lrow * 2;
-    std::uint32_t eit = 0;  // items finished by this tile
+    std::uint32_t eit = 0;      // items of this tile that went through its output buffer
+    std::uint32_t n_pairs = 0;  // pair items finished
+    std::uint32_t n_res = 0;    // residual items finished
     bool alive = true;
     const TcDesc* L = nullptr;
     std::uint16_t* y = nullptr;
@@ -576,10 +588,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
         mode = L->mode;
       }
       const int j = item - item_begin;
-      const bool second = EXTRA && mode == kTcPair && (j & 1);        // the up matrix of a pair
-      const bool first_of_pair = EXTRA && mode == kTcPair && !(j & 1);  // the gate matrix of a pair
+      const bool pair = EXTRA && mode == kTcPair;
+      const bool second = pair && tile == 1;         // this tile works on the up matrix
+      const bool first_of_pair = pair && tile == 0;  // this tile works on the gate matrix
       const std::uint16_t* S = second ? L->S2 : L->S;
-      const int row0 = ((EXTRA && mode == kTcPair) ? (j >> 1) : j) * kTcItemRows + tile * kTcRowsPerTile;
+      const int row0 = pair ? j * kTcRowsPerTile : j * kTcItemRows + tile * kTcRowsPerTile;
       const int row = row0 + lrow;
       const bool row_ok = row < LN;
       const std::uint16_t* srow = S + static_cast<std::size_t>(row_ok ? row : 0) * G;
@@ -628,28 +641,62 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
       }
       // the tile's rows leave through shared memory and one TMA store, issued by the
       // tile's store warp; the buffer is free again once the previous store has read it
-      if (eit >= 1 && !second) {
+      if (first_of_pair) {
+        // the gate outputs go to tile 0's buffer, where tile 1's thread of the same
+        // row picks them up; the buffer is free once tile 1 has taken the previous ones
+        if (n_pairs >= 1) {
+          const bool ok = tc_wait(&sm->g_free, (n_pairs - 1) & 1u, abort_flag);
+          alive = __all_sync(0xffffffffu, ok);
+          if (!alive) break;
+        }
+#pragma unroll
+        for (int n = 0; n < NTOK; ++n)
+          *reinterpret_cast<std::uint16_t*>(outp + n * (kTcRowsPerTile * 2)) = float_to_bf16_bits(acc[n]);
+        mbar_arrive(&sm->g_full);
+        ++n_pairs;
+        continue;
+      }
+      if (eit >= 1) {
         const bool ok = tc_wait(&sm->out_free[tile], (eit - 1) & 1u, abort_flag);
         alive = __all_sync(0xffffffffu, ok);
         if (!alive) break;
       }
-      if (first_of_pair) {
-        // the gate outputs wait in the tile's buffer, each at its own thread's slots
+      const std::uint8_t* gate_slots = outsm + lrow * 2;  // tile 0's buffer, this thread's row
+      if (second) {
+        const bool ok = tc_wait(&sm->g_full, n_pairs & 1u, abort_flag);
+        alive = __all_sync(0xffffffffu, ok);
+        if (!alive) break;
+      }
+      if (EXTRA && mode == kTcResidual) {
+        // the store lane has brought the tile's residual values into the buffer
+        const bool ok = tc_wait(&sm->res_full[tile], n_res & 1u, abort_flag);
+        ++n_res;
+        alive = __all_sync(0xffffffffu, ok);
+        if (!alive) break;
+#pragma unroll
+        for (int n = 0; n < NTOK; ++n) {
+          std::uint16_t* slot = reinterpret_cast<std::uint16_t*>(outp + n * (kTcRowsPerTile * 2));
+          *slot = add_bits(*slot, float_to_bf16_bits(acc[n]));
+        }
+      } else {
 #pragma unroll
         for (int n = 0; n < NTOK; ++n)
           *reinterpret_cast<std::uint16_t*>(outp + n * (kTcRowsPerTile * 2)) = float_to_bf16_bits(acc[n]);
-        continue;
       }
-#pragma unroll
-      for (int n = 0; n < NTOK; ++n) {
-        std::uint16_t* slot = reinterpret_cast<std::uint16_t*>(outp + n * (kTcRowsPerTile * 2));
-        std::uint16_t o = float_to_bf16_bits(acc[n]);
-        if (EXTRA && second) {
-          o = silu_mul_bits(bf16_bits_to_float(*slot), o);
-        } else if (EXTRA && mode == kTcResidual) {
-          if (row_ok && n < LM) o = add_bits(__ldg(L->res + static_cast<std::size_t>(n) * LN + row), o);
+      // The silu epilogue works on the thread's own slots of the buffer in a rolled
+      // loop: unrolled 64 times, its code slows the whole kernel down.
+      if (EXTRA && second) {
+#pragma unroll 2
+        for (int n = 0; n < NTOK; ++n) {
+          std::uint16_t* slot = reinterpret_cast<std::uint16_t*>(outp + n * (kTcRowsPerTile * 2));
+          const std::uint16_t g_bits =
+              *reinterpret_cast<const std::uint16_t*>(gate_slots + n * (kTcRowsPerTile * 2));
+          *slot = silu_mul_bits(bf16_bits_to_float(g_bits), *slot);
         }
-        *slot = o;
+      }
+      if (second) {
+        mbar_arrive(&sm->g_free);
+        ++n_pairs;
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       mbar_arrive(&sm->out_full[tile]);
@@ -674,8 +721,23 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
         }
         if (direct) continue;  // the read-back threads store these rows themselves
         const int j = item - item_begin;
-        if (pair && !(j & 1)) continue;  // a pair's first item leaves nothing to store yet
-        const int row0 = (pair ? (j >> 1) : j) * kTcItemRows + tile * kTcRowsPerTile;
+        if (pair && tile == 0) continue;  // a pair's outputs all leave through tile 1's buffer
+        const int row0 = pair ? j * kTcRowsPerTile : j * kTcItemRows + tile * kTcRowsPerTile;
+        if (EXTRA && L->mode == kTcResidual) {
+          // the buffer is free here (the previous store has read it): fetch the tile's
+          // residual values into it while the item is being computed
+          std::uint8_t* buf = outsm + tile * tc_out_bytes(NTOK);
+          if (row0 < LN) {
+            mbar_arrive_expect_tx(&sm->res_full[tile], tc_out_bytes(NTOK));
+            asm volatile(
+                "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+                " [%0], [%1, {%2, %3}], [%4];" ::"r"(smem_u32(buf)),
+                "l"(&L->rmap), "r"(row0), "r"(0), "r"(smem_u32(&sm->res_full[tile]))
+                : "memory");
+          } else {
+            mbar_arrive_expect_tx(&sm->res_full[tile], 0);
+          }
+        }
         if (!tc_wait(&sm->out_full[tile], n_stores & 1u, abort_flag)) {
           ok = false;
           break;
@@ -906,9 +968,11 @@ int run_tc_extra(const cudalm_b200_linear& l, const std::uint8_t* weight2,
     if (int rc = tc_encode(weight2, l.K / 8, l.N, 32, kTcRowsPerTile, 0, &d.tmap2)) return rc;
     d.S2 = scales2;
     d.mode = kTcPair;
-    p.total_items *= 2;
-    p.total_cost *= 2;
+    p.total_items = tc_desc_items(d);
+    p.total_cost = p.total_items * (((l.K >> 7) + 1) >> 1);
   } else if (residual) {
+    if (!aligned_to(residual, 16)) return CUDALM_B200_ERR_UNSUPPORTED;
+    if (int rc = tc_encode(residual, l.N, l.M, kTcRowsPerTile, ntok, 2, &d.rmap)) return rc;
     d.res = residual;
     d.mode = kTcResidual;
   }
