@@ -200,6 +200,10 @@ __device__ __forceinline__ std::uint16_t float_to_bf16_bits(float f) {
 
 #ifdef __CUDACC__
 // Epilogues of the MLP, in CUDALM's rounding order.
+__device__ __forceinline__ std::uint16_t silu_bits(std::uint16_t gate_bits) {
+  const float g = bf16_bits_to_float(gate_bits);
+  return float_to_bf16_bits(__fdiv_rn(g, 1.0f + expf(-g)));
+}
 __device__ __forceinline__ std::uint16_t silu_mul_bits(float g, std::uint16_t up_bits) {
   const float s = bf16_bits_to_float(float_to_bf16_bits(__fdiv_rn(g, 1.0f + expf(-g))));
   return float_to_bf16_bits(s * bf16_bits_to_float(up_bits));

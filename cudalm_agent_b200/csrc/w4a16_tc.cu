@@ -652,6 +652,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
 #pragma unroll
         for (int n = 0; n < NTOK; ++n)
           *reinterpret_cast<std::uint16_t*>(outp + n * (kTcRowsPerTile * 2)) = float_to_bf16_bits(acc[n]);
+        // silu of the rounded gate value, itself rounded, as CUDALM's epilogue forms it;
+        // a rolled loop over the thread's own slots keeps the kernel's code small, and
+        // tile 1's threads are left with one multiplication per value
+#pragma unroll 2
+        for (int n = 0; n < NTOK; ++n) {
+          std::uint16_t* slot = reinterpret_cast<std::uint16_t*>(outp + n * (kTcRowsPerTile * 2));
+          *slot = silu_bits(*slot);
+        }
         mbar_arrive(&sm->g_full);
         ++n_pairs;
         continue;
@@ -683,15 +691,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
         for (int n = 0; n < NTOK; ++n)
           *reinterpret_cast<std::uint16_t*>(outp + n * (kTcRowsPerTile * 2)) = float_to_bf16_bits(acc[n]);
       }
-      // The silu epilogue works on the thread's own slots of the buffer in a rolled
-      // loop: unrolled 64 times, its code slows the whole kernel down.
       if (EXTRA && second) {
-#pragma unroll 2
+#pragma unroll 8
         for (int n = 0; n < NTOK; ++n) {
           std::uint16_t* slot = reinterpret_cast<std::uint16_t*>(outp + n * (kTcRowsPerTile * 2));
-          const std::uint16_t g_bits =
+          const std::uint16_t s_bits =
               *reinterpret_cast<const std::uint16_t*>(gate_slots + n * (kTcRowsPerTile * 2));
-          *slot = silu_mul_bits(bf16_bits_to_float(g_bits), *slot);
+          *slot = float_to_bf16_bits(bf16_bits_to_float(s_bits) * bf16_bits_to_float(*slot));
         }
       }
       if (second) {

@@ -135,7 +135,8 @@ CUDALM_B200_API int cudalm_b200_gate_up_bf16(const uint8_t* gate_weight,
  * bf16 outputs of the gate and up projections of x [M, K]; replaces the two
  * projections and qwen35_silu_mul (CUDALM include/cudalm/kernels/qwen35_kernels.h:137-155,
  * src/kernels/qwen35_kernels.cu:459-476; call sites src/runtime/qwen35_deltanet.cpp:236-247,
- * src/runtime/qwen35_full_attention.cpp:317-331) with one launch per 16 rows.
+ * src/runtime/qwen35_full_attention.cpp:317-331) with one launch per 16 rows, or per
+ * 64 rows when M is at least the tensor path's smallest row count.
  * linear_residual: y[m][n] = bf16(float(residual[m][n]) + float(p)) with p the bf16
  * output of the projection; replaces the down / o_proj / out_proj projection and the
  * qwen35_add that follows it (src/kernels/qwen35_kernels.cu:442-456;
