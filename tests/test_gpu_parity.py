@@ -640,3 +640,48 @@ def test_group_of_very_many_tiny_projections(eng, orc):
         single = eng.int4_gemv_bf16(lin.weight, lin.scale, x)
         assert torch.equal(single, y), int(i)
     grp.close()
+
+
+@pytest.mark.parametrize("M", [1, 8, 32])
+def test_decode_step_replays_from_a_cuda_graph(eng, orc, M):
+    """The entries only enqueue work on the caller's stream (no allocation, no
+    synchronisation), as CUDALM's do (src/runtime/qwen35_model.cpp:202-210): an MLP
+    followed by the vocabulary pick is captured once and replayed on new inputs,
+    and every replay equals the eager calls bit for bit."""
+    import torch
+    K, N, V = 1024, 3584, 4096
+    gate, up, down, head = [eng.W4A16Linear(to_dev(W), to_dev(S, torch.float16))
+                            for _, W, S in (make_weights(orc, N, K, BASE_SEED + 900),
+                                            make_weights(orc, N, K, BASE_SEED + 901),
+                                            make_weights(orc, K, N, BASE_SEED + 902),
+                                            make_weights(orc, V, K, BASE_SEED + 903))]
+    lm = eng.LmHead(head, top_k=50, max_rows=32)
+    h = to_dev(make_x(orc, (M, K), BASE_SEED + 904), torch.bfloat16)
+    act = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    out = torch.empty((M, K), dtype=torch.bfloat16, device="cuda")
+
+    def step():
+        eng.gate_up_silu_bf16(gate, up, h, act)
+        eng.linear_residual_bf16(down, act, h, out)
+        return lm.forward(out)
+
+    def snapshot(res):
+        torch.cuda.synchronize()
+        return [t.clone() for t in (out, *res)]
+
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        step()  # the first call of each kernel sets its attributes: keep it out of the capture
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            res = step()
+    for trial in range(3):
+        h.copy_(to_dev(make_x(orc, (M, K), BASE_SEED + 910 + trial), torch.bfloat16))
+        want = snapshot(step())
+        for t in (out, *res):
+            t.zero_()
+        graph.replay()
+        got = snapshot(res)
+        for a, b in zip(want, got):
+            assert torch.equal(a, b), f"replay {trial} differs from the eager calls"
