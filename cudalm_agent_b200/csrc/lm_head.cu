@@ -58,7 +58,7 @@ __device__ __forceinline__ std::uint16_t composite_bits(std::uint64_t c) {
 }
 
 struct Workspace {
-  int* counts;              // [kMaxPassRows]
+  int* counts;              // [kMaxPassRows] candidates per row, then [kMaxPassRows] scan tickets per row
   float* cta_max;           // [kMaxCtas][rows]
   std::uint64_t* cand;      // [rows][kCandCap]
   std::uint16_t* logits;    // [rows][N] when the caller gave no logits buffer
@@ -82,19 +82,14 @@ size_t workspace_layout(int N, int rows, bool need_logits, unsigned char* base, 
 }
 
 // ---------------------------------------------------------------------------
-// collect: grid (slices, rows).  Each CTA derives the row's bound from the
-// per-CTA maxima and scans its slice of the row's logits.
+// The scan of one CTA of grid (slices, rows): the row's bound from the per-CTA
+// maxima (smax: kMaxCtas floats of shared memory), then the CTA's slice of the
+// row's logits; values at or above the bound become candidates.
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(256)
-lm_head_collect_kernel(const std::uint16_t* __restrict__ logits, int N, int rows,
-                       const float* __restrict__ cta_max, int ncta, int k, int id_offset,
-                       int* __restrict__ counts, std::uint64_t* __restrict__ cand) {
-  __shared__ float smax[kMaxCtas];
+__device__ void scan_slice(const std::uint16_t* __restrict__ logits, int N, int rows,
+                           const float* __restrict__ cta_max, int ncta, int k, int id_offset,
+                           int* counts, std::uint64_t* cand, float* smax) {
   __shared__ float bound;
-  // launched with programmatic stream serialisation: the grid may start while
-  // its predecessor drains, and must wait for it before reading its results
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int m = blockIdx.y;
   const int tid = threadIdx.x;
   for (int i = tid; i < ncta; i += blockDim.x) smax[i] = cta_max[static_cast<size_t>(i) * rows + m];
@@ -115,19 +110,50 @@ lm_head_collect_kernel(const std::uint16_t* __restrict__ logits, int N, int rows
   __syncthreads();
   const float b = bound;
   const std::uint16_t* row = logits + static_cast<size_t>(m) * N;
-  const long long per = (static_cast<long long>(N) + gridDim.x - 1) / gridDim.x;
+  // slices are whole 16-byte vectors of the row, so that a row on a 16-byte
+  // boundary is read eight values at a time, several loads in flight per thread
+  long long per = (static_cast<long long>(N) + gridDim.x - 1) / gridDim.x;
+  per = (per + 7) & ~7ll;
   const long long lo = per * blockIdx.x;
   long long hi = lo + per;
   if (hi > N) hi = N;
-  for (long long i = lo + tid; i < hi; i += blockDim.x) {
-    const std::uint16_t bits = row[i];
+  if (lo >= hi) return;  // (uniform over the CTA)
+  auto offer = [&](std::uint16_t bits, long long i) {
     if (bf16_bits_to_float(bits) >= b) {
       const int pos = atomicAdd(&counts[m], 1);
       if (pos < kCandCap)
         cand[static_cast<size_t>(m) * kCandCap + pos] =
             make_composite(bits, static_cast<std::uint32_t>(id_offset) + static_cast<std::uint32_t>(i));
     }
+  };
+  long long done = lo;
+  if ((reinterpret_cast<std::uintptr_t>(row) & 15u) == 0) {
+    const uint4* vrow = reinterpret_cast<const uint4*>(row + lo);
+    const long long nv = (hi - lo) >> 3;
+    constexpr int kInFlight = 8;
+    for (long long v0 = tid; v0 < nv; v0 += static_cast<long long>(kInFlight) * blockDim.x) {
+      uint4 q[kInFlight];
+#pragma unroll
+      for (int u = 0; u < kInFlight; ++u) {
+        const long long v = v0 + static_cast<long long>(u) * blockDim.x;
+        q[u] = v < nv ? __ldg(vrow + v) : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int u = 0; u < kInFlight; ++u) {
+        const long long v = v0 + static_cast<long long>(u) * blockDim.x;
+        if (v >= nv) break;
+        const std::uint32_t w[4] = {q[u].x, q[u].y, q[u].z, q[u].w};
+        const long long i0 = lo + (v << 3);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          offer(static_cast<std::uint16_t>(w[e] & 0xFFFFu), i0 + 2 * e);
+          offer(static_cast<std::uint16_t>(w[e] >> 16), i0 + 2 * e + 1);
+        }
+      }
+    }
+    done = lo + (nv << 3);
   }
+  for (long long i = done + tid; i < hi; i += blockDim.x) offer(row[i], i);
 }
 
 // Bitonic sort, descending, of n (a power of two) composites in shared memory.
@@ -188,22 +214,26 @@ struct SelectArgs {
   std::uint16_t* topk_val;
 };
 
-__global__ void __launch_bounds__(kSelectThreads)
-lm_head_select_kernel(const SelectArgs a) {
-  __shared__ std::uint64_t buf[kCandCap];
-  __shared__ int scratch[kSelectThreads / 32];
-  __shared__ int s_take;
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-  const int m = blockIdx.x;
-  const int tid = threadIdx.x;
+struct SelectSmem {
+  std::uint64_t buf[kCandCap];
+  int scratch[kSelectThreads / 32];
+  int take;
+};
+
+// The pick of row m by one CTA of kSelectThreads threads.
+__device__ void select_row(const SelectArgs& a, int m, int tid, SelectSmem& sm) {
+  std::uint64_t* buf = sm.buf;
+  int* scratch = sm.scratch;
+  int& s_take = sm.take;
   int n = 0;
   bool overflow = false;
   if (a.cand) {
-    n = a.counts[m];
+    // written by other CTAs of the same launch when the scan's last CTA picks: read from L2
+    n = __ldcg(a.counts + m);
     overflow = n > kCandCap;
     if (!overflow)
-      for (int i = tid; i < n; i += kSelectThreads) buf[i] = a.cand[static_cast<size_t>(m) * kCandCap + i];
+      for (int i = tid; i < n; i += kSelectThreads)
+        buf[i] = __ldcg(a.cand + static_cast<size_t>(m) * kCandCap + i);
   } else {
     n = a.n_lists * a.list_k;  // host guarantees n <= kCandCap
     for (int i = tid; i < n; i += kSelectThreads) {
@@ -266,12 +296,27 @@ lm_head_select_kernel(const SelectArgs a) {
     __syncthreads();
   }
 
-  // pad to a power of two (at least 64) with zeros, which sort last
-  int P = 64;
-  while (P < n) P <<= 1;
   __syncthreads();
-  for (int i = n + tid; i < P; i += kSelectThreads) buf[i] = 0ull;
-  bitonic_sort_desc(buf, P, tid, kSelectThreads);
+  if (n <= kSelectThreads) {
+    // the usual case, a few dozen candidates: every thread ranks its own candidate by
+    // counting (equal composites, which only padding produces, rank in slot order)
+    const std::uint64_t mine = tid < n ? buf[tid] : 0ull;
+    int rank = 0;
+    if (tid < n)
+      for (int j = 0; j < n; ++j) {
+        const std::uint64_t other = buf[j];
+        rank += (other > mine) || (other == mine && j < tid);
+      }
+    __syncthreads();
+    if (tid < n) buf[rank] = mine;
+    __syncthreads();
+  } else {
+    // pad to a power of two with zeros, which sort last
+    int P = 64;
+    while (P < n) P <<= 1;
+    for (int i = n + tid; i < P; i += kSelectThreads) buf[i] = 0ull;
+    bitonic_sort_desc(buf, P, tid, kSelectThreads);
+  }
 
   const int kk = a.k;
   for (int j = tid; j < kk; j += kSelectThreads) {
@@ -282,6 +327,40 @@ lm_head_select_kernel(const SelectArgs a) {
         real ? composite_bits(c) : static_cast<std::uint16_t>(0xFF80u);
     if (j == 0 && a.argmax_out) a.argmax_out[m] = real ? static_cast<std::int32_t>(composite_id(c)) : -1;
   }
+}
+
+__global__ void __launch_bounds__(kSelectThreads)
+lm_head_select_kernel(const SelectArgs a) {
+  __shared__ SelectSmem sm;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  select_row(a, blockIdx.x, threadIdx.x, sm);
+}
+
+// ---------------------------------------------------------------------------
+// scan + pick: grid (slices, rows).  Each CTA derives the row's bound from the
+// per-CTA maxima and scans its slice of the row's logits for candidates; the
+// CTA that finishes a row's scan last (a ticket per row) picks the row's
+// tokens, so the call needs no third launch.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(kSelectThreads)
+lm_head_scan_pick_kernel(const std::uint16_t* __restrict__ logits, int N, int rows,
+                         const float* __restrict__ cta_max, int ncta, int k, int id_offset,
+                         int* counts, int* tickets, std::uint64_t* cand, const SelectArgs a) {
+  __shared__ SelectSmem sm;
+  __shared__ int s_last;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int m = blockIdx.y;
+  const int tid = threadIdx.x;
+  scan_slice(logits, N, rows, cta_max, ncta, k, id_offset, counts, cand, reinterpret_cast<float*>(sm.buf));
+  __threadfence();  // this CTA's candidates and count are visible before its ticket
+  __syncthreads();
+  if (tid == 0) s_last = atomicAdd(&tickets[m], 1) == static_cast<int>(gridDim.x) - 1;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  select_row(a, m, tid, sm);
 }
 
 __global__ void zero_counts_kernel(int* counts, int n) {
@@ -361,27 +440,23 @@ int cudalm_b200_lm_head_topk(const uint8_t* weight, const uint16_t* scales, cons
     int ncta = 0;
     if (staged) {
       // the projection's first CTA also clears the candidate counters
-      if (int rc = run_linear_with_cta_max(l, ws.cta_max, &ncta, st, ws.counts, kMaxPassRows)) return rc;
+      if (int rc = run_linear_with_cta_max(l, ws.cta_max, &ncta, st, ws.counts, 2 * kMaxPassRows)) return rc;
       if (ncta > kMaxCtas) return CUDALM_B200_ERR_TOO_LARGE;
     } else {
       // no per-CTA maxima on the slow path: every logit is a candidate, and a
       // row longer than the candidate list takes the exact search
-      zero_counts_kernel<<<1, 64, 0, st>>>(ws.counts, kMaxPassRows);
+      zero_counts_kernel<<<1, 64, 0, st>>>(ws.counts, 2 * kMaxPassRows);
       if (int rc = check_launch()) return rc;
       if (int rc = run_linear_any(l, st)) return rc;
       ncta = 0;
     }
 
+    // every CTA first ranks the per-CTA maxima to find the row's bound, so the scan is
+    // cut into few, long slices: about two CTAs per SM over all rows
     int slices = (N + 4095) / 4096;
-    const int cap = num_sms() * 8 / rows > 1 ? num_sms() * 8 / rows : 1;
+    const int cap = (2 * num_sms() + rows - 1) / rows;
     if (slices > cap) slices = cap;
     if (slices < 1) slices = 1;
-    if (int rc = launch_after(lm_head_collect_kernel, dim3(slices, rows), dim3(256), st,
-                              static_cast<const std::uint16_t*>(logits), N, rows,
-                              static_cast<const float*>(ws.cta_max), ncta, top_k, id_offset, ws.counts,
-                              ws.cand))
-      return rc;
-
     SelectArgs a;
     std::memset(&a, 0, sizeof(a));
     a.cand = ws.cand;
@@ -394,7 +469,11 @@ int cudalm_b200_lm_head_topk(const uint8_t* weight, const uint16_t* scales, cons
     a.argmax_out = argmax_out ? argmax_out + m0 : nullptr;
     a.topk_idx = topk_idx + static_cast<size_t>(m0) * top_k;
     a.topk_val = topk_val + static_cast<size_t>(m0) * top_k;
-    if (int rc = launch_after(lm_head_select_kernel, dim3(rows), dim3(kSelectThreads), st, a)) return rc;
+    if (int rc = launch_after(lm_head_scan_pick_kernel, dim3(slices, rows), dim3(kSelectThreads), st,
+                              static_cast<const std::uint16_t*>(logits), N, rows,
+                              static_cast<const float*>(ws.cta_max), ncta, top_k, id_offset, ws.counts,
+                              ws.counts + kMaxPassRows, ws.cand, a))
+      return rc;
   }
   return CUDALM_B200_OK;
 }

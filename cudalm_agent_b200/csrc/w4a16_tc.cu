@@ -298,13 +298,27 @@ struct TcSmem {
 };
 constexpr int kTcHeaderBytes = 1024;
 
-// Order-preserving map float -> uint32 (and back) so that integer max gives the float max.
-__device__ __forceinline__ std::uint32_t float_key(float f) {
-  const std::uint32_t b = __float_as_uint(f);
-  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+// Order-preserving map of bf16 bits to a 16-bit key (and back to the float value), so
+// that an integer max gives the float max.
+__device__ __forceinline__ std::uint32_t bf16_key(std::uint32_t bits) {
+  const std::uint32_t b = bits & 0xFFFFu;
+  return (b & 0x8000u) ? (~b & 0xFFFFu) : (b | 0x8000u);
+}
+constexpr std::uint32_t kKeyMinusInf = 0x007Fu;  // bf16_key(0xFF80)
+// two floats rounded to nearest even into one word of bf16 values (lo in the low half)
+__device__ __forceinline__ std::uint32_t pack_bf16x2(float lo, float hi) {
+  std::uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+__device__ __forceinline__ std::uint32_t max_bf16x2(std::uint32_t a, std::uint32_t b) {
+  std::uint32_t r;
+  asm("max.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
 }
 __device__ __forceinline__ float key_float(std::uint32_t k) {
-  return __uint_as_float((k & 0x80000000u) ? (k & 0x7FFFFFFFu) : ~k);
+  const std::uint32_t bits = (k & 0x8000u) ? (k & 0x7FFFu) : (~k & 0xFFFFu);
+  return __uint_as_float(bits << 16);
 }
 static_assert(sizeof(TcSmem) <= kTcHeaderBytes, "barrier block too large");
 
@@ -379,7 +393,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
     sm->abort_flag = 0;
     mbar_init_fence();
   }
-  if (tid < 64) sm->row_max[tid] = float_key(-INFINITY);
+  if (tid < 64) sm->row_max[tid] = kKeyMinusInf;
   if (warp == 0) tmem_alloc(&sm->tmem_base, 512);
   tc_fence_before();
   __syncthreads();
@@ -622,12 +636,44 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
       }
       if (!alive) break;
       if (p.cta_max != nullptr) {
-        // one warp-wide integer max per activation row, then one shared-memory atomic
+        // Maxima over the warp's 32 weight rows for every activation row at once: the
+        // outputs are rounded to bf16 two to a word, and a butterfly of packed bf16
+        // maxima that halves the words a lane holds at each step leaves every word
+        // reduced over the warp on one lane, which merges it into the CTA's table.
+        constexpr int V = NTOK / 2;
+        std::uint32_t kv[V];
 #pragma unroll
-        for (int n = 0; n < NTOK; ++n) {
-          const float v = row_ok ? bf16_bits_to_float(float_to_bf16_bits(acc[n])) : -INFINITY;
-          const std::uint32_t k = __reduce_max_sync(0xffffffffu, float_key(v));
-          if (lane == 0 && n < LM) atomicMax(&sm->row_max[n], k);
+        for (int i = 0; i < V; ++i)
+          kv[i] = row_ok ? pack_bf16x2(acc[2 * i], acc[2 * i + 1]) : 0xFF80FF80u;  // -inf, -inf
+        int word = 0;  // which word this lane ends up holding
+#pragma unroll
+        for (int s = 0; s < 5; ++s) {
+          const int off = 16 >> s;
+          const int cnt = (V >> s) > 1 ? (V >> s) : 1;
+          if (cnt > 1) {
+            const int half = cnt / 2;
+            const bool upper = (lane & off) != 0;
+#pragma unroll
+            for (int i = 0; i < half; ++i) {
+              const std::uint32_t keep = upper ? kv[i + half] : kv[i];
+              const std::uint32_t send = upper ? kv[i] : kv[i + half];
+              kv[i] = max_bf16x2(keep, __shfl_xor_sync(0xffffffffu, send, off));
+            }
+            if (upper) word += half;
+          } else {
+            kv[0] = max_bf16x2(kv[0], __shfl_xor_sync(0xffffffffu, kv[0], off));
+          }
+        }
+        // V = 32: every lane holds a word of its own and merges both halves; fewer
+        // words: 32 / V lanes hold the same word and the first two take a half each
+        constexpr int kCopies = 32 / V;
+        const int copy = lane & (kCopies - 1);
+        if (kCopies == 1) {
+          if (2 * word < LM) atomicMax(&sm->row_max[2 * word], bf16_key(kv[0] & 0xFFFFu));
+          if (2 * word + 1 < LM) atomicMax(&sm->row_max[2 * word + 1], bf16_key(kv[0] >> 16));
+        } else if (copy < 2) {
+          const int n = 2 * word + copy;
+          if (n < LM) atomicMax(&sm->row_max[n], bf16_key(copy ? (kv[0] >> 16) : (kv[0] & 0xFFFFu)));
         }
       }
       if (direct) {
