@@ -295,22 +295,41 @@ def bench_lm_head(eng, torch, dist, rank, world, steps, warmup):
     # a second copy of the shard so consecutive steps do not reuse L2 lines
     lin2 = eng.W4A16Linear(lin.weight.clone(), lin.scale.clone())
     for M in (1, 32):
-        heads = [eng.VocabParallelLmHead(eng.LmHead(l, TOP_K, id_offset=lo, max_rows=M))
-                 for l in (lin, lin2)]
         x = torch.randn((M, HIDDEN), generator=gen, device="cuda", dtype=torch.float32)
         x = (x / x.pow(2).mean(dim=1, keepdim=True).sqrt()).to(torch.bfloat16)
-        res = {}
+        # the candidate lists cross NVLink inside the merge kernel ("peer"); the one
+        # all-gather + merge ("collective") is timed beside it and must give the same pick
+        modes = ["peer", "collective"] if world > 1 else ["collective"]
+        entry = {}
+        picks = {}
+        for mode in modes:
+            heads = [eng.VocabParallelLmHead(eng.LmHead(l, TOP_K, id_offset=lo, max_rows=M),
+                                             exchange=mode) for l in (lin, lin2)]
+            res = {}
 
-        def step(i):
-            res["out"] = heads[i % 2].forward(x)
+            def step(i):
+                res["out"] = heads[i % 2].forward(x)
 
-        total_ms, _ = time_steps(torch, step, steps, warmup, dist)
-        total_ms = max_over_ranks(torch, dist, total_ms)
-        out[f"M{M}"] = {"rows_per_s": M * steps / (total_ms * 1e-3),
-                        "us_per_call": total_ms * 1e3 / steps,
-                        "shard_rows": hi - lo,
-                        "shard_gbps": (lin.N * lin.K // 2 + lin.N * 16) * steps / (total_ms * 1e-3) / 1e9,
-                        "argmax_row0": int(res["out"][0][0].item())}
+            total_ms, _ = time_steps(torch, step, steps, warmup, dist)
+            total_ms = max_over_ranks(torch, dist, total_ms)
+            picks[mode] = [t.clone() for t in res["out"]]
+            for h in heads:
+                h.close()
+            if mode == modes[0]:
+                entry = {"rows_per_s": M * steps / (total_ms * 1e-3),
+                         "us_per_call": total_ms * 1e3 / steps,
+                         "shard_rows": hi - lo,
+                         "shard_gbps": (lin.N * lin.K // 2 + lin.N * 16) * steps / (total_ms * 1e-3) / 1e9,
+                         "argmax_row0": int(res["out"][0][0].item()),
+                         "exchange": ("peer memory, inside the merge kernel" if mode == "peer"
+                                      else "one all-gather" if world > 1 else "none")}
+            else:
+                entry["collective_us_per_call"] = total_ms * 1e3 / steps
+                same = all(torch.equal(a, b) for a, b in zip(picks[modes[0]], picks[mode]))
+                if not same:
+                    raise RuntimeError("peer exchange and all-gather picked different tokens")
+                entry["same_pick_as_collective"] = True
+        out[f"M{M}"] = entry
     return out
 
 

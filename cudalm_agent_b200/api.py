@@ -88,6 +88,13 @@ SIGNATURES = {
                                              _vp, _vp]),
     "cudalm_b200_topk_merge": (_ci, [_vp, _vp, _ci, _ci, _ci, _vp, _vp, _vp, _vp]),
     "cudalm_b200_topk_merge_packed": (_ci, [_vp, _ci, _ci, _ci, _ci, _ci, _vp, _vp, _vp, _vp]),
+    "cudalm_b200_exchange_bytes": (ctypes.c_size_t, [_ci, _ci]),
+    "cudalm_b200_exchange_create": (_ci, [ctypes.c_size_t, ctypes.POINTER(_vp), _vp]),
+    "cudalm_b200_exchange_open": (_ci, [_vp, ctypes.POINTER(_vp)]),
+    "cudalm_b200_exchange_close": (_ci, [_vp]),
+    "cudalm_b200_exchange_destroy": (_ci, [_vp]),
+    "cudalm_b200_topk_exchange_merge": (_ci, [_vp, ctypes.POINTER(_vp), _ci, _ci, _ci, _ci, _ci, _ci,
+                                             _vp, _vp, _vp, _vp]),
     "cudalm_b200_quantize_w4a16": (_ci, [_vp, _ci, _ci, _vp, _vp, _vp]),
     "cudalm_b200_set_tensor_path_min_rows": (_ci, [_ci]),
     "cudalm_b200_kernel_regs": (_ci, [ctypes.c_char_p]),

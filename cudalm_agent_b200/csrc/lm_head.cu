@@ -239,8 +239,9 @@ __device__ void select_row(const SelectArgs& a, int m, int tid, SelectSmem& sm) 
     for (int i = tid; i < n; i += kSelectThreads) {
       const int l = i / a.list_k, j = i - l * a.list_k;
       const size_t within = static_cast<size_t>(m) * a.list_k + j;
-      const std::int32_t id = a.list_idx[static_cast<size_t>(l) * a.idx_stride + within];
-      const std::uint16_t v = a.list_val[static_cast<size_t>(l) * a.val_stride + within];
+      // read from L2: a peer GPU may have written the lists into this GPU's memory
+      const std::int32_t id = __ldcg(a.list_idx + static_cast<size_t>(l) * a.idx_stride + within);
+      const std::uint16_t v = __ldcg(a.list_val + static_cast<size_t>(l) * a.val_stride + within);
       buf[i] = id < 0 ? 0ull : make_composite(v, static_cast<std::uint32_t>(id));
     }
   }
@@ -606,3 +607,217 @@ extern "C" int cudalm_b200_topk_merge_packed(const int32_t* gathered, int n_list
   lm_head_select_kernel<<<M, kSelectThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
   return check_launch();
 }
+
+// ---------------------------------------------------------------------------
+// Candidate exchange over peer memory, fused with the merge.
+//
+// Vocabulary-parallel ranks on one node each hold an exchange buffer that the
+// others map (CUDA IPC).  One kernel per rank, one CTA per activation row:
+// the CTA stores the row's local candidates (k ids, k values) into every rank's
+// buffer over NVLink, publishes a per-row epoch flag on every rank, waits (with
+// a time limit) until every rank's flag for the row has reached the epoch, and
+// merges the lists that have arrived in its own buffer.  Lists are double
+// buffered by epoch parity: a rank can be at most one call ahead of a peer
+// that is still merging, since the call after needs that peer's next flag.
+// Epochs live on the device (one per row), so a captured call replays.
+//
+// Buffer layout in 32-bit words: lists [2][world][words_per_list], then flags
+// [world][kMaxPassRows], then this rank's epochs [kMaxPassRows].
+// ---------------------------------------------------------------------------
+namespace cb200 {
+namespace {
+
+constexpr int kMaxPeers = 8;
+constexpr long long kExchangeWaitNs = 2000000000ll;  // 2 s
+
+struct ExchangeArgs {
+  std::uint32_t* bufs[kMaxPeers];  // every rank's buffer as mapped here; bufs[rank] is the local one
+  const std::int32_t* local_packed;
+  int rank, world, words_per_list, rows_cap, M, k;
+  std::int32_t* argmax_out;
+  std::int32_t* topk_idx;
+  std::uint16_t* topk_val;
+  int* status;
+};
+
+__device__ __forceinline__ void st_release_sys(std::uint32_t* p, std::uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ std::uint32_t ld_acquire_sys(const std::uint32_t* p) {
+  std::uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ long long global_ns() {
+  long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+__global__ void __launch_bounds__(kSelectThreads)
+topk_exchange_merge_kernel(const ExchangeArgs e) {
+  __shared__ SelectSmem sm;
+  __shared__ int s_ok;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int m = blockIdx.x;
+  const int tid = threadIdx.x;
+  const size_t lists_words = static_cast<size_t>(e.world) * e.words_per_list;
+  std::uint32_t* mine = e.bufs[e.rank];
+  std::uint32_t* my_flags = mine + 2 * lists_words;
+  std::uint32_t* my_epochs = my_flags + static_cast<size_t>(e.world) * kMaxPassRows;
+  const std::uint32_t epoch = my_epochs[m] + 1u;  // written only by this row's CTA, one call earlier
+  const size_t parity_off = (epoch & 1u) * lists_words;
+
+  // (1) this rank's candidates of row m into slot [rank] of every rank's buffer
+  const int k = e.k;
+  const size_t val_base = static_cast<size_t>(e.rows_cap) * k;  // in words: values start here
+  const std::int32_t* src_idx = e.local_packed + static_cast<size_t>(m) * k;
+  const std::uint16_t* src_val =
+      reinterpret_cast<const std::uint16_t*>(e.local_packed + val_base) + static_cast<size_t>(m) * k;
+  for (int i = tid; i < e.world * 2 * k; i += kSelectThreads) {
+    const int p = i / (2 * k), j = i - p * 2 * k;
+    std::uint32_t* slot = e.bufs[p] + parity_off + static_cast<size_t>(e.rank) * e.words_per_list;
+    if (j < k)
+      slot[static_cast<size_t>(m) * k + j] = static_cast<std::uint32_t>(src_idx[j]);
+    else
+      (reinterpret_cast<std::uint16_t*>(slot + val_base))[static_cast<size_t>(m) * k + (j - k)] = src_val[j - k];
+  }
+  __threadfence_system();
+  __syncthreads();
+  // (2) the row's epoch on every rank, (3) wait for every rank's
+  if (tid == 0) s_ok = 1;
+  __syncthreads();
+  if (tid < e.world) {
+    std::uint32_t* peer_flags = e.bufs[tid] + 2 * lists_words;
+    st_release_sys(peer_flags + static_cast<size_t>(e.rank) * kMaxPassRows + m, epoch);
+    const std::uint32_t* f = my_flags + static_cast<size_t>(tid) * kMaxPassRows + m;
+    const long long t0 = global_ns();
+    bool ok = true;
+    while (static_cast<std::int32_t>(ld_acquire_sys(f) - epoch) < 0) {
+      if (global_ns() - t0 > kExchangeWaitNs) {
+        ok = false;
+        break;
+      }
+      __nanosleep(200);
+    }
+    if (!ok) {
+      s_ok = 0;
+      atomicExch(e.status, CUDALM_B200_ERR_TIMEOUT);
+    }
+  }
+  __syncthreads();
+  if (tid == 0) my_epochs[m] = epoch;
+  if (!s_ok) return;  // a rank did not arrive: the status word says so, nothing is merged
+
+  // (4) merge the lists that arrived here
+  SelectArgs a;
+  a.cand = nullptr;
+  a.counts = nullptr;
+  const std::uint32_t* lists = mine + parity_off;
+  a.list_idx = reinterpret_cast<const std::int32_t*>(lists);
+  a.list_val = reinterpret_cast<const std::uint16_t*>(lists + val_base);
+  a.n_lists = e.world;
+  a.list_k = k;
+  a.idx_stride = e.words_per_list;
+  a.val_stride = 2ll * e.words_per_list;
+  a.logits = nullptr;
+  a.N = 0;
+  a.id_offset = 0;
+  a.rows = e.M;
+  a.k = k;
+  a.argmax_out = e.argmax_out;
+  a.topk_idx = e.topk_idx;
+  a.topk_val = e.topk_val;
+  select_row(a, m, tid, sm);
+}
+
+size_t exchange_words(int world, int words_per_list) {
+  return 2 * static_cast<size_t>(world) * words_per_list + static_cast<size_t>(world) * kMaxPassRows +
+         kMaxPassRows;
+}
+
+}  // namespace
+}  // namespace cb200
+
+extern "C" {
+
+size_t cudalm_b200_exchange_bytes(int world, int words_per_list) {
+  if (world < 1 || world > cb200::kMaxPeers || words_per_list < 1) return 0;
+  return cb200::exchange_words(world, words_per_list) * sizeof(std::uint32_t);
+}
+
+int cudalm_b200_exchange_create(size_t bytes, void** local, unsigned char* handle64) {
+  if (!local || !handle64 || bytes == 0) return CUDALM_B200_ERR_NULL;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handles are 64 bytes");
+  void* p = nullptr;
+  CB200_CUDA_TRY(cudaMalloc(&p, bytes));
+  cudaError_t err = cudaMemset(p, 0, bytes);
+  if (err == cudaSuccess) err = cudaDeviceSynchronize();
+  cudaIpcMemHandle_t h;
+  if (err == cudaSuccess) err = cudaIpcGetMemHandle(&h, p);
+  if (err != cudaSuccess) {
+    cb200::g_last_cuda_error = static_cast<int>(err);
+    cudaFree(p);
+    return CUDALM_B200_ERR_CUDA;
+  }
+  std::memcpy(handle64, &h, sizeof(h));
+  *local = p;
+  return CUDALM_B200_OK;
+}
+
+int cudalm_b200_exchange_open(const unsigned char* handle64, void** peer) {
+  if (!handle64 || !peer) return CUDALM_B200_ERR_NULL;
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle64, sizeof(h));
+  CB200_CUDA_TRY(cudaIpcOpenMemHandle(peer, h, cudaIpcMemLazyEnablePeerAccess));
+  return CUDALM_B200_OK;
+}
+
+int cudalm_b200_exchange_close(void* peer) {
+  if (!peer) return CUDALM_B200_ERR_NULL;
+  CB200_CUDA_TRY(cudaIpcCloseMemHandle(peer));
+  return CUDALM_B200_OK;
+}
+
+int cudalm_b200_exchange_destroy(void* local) {
+  if (!local) return CUDALM_B200_ERR_NULL;
+  CB200_CUDA_TRY(cudaFree(local));
+  return CUDALM_B200_OK;
+}
+
+int cudalm_b200_topk_exchange_merge(const int32_t* local_packed, void* const* bufs, int rank,
+                                    int world, int words_per_list, int rows_cap, int M, int k,
+                                    int32_t* argmax_out, int32_t* topk_idx, uint16_t* topk_val,
+                                    void* stream) {
+  using namespace cb200;
+  if (!local_packed || !bufs || !topk_idx || !topk_val) return CUDALM_B200_ERR_NULL;
+  if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world || M < 1 || k < 1 || rows_cap < M)
+    return CUDALM_B200_ERR_BAD_SHAPE;
+  if (M > kMaxPassRows || k > kMaxTopK || static_cast<long long>(world) * k > kCandCap)
+    return CUDALM_B200_ERR_TOO_LARGE;
+  const long long need = static_cast<long long>(rows_cap) * k + (static_cast<long long>(rows_cap) * k + 1) / 2;
+  if (words_per_list < need) return CUDALM_B200_ERR_BAD_SHAPE;
+  ExchangeArgs e;
+  std::memset(&e, 0, sizeof(e));
+  for (int r = 0; r < world; ++r) {
+    if (!bufs[r]) return CUDALM_B200_ERR_NULL;
+    e.bufs[r] = static_cast<std::uint32_t*>(bufs[r]);
+  }
+  e.local_packed = local_packed;
+  e.rank = rank;
+  e.world = world;
+  e.words_per_list = words_per_list;
+  e.rows_cap = rows_cap;
+  e.M = M;
+  e.k = k;
+  e.argmax_out = argmax_out;
+  e.topk_idx = topk_idx;
+  e.topk_val = topk_val;
+  e.status = device_status_word();
+  if (!e.status) return CUDALM_B200_ERR_CUDA;
+  return launch_after(topk_exchange_merge_kernel, dim3(M), dim3(kSelectThreads),
+                      static_cast<cudaStream_t>(stream), e);
+}
+
+}  // extern "C"

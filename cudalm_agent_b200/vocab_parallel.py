@@ -98,28 +98,104 @@ def unpack_candidates(gathered: torch.Tensor, rows: int, k: int):
     return ids, vals
 
 
+class PeerExchange:
+    """This rank's exchange buffer and its peers' buffers mapped over CUDA IPC, for
+    ``cudalm_b200_topk_exchange_merge``: the candidate lists cross NVLink as plain
+    stores from the kernel that also merges them, with no collective launch.  All
+    ranks of ``group`` must sit on one node, each on its own GPU."""
+
+    def __init__(self, words_per_list: int, rows_cap: int, top_k: int,
+                 group: Optional[dist.ProcessGroup] = None):
+        import ctypes
+        from . import api
+        self._lib = api.load_library()
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.words, self.rows_cap, self.top_k = words_per_list, rows_cap, top_k
+        nbytes = int(self._lib.cudalm_b200_exchange_bytes(self.world, words_per_list))
+        if nbytes == 0:
+            raise ValueError(f"no peer exchange for {self.world} ranks")
+        local = ctypes.c_void_p()
+        handle = ctypes.create_string_buffer(64)
+        api._check("exchange_create",
+                   self._lib.cudalm_b200_exchange_create(nbytes, ctypes.byref(local), handle))
+        self._local = local
+        handles: List[Optional[bytes]] = [None] * self.world
+        dist.all_gather_object(handles, handle.raw, group=group)
+        self._ptrs = (ctypes.c_void_p * self.world)()
+        self._opened: List[ctypes.c_void_p] = []
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                self._ptrs[r] = local.value
+                continue
+            peer = ctypes.c_void_p()
+            api._check("exchange_open", self._lib.cudalm_b200_exchange_open(h, ctypes.byref(peer)))
+            self._opened.append(peer)
+            self._ptrs[r] = peer.value
+        dist.barrier(group=group)  # every buffer is zeroed and mapped everywhere before the first call
+
+    def merge(self, packed: torch.Tensor, M: int):
+        """The merged pick of ``M`` rows from every rank's packed candidates."""
+        from . import api
+        dev = packed.device
+        argmax = torch.empty(M, dtype=torch.int32, device=dev)
+        idx = torch.empty((M, self.top_k), dtype=torch.int32, device=dev)
+        val = torch.empty((M, self.top_k), dtype=torch.bfloat16, device=dev)
+        api._check("topk_exchange_merge", self._lib.cudalm_b200_topk_exchange_merge(
+            api._ptr(packed), self._ptrs, self.rank, self.world, self.words, self.rows_cap, M,
+            self.top_k, api._ptr(argmax), api._ptr(idx), api._ptr(val), api._stream()))
+        return argmax, idx, val
+
+    def close(self) -> None:
+        """Unmaps the peers' buffers and frees this rank's (after a barrier: no peer
+        may still be storing into it)."""
+        if self._local is None:
+            return
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        for peer in self._opened:
+            self._lib.cudalm_b200_exchange_close(peer)
+        self._lib.cudalm_b200_exchange_destroy(self._local)
+        self._local, self._opened = None, []
+
+
 class VocabParallelLmHead:
     """Rank-local half of the vocabulary-parallel lm_head.
 
     ``local`` is an ``LmHead`` over this rank's rows with ``id_offset`` set to
-    the block's first token id.  ``forward(x)`` runs the local pick, all-gathers
-    the packed ``[max_rows, k]`` ids and values (one collective) and merges on
-    the device.
+    the block's first token id.  ``forward(x)`` runs the local pick, then either
+    exchanges the packed ``[max_rows, k]`` ids and values over peer memory inside
+    the merge kernel (``exchange="peer"``: ranks of one node) or all-gathers them
+    (``exchange="collective"``: one collective, any backend) and merges on the device.
     """
 
-    def __init__(self, local, group: Optional[dist.ProcessGroup] = None):
+    def __init__(self, local, group: Optional[dist.ProcessGroup] = None,
+                 exchange: str = "collective"):
         from .api import LmHead
         assert isinstance(local, LmHead)
+        if exchange not in ("collective", "peer"):
+            raise ValueError("exchange is 'collective' or 'peer'")
         self.local = local
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self._gathered = torch.empty((self.world, local.packed.numel()), dtype=torch.int32,
                                      device=local.packed.device)
+        self.peer = None
+        if exchange == "peer" and self.world > 1:
+            self.peer = PeerExchange(local.packed.numel(), local.max_rows, local.top_k, group)
 
     def forward(self, x: torch.Tensor):
         from .api import topk_merge_packed
         argmax, idx, val = self.local.forward(x)
         if self.world == 1:
             return argmax, idx, val
+        if self.peer is not None:
+            return self.peer.merge(self.local.packed, idx.shape[0])
         dist.all_gather_into_tensor(self._gathered.view(-1), self.local.packed, group=self.group)
         return topk_merge_packed(self._gathered, self.local.max_rows, idx.shape[0], self.local.top_k)
+
+    def close(self) -> None:
+        if self.peer is not None:
+            self.peer.close()
+            self.peer = None

@@ -222,6 +222,32 @@ CUDALM_B200_API int cudalm_b200_topk_merge_packed(const int32_t* gathered, int n
                                                   int32_t* topk_idx, uint16_t* topk_val,
                                                   void* stream);
 
+/* ---- candidate exchange over peer memory, fused with the merge -------------------
+ * For vocabulary-parallel ranks on one node (up to 8): instead of an all-gather
+ * followed by cudalm_b200_topk_merge_packed, ONE kernel per rank stores the rank's
+ * packed candidates (the layout above, `local_packed`) into every rank's exchange
+ * buffer over NVLink, publishes a per-row flag, waits (2 s limit, then status
+ * TIMEOUT in cudalm_b200_device_status and no merge) for every rank's flag and
+ * merges what has arrived.  There is no counterpart in CUDALM, whose lm_head is
+ * single-GPU (src/runtime/qwen35_model.cpp:290-292).
+ *
+ * Every rank creates a buffer of cudalm_b200_exchange_bytes(world, words_per_list)
+ * (zeroed; `handle64` receives its 64-byte CUDA IPC handle), sends the handle to
+ * its peers by any host channel, opens the peers' handles, and passes the `world`
+ * pointers (its own at [rank]) as the HOST array `bufs`.  All ranks must have opened
+ * all buffers before the first call, make the same sequence of calls (same M), and
+ * keep the calls of one rank on one stream.  M <= 32 rows per call. */
+CUDALM_B200_API size_t cudalm_b200_exchange_bytes(int world, int words_per_list);
+CUDALM_B200_API int cudalm_b200_exchange_create(size_t bytes, void** local, unsigned char* handle64);
+CUDALM_B200_API int cudalm_b200_exchange_open(const unsigned char* handle64, void** peer);
+CUDALM_B200_API int cudalm_b200_exchange_close(void* peer);
+CUDALM_B200_API int cudalm_b200_exchange_destroy(void* local);
+CUDALM_B200_API int cudalm_b200_topk_exchange_merge(const int32_t* local_packed, void* const* bufs,
+                                                    int rank, int world, int words_per_list,
+                                                    int rows_cap, int M, int k,
+                                                    int32_t* argmax_out, int32_t* topk_idx,
+                                                    uint16_t* topk_val, void* stream);
+
 /* ---- token sampling over the candidate lists -----------------------------------
  * CUDALM's sample_token (include/cudalm/sampling.h:131-234; called per row on the
  * host after a 497 KB copy of the logits, src/runtime/scheduler.cpp:59-108) on the

@@ -685,3 +685,41 @@ def test_decode_step_replays_from_a_cuda_graph(eng, orc, M):
         got = snapshot(res)
         for a, b in zip(want, got):
             assert torch.equal(a, b), f"replay {trial} differs from the eager calls"
+
+
+def test_peer_exchange_merge_with_one_rank(eng, orc):
+    """The exchange-and-merge kernel with this GPU as its only rank: the candidates go
+    through the exchange buffer (both parities, rows with different call counts) and
+    come back as the pick the local kernel made."""
+    import ctypes
+    import torch
+    from cudalm_agent_b200 import api
+    lib = api.load_library()
+    N, K, k, rows_cap = 4096, 1024, 50, 32
+    _, W, S = make_weights(orc, N, K, BASE_SEED + 950)
+    head = eng.LmHead(eng.W4A16Linear(to_dev(W), to_dev(S, torch.float16)), top_k=k, max_rows=rows_cap)
+    words = head.packed.numel()
+    nbytes = lib.cudalm_b200_exchange_bytes(1, words)
+    assert nbytes > 0 and lib.cudalm_b200_exchange_bytes(9, words) == 0
+    local, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+    assert lib.cudalm_b200_exchange_create(nbytes, ctypes.byref(local), handle) == 0
+    bufs = (ctypes.c_void_p * 1)(local.value)
+    try:
+        for trial, M in enumerate((32, 5, 32, 1, 17)):
+            x = to_dev(make_x(orc, (M, K), BASE_SEED + 960 + trial, "rmsnorm"), torch.bfloat16)
+            argmax, idx, val = [t.clone() for t in head.forward(x)]
+            got_a = torch.empty(M, dtype=torch.int32, device="cuda")
+            got_i = torch.empty((M, k), dtype=torch.int32, device="cuda")
+            got_v = torch.empty((M, k), dtype=torch.bfloat16, device="cuda")
+            st = lib.cudalm_b200_topk_exchange_merge(api._ptr(head.packed), bufs, 0, 1, words, rows_cap,
+                                                     M, k, api._ptr(got_a), api._ptr(got_i),
+                                                     api._ptr(got_v), api._stream())
+            assert st == 0
+            torch.cuda.synchronize()
+            assert torch.equal(got_a, argmax) and torch.equal(got_i, idx) and torch.equal(got_v, val)
+        assert lib.cudalm_b200_topk_exchange_merge(api._ptr(head.packed), bufs, 1, 1, words, rows_cap,
+                                                   1, k, None, api._ptr(got_i), api._ptr(got_v),
+                                                   api._stream()) != 0  # rank outside the world
+    finally:
+        torch.cuda.synchronize()
+        assert lib.cudalm_b200_exchange_destroy(local) == 0
