@@ -95,6 +95,9 @@ SIGNATURES = {
     "cudalm_b200_exchange_destroy": (_ci, [_vp]),
     "cudalm_b200_topk_exchange_merge": (_ci, [_vp, ctypes.POINTER(_vp), _ci, _ci, _ci, _ci, _ci, _ci,
                                              _vp, _vp, _vp, _vp]),
+    "cudalm_b200_lm_head_topk_exchange": (_ci, [_vp, _vp, _vp, _ci, _ci, _ci, _ci, _ci, _vp, _vp, _ci,
+                                               _vp, ctypes.c_size_t, ctypes.POINTER(_vp), _ci, _ci,
+                                               _ci, _vp, _vp, _vp, _vp]),
     "cudalm_b200_quantize_w4a16": (_ci, [_vp, _ci, _ci, _vp, _vp, _vp]),
     "cudalm_b200_set_tensor_path_min_rows": (_ci, [_ci]),
     "cudalm_b200_kernel_regs": (_ci, [ctypes.c_char_p]),

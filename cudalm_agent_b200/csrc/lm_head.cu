@@ -338,6 +338,114 @@ lm_head_select_kernel(const SelectArgs a) {
   select_row(a, blockIdx.x, threadIdx.x, sm);
 }
 
+constexpr int kMaxPeers = 8;
+constexpr long long kExchangeWaitNs = 2000000000ll;  // 2 s
+
+struct ExchangeArgs {
+  std::uint32_t* bufs[kMaxPeers];  // every rank's buffer as mapped here; bufs[rank] is the local one
+  const std::int32_t* local_packed;
+  int rank, world, words_per_list, rows_cap, M, k;
+  std::int32_t* argmax_out;
+  std::int32_t* topk_idx;
+  std::uint16_t* topk_val;
+  int* status;
+};
+
+__device__ __forceinline__ void st_release_sys(std::uint32_t* p, std::uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ std::uint32_t ld_acquire_sys(const std::uint32_t* p) {
+  std::uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ long long global_ns() {
+  long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Row m's exchange and merge by one CTA of kSelectThreads threads.
+__device__ void exchange_row(const ExchangeArgs& e, int m, int tid, SelectSmem& sm) {
+  __shared__ int s_ok;
+  const size_t lists_words = static_cast<size_t>(e.world) * e.words_per_list;
+  std::uint32_t* mine = e.bufs[e.rank];
+  std::uint32_t* my_flags = mine + 2 * lists_words;
+  std::uint32_t* my_epochs = my_flags + static_cast<size_t>(e.world) * kMaxPassRows;
+  const std::uint32_t epoch = my_epochs[m] + 1u;  // written only by this row's CTA, one call earlier
+  const size_t parity_off = (epoch & 1u) * lists_words;
+
+  // (1) this rank's candidates of row m into slot [rank] of every rank's buffer
+  const int k = e.k;
+  const size_t val_base = static_cast<size_t>(e.rows_cap) * k;  // in words: values start here
+  const std::int32_t* src_idx = e.local_packed + static_cast<size_t>(m) * k;
+  const std::uint16_t* src_val =
+      reinterpret_cast<const std::uint16_t*>(e.local_packed + val_base) + static_cast<size_t>(m) * k;
+  for (int i = tid; i < e.world * 2 * k; i += kSelectThreads) {
+    const int p = i / (2 * k), j = i - p * 2 * k;
+    std::uint32_t* slot = e.bufs[p] + parity_off + static_cast<size_t>(e.rank) * e.words_per_list;
+    if (j < k)
+      slot[static_cast<size_t>(m) * k + j] = static_cast<std::uint32_t>(src_idx[j]);
+    else
+      (reinterpret_cast<std::uint16_t*>(slot + val_base))[static_cast<size_t>(m) * k + (j - k)] = src_val[j - k];
+  }
+  __threadfence_system();
+  __syncthreads();
+  // (2) the row's epoch on every rank, (3) wait for every rank's
+  if (tid == 0) s_ok = 1;
+  __syncthreads();
+  if (tid < e.world) {
+    std::uint32_t* peer_flags = e.bufs[tid] + 2 * lists_words;
+    st_release_sys(peer_flags + static_cast<size_t>(e.rank) * kMaxPassRows + m, epoch);
+    const std::uint32_t* f = my_flags + static_cast<size_t>(tid) * kMaxPassRows + m;
+    const long long t0 = global_ns();
+    bool ok = true;
+    while (static_cast<std::int32_t>(ld_acquire_sys(f) - epoch) < 0) {
+      if (global_ns() - t0 > kExchangeWaitNs) {
+        ok = false;
+        break;
+      }
+      __nanosleep(200);
+    }
+    if (!ok) {
+      s_ok = 0;
+      atomicExch(e.status, CUDALM_B200_ERR_TIMEOUT);
+    }
+  }
+  __syncthreads();
+  if (tid == 0) my_epochs[m] = epoch;
+  if (!s_ok) return;  // a rank did not arrive: the status word says so, nothing is merged
+
+  // (4) merge the lists that arrived here
+  SelectArgs a;
+  a.cand = nullptr;
+  a.counts = nullptr;
+  const std::uint32_t* lists = mine + parity_off;
+  a.list_idx = reinterpret_cast<const std::int32_t*>(lists);
+  a.list_val = reinterpret_cast<const std::uint16_t*>(lists + val_base);
+  a.n_lists = e.world;
+  a.list_k = k;
+  a.idx_stride = e.words_per_list;
+  a.val_stride = 2ll * e.words_per_list;
+  a.logits = nullptr;
+  a.N = 0;
+  a.id_offset = 0;
+  a.rows = e.M;
+  a.k = k;
+  a.argmax_out = e.argmax_out;
+  a.topk_idx = e.topk_idx;
+  a.topk_val = e.topk_val;
+  select_row(a, m, tid, sm);
+}
+
+__global__ void __launch_bounds__(kSelectThreads)
+topk_exchange_merge_kernel(const ExchangeArgs e) {
+  __shared__ SelectSmem sm;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  exchange_row(e, blockIdx.x, threadIdx.x, sm);
+}
+
 // ---------------------------------------------------------------------------
 // scan + pick: grid (slices, rows).  Each CTA derives the row's bound from the
 // per-CTA maxima and scans its slice of the row's logits for candidates; the
@@ -347,7 +455,8 @@ lm_head_select_kernel(const SelectArgs a) {
 __global__ void __launch_bounds__(kSelectThreads)
 lm_head_scan_pick_kernel(const std::uint16_t* __restrict__ logits, int N, int rows,
                          const float* __restrict__ cta_max, int ncta, int k, int id_offset,
-                         int* counts, int* tickets, std::uint64_t* cand, const SelectArgs a) {
+                         int* counts, int* tickets, std::uint64_t* cand, const SelectArgs a,
+                         const ExchangeArgs e) {
   __shared__ SelectSmem sm;
   __shared__ int s_last;
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -362,6 +471,12 @@ lm_head_scan_pick_kernel(const std::uint16_t* __restrict__ logits, int N, int ro
   if (!s_last) return;
   __threadfence();
   select_row(a, m, tid, sm);
+  if (e.world >= 1) {  // 0: no exchange
+    // vocabulary-parallel: the same CTA sends the row's pick to the other ranks and
+    // merges theirs (its own global stores are visible to it after the barrier)
+    __syncthreads();
+    exchange_row(e, m, tid, sm);
+  }
 }
 
 __global__ void zero_counts_kernel(int* counts, int n) {
@@ -410,11 +525,13 @@ size_t cudalm_b200_lm_head_workspace_bytes(int N, int K, int M, int top_k, int n
   return workspace_layout(N, rows, need_logits != 0, nullptr, nullptr);
 }
 
-int cudalm_b200_lm_head_topk(const uint8_t* weight, const uint16_t* scales, const uint16_t* x,
+// `ex` non-null: the rows' picks are also exchanged with the other ranks and merged
+// by the CTA that made them (one pass only).
+static int lm_head_topk_impl(const uint8_t* weight, const uint16_t* scales, const uint16_t* x,
                              int N, int K, int M, int top_k, int id_offset,
                              uint16_t* logits_out, int32_t* argmax_out, int32_t* topk_idx,
                              uint16_t* topk_val, void* workspace, size_t workspace_bytes,
-                             void* stream) {
+                             void* stream, const ExchangeArgs* ex) {
   if (!weight || !scales || !x || !topk_idx || !topk_val) return CUDALM_B200_ERR_NULL;
   if (N < 1 || K <= 0 || (K % 128) != 0 || M < 1 || id_offset < 0) return CUDALM_B200_ERR_BAD_SHAPE;
   if (top_k < 1 || top_k > kMaxTopK) return CUDALM_B200_ERR_TOO_LARGE;
@@ -429,6 +546,10 @@ int cudalm_b200_lm_head_topk(const uint8_t* weight, const uint16_t* scales, cons
   const bool staged = per_pass > 0 && aligned_to(weight, 16);
   if (!staged) per_pass = kMaxPassRows;
   const int rows_cap = M < kMaxPassRows ? M : kMaxPassRows;
+
+  if (ex && M > per_pass) return CUDALM_B200_ERR_UNSUPPORTED;
+  ExchangeArgs no_exchange;
+  std::memset(&no_exchange, 0, sizeof(no_exchange));
 
   for (int m0 = 0; m0 < M; m0 += per_pass) {
     const int rows = (M - m0 < per_pass) ? (M - m0) : per_pass;
@@ -473,10 +594,19 @@ int cudalm_b200_lm_head_topk(const uint8_t* weight, const uint16_t* scales, cons
     if (int rc = launch_after(lm_head_scan_pick_kernel, dim3(slices, rows), dim3(kSelectThreads), st,
                               static_cast<const std::uint16_t*>(logits), N, rows,
                               static_cast<const float*>(ws.cta_max), ncta, top_k, id_offset, ws.counts,
-                              ws.counts + kMaxPassRows, ws.cand, a))
+                              ws.counts + kMaxPassRows, ws.cand, a, ex ? *ex : no_exchange))
       return rc;
   }
   return CUDALM_B200_OK;
+}
+
+int cudalm_b200_lm_head_topk(const uint8_t* weight, const uint16_t* scales, const uint16_t* x,
+                             int N, int K, int M, int top_k, int id_offset,
+                             uint16_t* logits_out, int32_t* argmax_out, int32_t* topk_idx,
+                             uint16_t* topk_val, void* workspace, size_t workspace_bytes,
+                             void* stream) {
+  return lm_head_topk_impl(weight, scales, x, N, K, M, top_k, id_offset, logits_out, argmax_out,
+                           topk_idx, topk_val, workspace, workspace_bytes, stream, nullptr);
 }
 
 int cudalm_b200_topk_merge(const int32_t* list_idx, const uint16_t* list_val, int n_lists, int M,
@@ -627,111 +757,6 @@ extern "C" int cudalm_b200_topk_merge_packed(const int32_t* gathered, int n_list
 namespace cb200 {
 namespace {
 
-constexpr int kMaxPeers = 8;
-constexpr long long kExchangeWaitNs = 2000000000ll;  // 2 s
-
-struct ExchangeArgs {
-  std::uint32_t* bufs[kMaxPeers];  // every rank's buffer as mapped here; bufs[rank] is the local one
-  const std::int32_t* local_packed;
-  int rank, world, words_per_list, rows_cap, M, k;
-  std::int32_t* argmax_out;
-  std::int32_t* topk_idx;
-  std::uint16_t* topk_val;
-  int* status;
-};
-
-__device__ __forceinline__ void st_release_sys(std::uint32_t* p, std::uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ std::uint32_t ld_acquire_sys(const std::uint32_t* p) {
-  std::uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ long long global_ns() {
-  long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-
-__global__ void __launch_bounds__(kSelectThreads)
-topk_exchange_merge_kernel(const ExchangeArgs e) {
-  __shared__ SelectSmem sm;
-  __shared__ int s_ok;
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-  const int m = blockIdx.x;
-  const int tid = threadIdx.x;
-  const size_t lists_words = static_cast<size_t>(e.world) * e.words_per_list;
-  std::uint32_t* mine = e.bufs[e.rank];
-  std::uint32_t* my_flags = mine + 2 * lists_words;
-  std::uint32_t* my_epochs = my_flags + static_cast<size_t>(e.world) * kMaxPassRows;
-  const std::uint32_t epoch = my_epochs[m] + 1u;  // written only by this row's CTA, one call earlier
-  const size_t parity_off = (epoch & 1u) * lists_words;
-
-  // (1) this rank's candidates of row m into slot [rank] of every rank's buffer
-  const int k = e.k;
-  const size_t val_base = static_cast<size_t>(e.rows_cap) * k;  // in words: values start here
-  const std::int32_t* src_idx = e.local_packed + static_cast<size_t>(m) * k;
-  const std::uint16_t* src_val =
-      reinterpret_cast<const std::uint16_t*>(e.local_packed + val_base) + static_cast<size_t>(m) * k;
-  for (int i = tid; i < e.world * 2 * k; i += kSelectThreads) {
-    const int p = i / (2 * k), j = i - p * 2 * k;
-    std::uint32_t* slot = e.bufs[p] + parity_off + static_cast<size_t>(e.rank) * e.words_per_list;
-    if (j < k)
-      slot[static_cast<size_t>(m) * k + j] = static_cast<std::uint32_t>(src_idx[j]);
-    else
-      (reinterpret_cast<std::uint16_t*>(slot + val_base))[static_cast<size_t>(m) * k + (j - k)] = src_val[j - k];
-  }
-  __threadfence_system();
-  __syncthreads();
-  // (2) the row's epoch on every rank, (3) wait for every rank's
-  if (tid == 0) s_ok = 1;
-  __syncthreads();
-  if (tid < e.world) {
-    std::uint32_t* peer_flags = e.bufs[tid] + 2 * lists_words;
-    st_release_sys(peer_flags + static_cast<size_t>(e.rank) * kMaxPassRows + m, epoch);
-    const std::uint32_t* f = my_flags + static_cast<size_t>(tid) * kMaxPassRows + m;
-    const long long t0 = global_ns();
-    bool ok = true;
-    while (static_cast<std::int32_t>(ld_acquire_sys(f) - epoch) < 0) {
-      if (global_ns() - t0 > kExchangeWaitNs) {
-        ok = false;
-        break;
-      }
-      __nanosleep(200);
-    }
-    if (!ok) {
-      s_ok = 0;
-      atomicExch(e.status, CUDALM_B200_ERR_TIMEOUT);
-    }
-  }
-  __syncthreads();
-  if (tid == 0) my_epochs[m] = epoch;
-  if (!s_ok) return;  // a rank did not arrive: the status word says so, nothing is merged
-
-  // (4) merge the lists that arrived here
-  SelectArgs a;
-  a.cand = nullptr;
-  a.counts = nullptr;
-  const std::uint32_t* lists = mine + parity_off;
-  a.list_idx = reinterpret_cast<const std::int32_t*>(lists);
-  a.list_val = reinterpret_cast<const std::uint16_t*>(lists + val_base);
-  a.n_lists = e.world;
-  a.list_k = k;
-  a.idx_stride = e.words_per_list;
-  a.val_stride = 2ll * e.words_per_list;
-  a.logits = nullptr;
-  a.N = 0;
-  a.id_offset = 0;
-  a.rows = e.M;
-  a.k = k;
-  a.argmax_out = e.argmax_out;
-  a.topk_idx = e.topk_idx;
-  a.topk_val = e.topk_val;
-  select_row(a, m, tid, sm);
-}
-
 size_t exchange_words(int world, int words_per_list) {
   return 2 * static_cast<size_t>(world) * words_per_list + static_cast<size_t>(world) * kMaxPassRows +
          kMaxPassRows;
@@ -786,10 +811,9 @@ int cudalm_b200_exchange_destroy(void* local) {
   return CUDALM_B200_OK;
 }
 
-int cudalm_b200_topk_exchange_merge(const int32_t* local_packed, void* const* bufs, int rank,
-                                    int world, int words_per_list, int rows_cap, int M, int k,
-                                    int32_t* argmax_out, int32_t* topk_idx, uint16_t* topk_val,
-                                    void* stream) {
+static int fill_exchange_args(const int32_t* local_packed, void* const* bufs, int rank, int world,
+                              int words_per_list, int rows_cap, int M, int k, int32_t* argmax_out,
+                              int32_t* topk_idx, uint16_t* topk_val, cb200::ExchangeArgs* out) {
   using namespace cb200;
   if (!local_packed || !bufs || !topk_idx || !topk_val) return CUDALM_B200_ERR_NULL;
   if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world || M < 1 || k < 1 || rows_cap < M)
@@ -816,8 +840,40 @@ int cudalm_b200_topk_exchange_merge(const int32_t* local_packed, void* const* bu
   e.topk_val = topk_val;
   e.status = device_status_word();
   if (!e.status) return CUDALM_B200_ERR_CUDA;
-  return launch_after(topk_exchange_merge_kernel, dim3(M), dim3(kSelectThreads),
-                      static_cast<cudaStream_t>(stream), e);
+  *out = e;
+  return CUDALM_B200_OK;
+}
+
+int cudalm_b200_topk_exchange_merge(const int32_t* local_packed, void* const* bufs, int rank,
+                                    int world, int words_per_list, int rows_cap, int M, int k,
+                                    int32_t* argmax_out, int32_t* topk_idx, uint16_t* topk_val,
+                                    void* stream) {
+  cb200::ExchangeArgs e;
+  if (int rc = fill_exchange_args(local_packed, bufs, rank, world, words_per_list, rows_cap, M, k,
+                                  argmax_out, topk_idx, topk_val, &e))
+    return rc;
+  return cb200::launch_after(cb200::topk_exchange_merge_kernel, dim3(M), dim3(cb200::kSelectThreads),
+                             static_cast<cudaStream_t>(stream), e);
+}
+
+int cudalm_b200_lm_head_topk_exchange(const uint8_t* weight, const uint16_t* scales,
+                                      const uint16_t* x, int N, int K, int M, int top_k,
+                                      int id_offset, uint16_t* logits_out, int32_t* local_packed,
+                                      int rows_cap, void* workspace, size_t workspace_bytes,
+                                      void* const* bufs, int rank, int world, int words_per_list,
+                                      int32_t* argmax_out, int32_t* topk_idx, uint16_t* topk_val,
+                                      void* stream) {
+  if (!local_packed) return CUDALM_B200_ERR_NULL;
+  if (rows_cap < M || rows_cap < 1 || top_k < 1) return CUDALM_B200_ERR_BAD_SHAPE;
+  cb200::ExchangeArgs e;
+  if (int rc = fill_exchange_args(local_packed, bufs, rank, world, words_per_list, rows_cap, M, top_k,
+                                  argmax_out, topk_idx, topk_val, &e))
+    return rc;
+  // the local pick lands in the packed buffer: ids [rows_cap][k], then values
+  int32_t* local_idx = local_packed;
+  uint16_t* local_val = reinterpret_cast<uint16_t*>(local_packed + static_cast<size_t>(rows_cap) * top_k);
+  return lm_head_topk_impl(weight, scales, x, N, K, M, top_k, id_offset, logits_out, nullptr, local_idx,
+                           local_val, workspace, workspace_bytes, stream, &e);
 }
 
 }  // extern "C"

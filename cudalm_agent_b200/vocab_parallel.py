@@ -147,6 +147,27 @@ class PeerExchange:
             self.top_k, api._ptr(argmax), api._ptr(idx), api._ptr(val), api._stream()))
         return argmax, idx, val
 
+    def forward(self, head, x: torch.Tensor):
+        """Projection, local pick, exchange and merge of one rank in two launches
+        (``head``: this rank's ``LmHead``).  Returns None when the rows do not fit one
+        pass; the caller then runs ``head.forward`` and ``merge``."""
+        from . import api
+        M = 1 if x.dim() == 1 else int(x.shape[0])
+        dev = x.device
+        argmax = torch.empty(M, dtype=torch.int32, device=dev)
+        idx = torch.empty((M, self.top_k), dtype=torch.int32, device=dev)
+        val = torch.empty((M, self.top_k), dtype=torch.bfloat16, device=dev)
+        rows = head.rows
+        st = self._lib.cudalm_b200_lm_head_topk_exchange(
+            api._ptr(rows.weight), api._ptr(rows.scale), api._ptr(x), rows.N, rows.K, M, self.top_k,
+            head.id_offset, api._ptr(head.logits), api._ptr(head.packed), self.rows_cap,
+            api._ptr(head.workspace), head.workspace.numel(), self._ptrs, self.rank, self.world,
+            self.words, api._ptr(argmax), api._ptr(idx), api._ptr(val), api._stream())
+        if st == 6:  # UNSUPPORTED
+            return None
+        api._check("lm_head_topk_exchange", st)
+        return argmax, idx, val
+
     def close(self) -> None:
         """Unmaps the peers' buffers and frees this rank's (after a barrier: no peer
         may still be storing into it)."""
@@ -187,6 +208,10 @@ class VocabParallelLmHead:
 
     def forward(self, x: torch.Tensor):
         from .api import topk_merge_packed
+        if self.peer is not None:
+            fused = self.peer.forward(self.local, x)
+            if fused is not None:
+                return fused
         argmax, idx, val = self.local.forward(x)
         if self.world == 1:
             return argmax, idx, val

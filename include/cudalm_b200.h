@@ -248,6 +248,19 @@ CUDALM_B200_API int cudalm_b200_topk_exchange_merge(const int32_t* local_packed,
                                                     int32_t* argmax_out, int32_t* topk_idx,
                                                     uint16_t* topk_val, void* stream);
 
+/* The whole vocabulary-parallel step of one rank in two launches: the projection of
+ * this rank's rows, then the scan whose last CTA per row picks the row's local
+ * candidates (into `local_packed`: ids int32 [rows_cap][top_k], then values bf16),
+ * sends them to the other ranks and merges theirs as cudalm_b200_topk_exchange_merge
+ * does; argmax_out / topk_idx / topk_val receive the merged pick.  Arguments as
+ * cudalm_b200_lm_head_topk and cudalm_b200_topk_exchange_merge; M must fit one pass
+ * (UNSUPPORTED otherwise: call the two entries one after the other). */
+CUDALM_B200_API int cudalm_b200_lm_head_topk_exchange(
+    const uint8_t* weight, const uint16_t* scales, const uint16_t* x, int N, int K, int M,
+    int top_k, int id_offset, uint16_t* logits_out, int32_t* local_packed, int rows_cap,
+    void* workspace, size_t workspace_bytes, void* const* bufs, int rank, int world,
+    int words_per_list, int32_t* argmax_out, int32_t* topk_idx, uint16_t* topk_val, void* stream);
+
 /* ---- token sampling over the candidate lists -----------------------------------
  * CUDALM's sample_token (include/cudalm/sampling.h:131-234; called per row on the
  * host after a 497 KB copy of the logits, src/runtime/scheduler.cpp:59-108) on the

@@ -717,6 +717,16 @@ def test_peer_exchange_merge_with_one_rank(eng, orc):
             assert st == 0
             torch.cuda.synchronize()
             assert torch.equal(got_a, argmax) and torch.equal(got_i, idx) and torch.equal(got_v, val)
+            # the same through the fused entry (projection, pick, exchange and merge)
+            got_i.zero_()
+            got_a.zero_()
+            st = lib.cudalm_b200_lm_head_topk_exchange(
+                api._ptr(head.rows.weight), api._ptr(head.rows.scale), api._ptr(x), N, K, M, k, 0, None,
+                api._ptr(head.packed), rows_cap, api._ptr(head.workspace), head.workspace.numel(), bufs,
+                0, 1, words, api._ptr(got_a), api._ptr(got_i), api._ptr(got_v), api._stream())
+            assert st == 0
+            torch.cuda.synchronize()
+            assert torch.equal(got_a, argmax) and torch.equal(got_i, idx) and torch.equal(got_v, val)
         assert lib.cudalm_b200_topk_exchange_merge(api._ptr(head.packed), bufs, 1, 1, words, rows_cap,
                                                    1, k, None, api._ptr(got_i), api._ptr(got_v),
                                                    api._stream()) != 0  # rank outside the world
