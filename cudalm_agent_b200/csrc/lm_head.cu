@@ -389,12 +389,13 @@ __device__ void exchange_row(const ExchangeArgs& e, int m, int tid, SelectSmem& 
     else
       (reinterpret_cast<std::uint16_t*>(slot + val_base))[static_cast<size_t>(m) * k + (j - k)] = src_val[j - k];
   }
-  __threadfence_system();
-  __syncthreads();
-  // (2) the row's epoch on every rank, (3) wait for every rank's
+  // (2) the row's epoch on every rank, (3) wait for every rank's.  The CTA's stores are
+  // ordered before the flags by the barrier and the publishing threads' own fence
+  // (fences are cumulative), so only `world` threads pay a system-wide fence.
   if (tid == 0) s_ok = 1;
   __syncthreads();
   if (tid < e.world) {
+    __threadfence_system();
     std::uint32_t* peer_flags = e.bufs[tid] + 2 * lists_words;
     st_release_sys(peer_flags + static_cast<size_t>(e.rank) * kMaxPassRows + m, epoch);
     const std::uint32_t* f = my_flags + static_cast<size_t>(tid) * kMaxPassRows + m;
@@ -405,7 +406,7 @@ __device__ void exchange_row(const ExchangeArgs& e, int m, int tid, SelectSmem& 
         ok = false;
         break;
       }
-      __nanosleep(200);
+      __nanosleep(100);
     }
     if (!ok) {
       s_ok = 0;
@@ -464,12 +465,16 @@ lm_head_scan_pick_kernel(const std::uint16_t* __restrict__ logits, int N, int ro
   const int m = blockIdx.y;
   const int tid = threadIdx.x;
   scan_slice(logits, N, rows, cta_max, ncta, k, id_offset, counts, cand, reinterpret_cast<float*>(sm.buf));
-  __threadfence();  // this CTA's candidates and count are visible before its ticket
+  // this CTA's candidates and count are visible before its ticket: the barrier orders
+  // them before thread 0's fence, which is cumulative
   __syncthreads();
-  if (tid == 0) s_last = atomicAdd(&tickets[m], 1) == static_cast<int>(gridDim.x) - 1;
+  if (tid == 0) {
+    __threadfence();
+    s_last = atomicAdd(&tickets[m], 1) == static_cast<int>(gridDim.x) - 1;
+    __threadfence();
+  }
   __syncthreads();
   if (!s_last) return;
-  __threadfence();
   select_row(a, m, tid, sm);
   if (e.world >= 1) {  // 0: no exchange
     // vocabulary-parallel: the same CTA sends the row's pick to the other ranks and
