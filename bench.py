@@ -302,9 +302,21 @@ def bench_lm_head(eng, torch, dist, rank, world, steps, warmup):
         modes = ["peer", "collective"] if world > 1 else ["collective"]
         entry = {}
         picks = {}
-        for mode in modes:
-            heads = [eng.VocabParallelLmHead(eng.LmHead(l, TOP_K, id_offset=lo, max_rows=M),
-                                             exchange=mode) for l in (lin, lin2)]
+        for mode in list(modes):
+            try:
+                heads = [eng.VocabParallelLmHead(eng.LmHead(l, TOP_K, id_offset=lo, max_rows=M),
+                                                 exchange=mode) for l in (lin, lin2)]
+                failed = 0
+            except Exception as exc:  # e.g. the ranks' GPUs cannot map one another's memory
+                heads, failed, why = [], 1, f"{type(exc).__name__}: {exc}"
+            failed_anywhere = failed != 0  # PeerExchange raises on every rank or on none
+            if failed_anywhere:
+                if mode != "peer":
+                    raise RuntimeError("the collective exchange could not be set up")
+                modes.remove("peer")
+                entry_note = f"peer exchange unavailable ({why})"
+                picks["note"] = entry_note
+                continue
             res = {}
 
             def step(i):
@@ -329,6 +341,8 @@ def bench_lm_head(eng, torch, dist, rank, world, steps, warmup):
                 if not same:
                     raise RuntimeError("peer exchange and all-gather picked different tokens")
                 entry["same_pick_as_collective"] = True
+        if "note" in picks:
+            entry["note"] = picks["note"]
         out[f"M{M}"] = entry
     return out
 

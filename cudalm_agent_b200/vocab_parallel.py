@@ -116,24 +116,35 @@ class PeerExchange:
         nbytes = int(self._lib.cudalm_b200_exchange_bytes(self.world, words_per_list))
         if nbytes == 0:
             raise ValueError(f"no peer exchange for {self.world} ranks")
+        # Every rank goes through the same collectives whether or not a step failed
+        # locally, and all ranks raise together: a rank that cannot map a peer must not
+        # leave the others waiting.
         local = ctypes.c_void_p()
         handle = ctypes.create_string_buffer(64)
-        api._check("exchange_create",
-                   self._lib.cudalm_b200_exchange_create(nbytes, ctypes.byref(local), handle))
-        self._local = local
+        st = self._lib.cudalm_b200_exchange_create(nbytes, ctypes.byref(local), handle)
+        self._local = local if st == 0 else None
         handles: List[Optional[bytes]] = [None] * self.world
-        dist.all_gather_object(handles, handle.raw, group=group)
+        dist.all_gather_object(handles, handle.raw if st == 0 else None, group=group)
         self._ptrs = (ctypes.c_void_p * self.world)()
         self._opened: List[ctypes.c_void_p] = []
-        for r, h in enumerate(handles):
-            if r == self.rank:
-                self._ptrs[r] = local.value
-                continue
-            peer = ctypes.c_void_p()
-            api._check("exchange_open", self._lib.cudalm_b200_exchange_open(h, ctypes.byref(peer)))
-            self._opened.append(peer)
-            self._ptrs[r] = peer.value
-        dist.barrier(group=group)  # every buffer is zeroed and mapped everywhere before the first call
+        ok = st == 0 and all(h is not None for h in handles)
+        if ok:
+            for r, h in enumerate(handles):
+                if r == self.rank:
+                    self._ptrs[r] = local.value
+                    continue
+                peer = ctypes.c_void_p()
+                if self._lib.cudalm_b200_exchange_open(h, ctypes.byref(peer)) != 0:
+                    ok = False
+                    break
+                self._opened.append(peer)
+                self._ptrs[r] = peer.value
+        verdicts: List[Optional[bool]] = [None] * self.world
+        dist.all_gather_object(verdicts, ok, group=group)  # also: every buffer is mapped everywhere
+        if not all(verdicts):
+            self._release()
+            bad = [r for r, v in enumerate(verdicts) if not v]
+            raise RuntimeError(f"peer exchange: ranks {bad} could not create or map the buffers")
 
     def merge(self, packed: torch.Tensor, M: int):
         """The merged pick of ``M`` rows from every rank's packed candidates."""
@@ -168,6 +179,13 @@ class PeerExchange:
         api._check("lm_head_topk_exchange", st)
         return argmax, idx, val
 
+    def _release(self) -> None:
+        for peer in self._opened:
+            self._lib.cudalm_b200_exchange_close(peer)
+        if self._local is not None:
+            self._lib.cudalm_b200_exchange_destroy(self._local)
+        self._local, self._opened = None, []
+
     def close(self) -> None:
         """Unmaps the peers' buffers and frees this rank's (after a barrier: no peer
         may still be storing into it)."""
@@ -175,10 +193,7 @@ class PeerExchange:
             return
         torch.cuda.synchronize()
         dist.barrier(group=self.group)
-        for peer in self._opened:
-            self._lib.cudalm_b200_exchange_close(peer)
-        self._lib.cudalm_b200_exchange_destroy(self._local)
-        self._local, self._opened = None, []
+        self._release()
 
 
 class VocabParallelLmHead:
