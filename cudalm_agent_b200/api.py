@@ -76,6 +76,11 @@ SIGNATURES = {
     "cudalm_b200_v2_metadata_at": (_ci, [_vp, _ci, _vp, _vp]),
     "cudalm_b200_v2_upload": (_ci, [_vp, _ci, _vp, ctypes.c_size_t, _vp]),
     "cudalm_b200_v2_linear": (_ci, [_vp, ctypes.c_char_p, ctypes.c_char_p, _vp, _vp, _vp, _vp]),
+    "cudalm_b200_v2_validate_layer": (_ci, [_vp, _ci, ctypes.c_char_p, ctypes.c_size_t]),
+    "cudalm_b200_v2_validate_full_model": (_ci, [_vp, ctypes.c_char_p, ctypes.c_size_t]),
+    "cudalm_b200_v2_layer_device_bytes": (ctypes.c_size_t, [_vp, _ci]),
+    "cudalm_b200_v2_load_layer": (_ci, [_vp, _ci, _vp, ctypes.c_size_t, _vp, _vp, ctypes.c_char_p,
+                                        ctypes.c_size_t]),
     "cudalm_b200_sample_topk": (_ci, [_vp, _vp, _ci, _ci, ctypes.c_float, _ci, ctypes.c_float, _vp,
                                       _vp, _vp]),
     "cudalm_b200_gate_up_silu_bf16": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _vp]),
@@ -100,6 +105,7 @@ SIGNATURES = {
                                                _ci, _vp, _vp, _vp, _vp]),
     "cudalm_b200_quantize_w4a16": (_ci, [_vp, _ci, _ci, _vp, _vp, _vp]),
     "cudalm_b200_set_tensor_path_min_rows": (_ci, [_ci]),
+    "cudalm_b200_set_direct_path_max_bytes": (ctypes.c_int64, [ctypes.c_int64]),
     "cudalm_b200_kernel_regs": (_ci, [ctypes.c_char_p]),
     "cudalm_b200_launch_count": (ctypes.c_int64, []),
 }
@@ -166,6 +172,12 @@ def set_tensor_path_min_rows(min_rows: int) -> int:
     """Batched calls with at least this many rows take the tcgen05 kernel
     (default 17); returns the previous value."""
     return int(load_library().cudalm_b200_set_tensor_path_min_rows(int(min_rows)))
+
+
+def set_direct_path_max_bytes(max_bytes: int) -> int:
+    """Single calls with at most 8 rows and at most this many weight bytes take
+    the lean kernel (0: never); returns the previous value."""
+    return int(load_library().cudalm_b200_set_direct_path_max_bytes(int(max_bytes)))
 
 
 def launch_count() -> int:

@@ -26,6 +26,14 @@ void tc_group_destroy(TcGroup* g);
 // Smallest M that takes the tensor-memory kernel (runtime knob; see
 // cudalm_b200_set_tensor_path_min_rows).
 std::atomic<int> g_tc_min_rows{17};
+// lean kernel for single calls of a few megabytes (w4a16_direct.cu)
+bool direct_eligible(const cudalm_b200_linear& l, const std::uint8_t* weight2);
+long long direct_weight_bytes(const cudalm_b200_linear& l, bool pair);
+int run_direct(const cudalm_b200_linear* ls, int count, const std::uint8_t* const* weight2,
+               const std::uint16_t* const* scales2, const std::uint16_t* const* residual,
+               cudaStream_t stream);
+int direct_kernel_regs();
+extern std::atomic<long long> g_direct_max_bytes;
 
 // ---------------------------------------------------------------------------
 // Fallback for inputs the streaming kernel does not take: a weight base that is
@@ -111,7 +119,8 @@ bool make_plan(int kmax, int mmax, Plan* out, bool several = false) {
   while (nt * 8 < mmax && nt < 8) nt *= 2;
   // at least 4 KB: the region doubles as reduction scratch at the kernel's end
   // activations, + the all-zero row, + the per-group offset sums [K/128][8*nt]
-  int x_bytes = round_up((mmax + 1) * (2 * kmax + 32) + (kmax / 128) * nt * 8 * 4, 128);
+  // ... + the out-of-range flag word in the buffer's last bytes
+  int x_bytes = round_up((mmax + 1) * (2 * kmax + 32) + (kmax / 128) * nt * 8 * 4, 128) + kXFlagBytes;
   if (x_bytes < 4096) x_bytes = 4096;
 #ifdef CB200_WARPS
   for (int nwarps : {CB200_WARPS}) {
@@ -331,11 +340,14 @@ struct LinearExtra {
 int to_dev(const cudalm_b200_linear& l, int mt_begin, int cost_begin, LinearDev* d,
            const LinearExtra* ex = nullptr) {
   if (int rc = encode_weight_map(l.weight, l.N, l.K, &d->tmap)) return rc;
+  d->W = l.weight;
+  d->W2 = nullptr;
   d->S2 = nullptr;
   d->res = nullptr;
   int extra_flags = 0;
   if (ex && ex->weight2) {
     if (int rc = encode_weight_map(ex->weight2, l.N, l.K, &d->tmap2)) return rc;
+    d->W2 = ex->weight2;
     d->S2 = ex->scales2;
     extra_flags |= kFlagPair | (aligned_to(ex->scales2, 16) ? kFlagScales2Bulk : 0);
   } else if (ex && ex->residual) {
@@ -365,6 +377,9 @@ int run_fallback(const cudalm_b200_linear& l, cudaStream_t stream) {
 // One projection with any M: passes of as many rows as fit in shared memory.
 int run_single(cudalm_b200_linear l, cudaStream_t stream) {
   if (int rc = validate(l)) return rc;
+  if (direct_eligible(l, nullptr) &&
+      direct_weight_bytes(l, false) <= g_direct_max_bytes.load(std::memory_order_relaxed))
+    return run_direct(&l, 1, nullptr, nullptr, nullptr, stream);
   if (l.M >= g_tc_min_rows.load(std::memory_order_relaxed)) {
     // passes of up to 64 rows on the tensor-memory kernel
     cudalm_b200_linear probe = l;
@@ -407,6 +422,13 @@ int run_extra(cudalm_b200_linear l, const LinearExtra& ex, cudaStream_t stream) 
   if (int rc = validate(l)) return rc;
   const bool pair = ex.weight2 != nullptr;
   if (pair && !ex.scales2) return CUDALM_B200_ERR_NULL;
+  if (direct_eligible(l, ex.weight2) &&
+      direct_weight_bytes(l, pair) <= g_direct_max_bytes.load(std::memory_order_relaxed)) {
+    const std::uint8_t* w2[1] = {ex.weight2};
+    const std::uint16_t* s2[1] = {ex.scales2};
+    const std::uint16_t* rs[1] = {ex.residual};
+    return run_direct(&l, 1, w2, s2, rs, stream);
+  }
   if (l.M >= g_tc_min_rows.load(std::memory_order_relaxed)) {
     // passes of up to 64 rows on the tensor-memory kernel, when it takes the call
     bool done = true;
@@ -533,6 +555,16 @@ int cudalm_b200_linear_multi(const cudalm_b200_linear* linears, int count, void*
     all_stream &= stream_eligible(linears[i]);
     kmax = linears[i].K > kmax ? linears[i].K : kmax;
     mmax = linears[i].M > mmax ? linears[i].M : mmax;
+  }
+  {
+    bool all_direct = true;
+    long long wbytes = 0;
+    for (int i = 0; i < count; ++i) {
+      all_direct &= direct_eligible(linears[i], nullptr);
+      wbytes += direct_weight_bytes(linears[i], false);
+    }
+    if (all_direct && wbytes <= g_direct_max_bytes.load(std::memory_order_relaxed))
+      return run_direct(linears, count, nullptr, nullptr, nullptr, st);
   }
   if (mmax >= g_tc_min_rows.load(std::memory_order_relaxed)) {
     bool all_tc = true;
@@ -813,6 +845,11 @@ int cudalm_b200_set_tensor_path_min_rows(int min_rows) {
   return g_tc_min_rows.exchange(min_rows);
 }
 
+int64_t cudalm_b200_set_direct_path_max_bytes(int64_t max_bytes) {
+  if (max_bytes < 0) max_bytes = 0;
+  return g_direct_max_bytes.exchange(max_bytes);
+}
+
 int64_t cudalm_b200_group_bytes(const cudalm_b200_group* group) {
   return group ? group->bytes : 0;
 }
@@ -829,6 +866,7 @@ int cudalm_b200_kernel_regs(const char* kernel_name) {
 #undef CB200_NAME
   if (std::strcmp(kernel_name, "w4a16_fallback") == 0)
     fn = reinterpret_cast<const void*>(&w4a16_fallback_kernel);
+  if (std::strcmp(kernel_name, "w4a16_direct") == 0) return direct_kernel_regs();
   if (!fn) return -1;
   cudaFuncAttributes attr;
   if (cudaFuncGetAttributes(&attr, fn) != cudaSuccess) {

@@ -41,7 +41,7 @@ constexpr int kMaxDepth = 4;
 constexpr int kMaxWarps = 16;
 // shared-memory header: "full" mbarriers [kMaxWarps][kMaxDepth], CtaControl, and in
 // its last 512 bytes the "empty" mbarriers [kMaxWarps][kMaxDepth] of the producer form
-constexpr int kHeaderBytes = 1920;
+constexpr int kHeaderBytes = 2048;
 // projections of a CTA's range whose descriptors are kept in shared memory
 constexpr int kDescCache = 8;
 // largest M*K one warp refills on its own (the barrier-free change of projection)
@@ -58,6 +58,8 @@ enum : int {
 struct alignas(64) LinearDev {
   CUtensorMap tmap;   // weight matrix as uint32 [N][K/8], box 16 rows x CG*16 words
   CUtensorMap tmap2;  // second matrix of a pair (kFlagPair)
+  const std::uint8_t* W;     // the same matrices for plain loads (activations out of range)
+  const std::uint8_t* W2;
   const std::uint16_t* S;
   const std::uint16_t* S2;   // scales of the second matrix
   const std::uint16_t* res;  // residual [M][N] (kFlagResidual)
@@ -132,6 +134,8 @@ __device__ __forceinline__ int mtile_at_cost(const StreamParams& p, long long co
 struct DescLite {
   const CUtensorMap* tmap;
   const CUtensorMap* tmap2;
+  const std::uint8_t* W;
+  const std::uint8_t* W2;
   const std::uint16_t* S;
   const std::uint16_t* S2;
   const std::uint16_t* res;
@@ -173,8 +177,8 @@ __device__ __forceinline__ void st_volatile_s32(int* p, int v) {
 __device__ __forceinline__ DescLite get_desc(const DescSource& ds, int d) {
   if (d - ds.d_first < kDescCache) return ds.cache[d - ds.d_first];
   const LinearDev* L = desc_table(*ds.p) + d;
-  return DescLite{&L->tmap, &L->tmap2, L->S, L->S2, L->res, L->x, L->y,
-                  L->N,     L->K,      L->M, L->mt_begin, L->flags, 0};
+  return DescLite{&L->tmap, &L->tmap2, L->W, L->W2, L->S, L->S2, L->res, L->x, L->y,
+                  L->N,     L->K,      L->M,  L->mt_begin, L->flags, 0};
 }
 
 // Position of a warp in the launch: an m-tile, the chunk inside it and the
@@ -341,13 +345,71 @@ __device__ __forceinline__ void store_x_value(std::uint8_t* xs, int rsx, int n, 
       float_to_bf16_bits(f);
 }
 
+// Range of activations the tiny-number arithmetic represents: x * 2^64 must stay
+// finite (|x| < 2^63; 2^62 is used), and a quantisation group whose largest magnitude is
+// below 2^-50 would lose its products to fp32 underflow.  A projection whose
+// activations fall outside (infinities and NaNs included) is flagged when its
+// activations are staged, and its m-tiles are then recomputed from global memory in
+// the CPU reference's own order (slow_mtile), so that every input a bf16 can hold gives
+// the reference's result.  The flag word sits in the last 16 bytes of an activation
+// buffer and holds (projection index + 1) of a flagged projection.
+constexpr std::uint32_t kXBigBits = (127u + 62u) << 7;
+constexpr std::uint32_t kXTinyBits = (127u - 50u) << 7;
+constexpr int kXFlagBytes = 128;  // reserved at the end of every activation buffer
+__device__ __forceinline__ std::uint32_t abs_bits4(uint2 v) {
+  const std::uint32_t a = v.x & 0x7FFF7FFFu, b = v.y & 0x7FFF7FFFu;
+  return max(max(a & 0xFFFFu, a >> 16), max(b & 0xFFFFu, b >> 16));
+}
+// `absmax` = this lane's largest |bits| over a span that the warp covers together
+// (at most one quantisation group of one activation row); all 32 lanes call.
+__device__ __forceinline__ bool span_out_of_range(std::uint32_t absmax) {
+  const std::uint32_t m = __reduce_max_sync(0xffffffffu, absmax);
+  return m >= kXBigBits || (m != 0u && m < kXTinyBits);
+}
+__device__ __forceinline__ int* x_flag_word(std::uint8_t* xs, int x_bytes) {
+  return reinterpret_cast<int*>(xs + x_bytes - 16);
+}
+
+// The m-tile's outputs of this lane's fragment, from global memory, term by term in the
+// order of the CPU reference (CUDALM tests/cuda/test_int4_gemv_bf16.cpp:54-69): for
+// each byte, acc += (lo * s) * x[2b], then acc += (hi * s) * x[2b + 1].
+template <int NT>
+__device__ __noinline__ void slow_mtile(const std::uint8_t* W, const std::uint16_t* S,
+                                        const std::uint16_t* x, int N, int K, int M, int row0,
+                                        int lane, float (&out)[NT][4]) {
+  const int r8 = lane >> 2, t = lane & 3;
+  for (int nt = 0; nt < NT; ++nt) {
+    for (int e = 0; e < 4; ++e) {
+      const int row = row0 + r8 + (e >> 1) * 8;
+      const int col = nt * 8 + 2 * t + (e & 1);
+      float a = 0.f;
+      if (row < N && col < M) {
+        const std::uint8_t* wr = W + static_cast<std::size_t>(row) * (K >> 1);
+        const std::uint16_t* sr = S + static_cast<std::size_t>(row) * (K >> 7);
+        const std::uint16_t* xr = x + static_cast<std::size_t>(col) * K;
+        for (int b = 0; b < (K >> 1); ++b) {
+          const std::uint8_t byte = wr[b];
+          const float sc = __half2float(__ushort_as_half(sr[b >> 6]));
+          const int lo = static_cast<int>(static_cast<std::int8_t>((byte & 0x0Fu) << 4)) >> 4;
+          const int hi = static_cast<int>(static_cast<std::int8_t>(byte)) >> 4;
+          a = __fadd_rn(a, __fmul_rn(__fmul_rn(static_cast<float>(lo), sc), bf16_bits_to_float(xr[2 * b])));
+          a = __fadd_rn(a, __fmul_rn(__fmul_rn(static_cast<float>(hi), sc), bf16_bits_to_float(xr[2 * b + 1])));
+        }
+      }
+      out[nt][e] = a;
+    }
+  }
+}
+
 template <int U, bool kFromShared = false>
 __device__ __forceinline__ void fill_x_fragments(std::uint8_t* xs, const std::uint16_t* x,
                                                  int M, int K, int rsx, int tid,
-                                                 int nthreads) {
+                                                 int nthreads, int* flag, int tag) {
   const int total = M * K;
+  bool bad = false;
   if ((reinterpret_cast<std::uintptr_t>(x) & 7u) == 0) {
-    // four values per 8-byte load, U loads in flight per thread
+    // four values per 8-byte load, U loads in flight per thread; a warp's 32 loads of
+    // one step are 128 consecutive values, i.e. one group of one row
     const int quads = total >> 2;
     for (int q0 = tid; q0 < quads; q0 += U * nthreads) {
       uint2 v[U];
@@ -361,6 +423,7 @@ __device__ __forceinline__ void fill_x_fragments(std::uint8_t* xs, const std::ui
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const int qi = q0 + u * nthreads;
+        bad |= span_out_of_range(abs_bits4(v[u]));
         if (qi < quads) {
           const int idx = qi << 2;
           const int n = idx / K;
@@ -375,9 +438,12 @@ __device__ __forceinline__ void fill_x_fragments(std::uint8_t* xs, const std::ui
   } else {
     for (int idx = tid; idx < total; idx += nthreads) {
       const int n = idx / K;
-      store_x_value(xs, rsx, n, idx - n * K, kFromShared ? x[idx] : __ldg(x + idx));
+      const std::uint16_t bits = kFromShared ? x[idx] : __ldg(x + idx);
+      bad |= span_out_of_range(bits & 0x7FFFu);
+      store_x_value(xs, rsx, n, idx - n * K, bits);
     }
   }
+  if (bad && (tid & 31) == 0) st_volatile_s32(flag, tag);
   for (int idx = tid; idx < K / 2; idx += nthreads)
     *reinterpret_cast<std::uint32_t*>(xs + M * rsx + idx * 4) = 0u;
 }
@@ -619,24 +685,28 @@ __device__ __forceinline__ bool service_fill(const DescSource& ds, CtaControl* c
     const int rsx = 2 * LK + 32;
     std::uint8_t* xb = x_buffer(xs0, ds.p->x_bytes, e & 1);
     const bool staged = (reinterpret_cast<std::uintptr_t>(L.x) & 15u) == 0;
+    bool bad = false;
     for (int g = warp; g < G; g += nwarps) {
       for (int n = 0; n < LM; ++n) {
         const int k = g * 128 + lane * 4;
+        uint2 v;
         if (staged) {
-          const uint2 v = *reinterpret_cast<const uint2*>(staging + (static_cast<std::size_t>(n) * LK + k) * 2);
-          store_x_value(xb, rsx, n, k, static_cast<std::uint16_t>(v.x & 0xFFFFu));
-          store_x_value(xb, rsx, n, k + 1, static_cast<std::uint16_t>(v.x >> 16));
-          store_x_value(xb, rsx, n, k + 2, static_cast<std::uint16_t>(v.y & 0xFFFFu));
-          store_x_value(xb, rsx, n, k + 3, static_cast<std::uint16_t>(v.y >> 16));
+          v = *reinterpret_cast<const uint2*>(staging + (static_cast<std::size_t>(n) * LK + k) * 2);
         } else {
           const std::uint16_t* src = L.x + static_cast<std::size_t>(n) * LK + k;
-#pragma unroll
-          for (int i = 0; i < 4; ++i) store_x_value(xb, rsx, n, k + i, __ldg(src + i));
+          v.x = static_cast<std::uint32_t>(__ldg(src)) | (static_cast<std::uint32_t>(__ldg(src + 1)) << 16);
+          v.y = static_cast<std::uint32_t>(__ldg(src + 2)) | (static_cast<std::uint32_t>(__ldg(src + 3)) << 16);
         }
+        bad |= span_out_of_range(abs_bits4(v));
+        store_x_value(xb, rsx, n, k, static_cast<std::uint16_t>(v.x & 0xFFFFu));
+        store_x_value(xb, rsx, n, k + 1, static_cast<std::uint16_t>(v.x >> 16));
+        store_x_value(xb, rsx, n, k + 2, static_cast<std::uint16_t>(v.y & 0xFFFFu));
+        store_x_value(xb, rsx, n, k + 3, static_cast<std::uint16_t>(v.y >> 16));
       }
       // the all-zero row's part of this group
       *reinterpret_cast<uint2*>(xb + LM * rsx + g * 256 + lane * 8) = make_uint2(0u, 0u);
     }
+    if (bad && lane == 0) st_volatile_s32(x_flag_word(xb, ds.p->x_bytes), e + 1);
     __syncwarp();
     build_bias<NT>(xb, reinterpret_cast<float*>(xb + (LM + 1) * rsx), G, rsx, LM, warp, lane, nwarps);
     __threadfence_block();
@@ -740,6 +810,8 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
   }
   if (tid < NWARPS) ctl->issued[tid] = 0;
   if (tid == 0) {
+    *x_flag_word(xs0, p.x_bytes) = 0;
+    if (async_switch) *x_flag_word(xs0 + p.x_bytes, p.x_bytes) = 0;
     ctl->fill_claim = ctl->fill_done = d_first;
     ctl->fill_parts = 0;
     ctl->abort = 0;
@@ -751,11 +823,12 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
     // descriptors are written when a launch is set up, never by a kernel, so
     // they may be read before the wait on the previous grid
     const int d = d_first + tid;
-    DescLite v{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0x7fffffff, 0, 0};
+    DescLite v{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr,
+               0,       0,       0,       0x7fffffff, 0, 0};
     if (d < p.n_desc) {
       const LinearDev* L = desc_table(p) + d;
-      v = DescLite{&L->tmap, &L->tmap2, L->S, L->S2, L->res, L->x, L->y,
-                   L->N,     L->K,      L->M, L->mt_begin, L->flags, 0};
+      v = DescLite{&L->tmap, &L->tmap2, L->W, L->W2, L->S, L->S2, L->res, L->x, L->y,
+                   L->N,     L->K,      L->M,  L->mt_begin, L->flags, 0};
     }
     ctl->desc[tid] = v;
   }
@@ -900,7 +973,7 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
       // the whole CTA refills the buffer together
       consumer_sync();  // every warp is done with the previous activations
       xs = x_buffer(xs0, p.x_bytes, async_switch ? (d & 1) : 0);
-      fill_x_fragments<4>(xs, L.x, LM, LK, rsx, tid, NWARPS * 32);
+      fill_x_fragments<4>(xs, L.x, LM, LK, rsx, tid, NWARPS * 32, x_flag_word(xs, p.x_bytes), d + 1);
       consumer_sync();
       build_bias<NT>(xs, reinterpret_cast<float*>(xs + (LM + 1) * rsx), G, rsx, LM, warp, lane,
                      NWARPS);
@@ -926,6 +999,8 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
       xs = x_buffer(xs0, p.x_bytes, d & 1);
     }
     const float* bias = reinterpret_cast<const float*>(xs + (LM + 1) * rsx);
+    // activations outside the range of the tiny-number arithmetic: see slow_mtile
+    const bool odd = ld_volatile_s32(x_flag_word(xs, p.x_bytes)) == d + 1;
 
     while (cc.valid && cc.d == d) {
       float acc[NT][4];
@@ -990,16 +1065,31 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
         }
       }
       cc_next_mtile();
+      float out_scale = CB200_OUT_SCALE;
+      if (odd && !dead) {
+        out_scale = 1.0f;
+        if (EXTRA && NT <= 2 && (L.flags & kFlagPair)) {
+          float g[NT][4];
+          slow_mtile<NT>(L.W, L.S, L.x, LN, LK, LM, row0, lane, g);
+#pragma unroll
+          for (int nt = 0; nt < kGateTiles; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) gate[nt][i] = bf16_bits_to_float(float_to_bf16_bits(g[nt][i]));
+          slow_mtile<NT>(L.W2, L.S2, L.x, LN, LK, LM, row0, lane, acc);
+        } else {
+          slow_mtile<NT>(L.W, L.S, L.x, LN, LK, LM, row0, lane, acc);
+        }
+      }
       if (!dead) {
         const int r8 = lane >> 2, t = lane & 3;
         const int row_lo = row0 + r8, row_hi = row_lo + 8;
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
           const int col = nt * 8 + 2 * t;
-          std::uint16_t o0 = float_to_bf16_bits(acc[nt][0] * CB200_OUT_SCALE);
-          std::uint16_t o1 = float_to_bf16_bits(acc[nt][1] * CB200_OUT_SCALE);
-          std::uint16_t o2 = float_to_bf16_bits(acc[nt][2] * CB200_OUT_SCALE);
-          std::uint16_t o3 = float_to_bf16_bits(acc[nt][3] * CB200_OUT_SCALE);
+          std::uint16_t o0 = float_to_bf16_bits(acc[nt][0] * out_scale);
+          std::uint16_t o1 = float_to_bf16_bits(acc[nt][1] * out_scale);
+          std::uint16_t o2 = float_to_bf16_bits(acc[nt][2] * out_scale);
+          std::uint16_t o3 = float_to_bf16_bits(acc[nt][3] * out_scale);
           if (EXTRA && NT <= 2 && (L.flags & kFlagPair)) {
             // CUDALM's rounding order (src/kernels/qwen35_kernels.cu:459-476):
             // s = bf16(g / (1 + exp(-g))), then bf16(float(s) * float(u))

@@ -307,4 +307,237 @@ int cudalm_b200_v2_linear(const cudalm_b200_v2_file* f, const char* weight_name,
   return CUDALM_B200_OK;
 }
 
+// ---------------------------------------------------------------------------
+// Model-level loading: the tensor set of one decoder layer, checked against the
+// file's configuration and uploaded (CUDALM src/runtime/weight_loader_v2.cpp:
+// validate_layer 273-372, validate_full_model 383-408, Qwen35LayerWeights::load
+// 416-499).
+// ---------------------------------------------------------------------------
+}  // extern "C"
+
+namespace {
+
+struct ModelConfig {
+  int hidden, layers, inter, vocab, heads, kv_heads, head_dim;
+  int lin_k_heads, lin_v_heads, lin_kd, lin_vd, conv, interval, group;
+};
+
+ModelConfig read_config(const cudalm_b200_v2_file* f) {
+  const std::uint8_t* c = f->bytes.data() + f->config_offset;
+  ModelConfig m;
+  m.hidden = i32_at(c + 0);
+  m.layers = i32_at(c + 4);
+  m.inter = i32_at(c + 8);
+  m.vocab = i32_at(c + 12);
+  m.heads = i32_at(c + 16);
+  m.kv_heads = i32_at(c + 20);
+  m.head_dim = i32_at(c + 24);
+  m.lin_k_heads = i32_at(c + 28);
+  m.lin_v_heads = i32_at(c + 32);
+  m.lin_kd = i32_at(c + 36);
+  m.lin_vd = i32_at(c + 40);
+  m.conv = i32_at(c + 44);
+  m.interval = i32_at(c + 48);
+  m.group = i32_at(c + 52);
+  return m;
+}
+
+// CUDALM include/cudalm/qwen35_config.h:82-85
+bool is_full_attention(const ModelConfig& c, int i) {
+  return i >= 0 && i < c.layers && c.interval > 0 && (i + 1) % c.interval == 0;
+}
+
+const char* dtype_name(int dtype) {
+  switch (dtype) {
+    case CUDALM_B200_V2_FP16: return "fp16";
+    case CUDALM_B200_V2_INT4_PACKED: return "int4_packed";
+    case CUDALM_B200_V2_FP16_SCALE: return "fp16_scale";
+    case CUDALM_B200_V2_FP32: return "fp32";
+    case CUDALM_B200_V2_BF16: return "bf16";
+    default: return "?";
+  }
+}
+
+// One tensor a layer must hold.  `proj` >= 0: the weight (part 0) or scale (part 1)
+// of that projection; else `aux` >= 0: one of the layer's other tensors.
+struct Expect {
+  std::string name;
+  int dtype;
+  std::vector<long long> dims;
+  int proj, part, aux;
+};
+
+// The layer's tensors in the order the reference checks them, so that the first
+// fault found is the one it reports.
+std::vector<Expect> layer_expectations(const ModelConfig& c, int layer) {
+  const std::string L = "layers." + std::to_string(layer) + ".";
+  const long long H = c.hidden, G = c.group;
+  std::vector<Expect> out;
+  auto aux = [&](const char* n, int dtype, std::vector<long long> dims, int slot) {
+    out.push_back(Expect{L + n, dtype, std::move(dims), -1, 0, slot});
+  };
+  auto weight = [&](const char* n, long long N, long long K, int proj) {
+    out.push_back(Expect{L + n + ".weight", CUDALM_B200_V2_INT4_PACKED, {N, K / 2}, proj, 0, -1});
+  };
+  auto scale = [&](const char* n, long long N, long long K, int proj) {
+    out.push_back(Expect{L + n + ".scale", CUDALM_B200_V2_FP16_SCALE, {N, K / G}, proj, 1, -1});
+  };
+  aux("input_layernorm.weight", CUDALM_B200_V2_BF16, {H}, CUDALM_B200_AUX_INPUT_LAYERNORM);
+  aux("post_attention_layernorm.weight", CUDALM_B200_V2_BF16, {H}, CUDALM_B200_AUX_POST_ATTENTION_LAYERNORM);
+  weight("mlp.gate_proj", c.inter, H, CUDALM_B200_PROJ_GATE);
+  weight("mlp.up_proj", c.inter, H, CUDALM_B200_PROJ_UP);
+  scale("mlp.gate_proj", c.inter, H, CUDALM_B200_PROJ_GATE);
+  scale("mlp.up_proj", c.inter, H, CUDALM_B200_PROJ_UP);
+  weight("mlp.down_proj", H, c.inter, CUDALM_B200_PROJ_DOWN);
+  scale("mlp.down_proj", H, c.inter, CUDALM_B200_PROJ_DOWN);
+  if (is_full_attention(c, layer)) {
+    const long long qo = 2ll * c.heads * c.head_dim, kvo = 1ll * c.kv_heads * c.head_dim;
+    const long long oin = 1ll * c.heads * c.head_dim;
+    weight("self_attn.q_proj", qo, H, CUDALM_B200_PROJ_Q);
+    scale("self_attn.q_proj", qo, H, CUDALM_B200_PROJ_Q);
+    weight("self_attn.k_proj", kvo, H, CUDALM_B200_PROJ_K);
+    scale("self_attn.k_proj", kvo, H, CUDALM_B200_PROJ_K);
+    weight("self_attn.v_proj", kvo, H, CUDALM_B200_PROJ_V);
+    scale("self_attn.v_proj", kvo, H, CUDALM_B200_PROJ_V);
+    weight("self_attn.o_proj", H, oin, CUDALM_B200_PROJ_O);
+    scale("self_attn.o_proj", H, oin, CUDALM_B200_PROJ_O);
+    aux("self_attn.q_norm.weight", CUDALM_B200_V2_BF16, {c.head_dim}, CUDALM_B200_AUX_Q_NORM);
+    aux("self_attn.k_norm.weight", CUDALM_B200_V2_BF16, {c.head_dim}, CUDALM_B200_AUX_K_NORM);
+  } else {
+    const long long cv = 1ll * c.lin_v_heads * c.lin_vd;
+    const long long cd = 2ll * c.lin_k_heads * c.lin_kd + cv;
+    weight("linear_attn.in_proj_qkv", cd, H, CUDALM_B200_PROJ_IN_QKV);
+    scale("linear_attn.in_proj_qkv", cd, H, CUDALM_B200_PROJ_IN_QKV);
+    weight("linear_attn.in_proj_z", cv, H, CUDALM_B200_PROJ_IN_Z);
+    scale("linear_attn.in_proj_z", cv, H, CUDALM_B200_PROJ_IN_Z);
+    weight("linear_attn.in_proj_b", c.lin_v_heads, H, CUDALM_B200_PROJ_IN_B);
+    scale("linear_attn.in_proj_b", c.lin_v_heads, H, CUDALM_B200_PROJ_IN_B);
+    weight("linear_attn.in_proj_a", c.lin_v_heads, H, CUDALM_B200_PROJ_IN_A);
+    scale("linear_attn.in_proj_a", c.lin_v_heads, H, CUDALM_B200_PROJ_IN_A);
+    weight("linear_attn.out_proj", H, cv, CUDALM_B200_PROJ_OUT);
+    scale("linear_attn.out_proj", H, cv, CUDALM_B200_PROJ_OUT);
+    aux("linear_attn.conv1d.weight", CUDALM_B200_V2_BF16, {cd, 1, c.conv}, CUDALM_B200_AUX_CONV1D);
+    aux("linear_attn.dt_bias", CUDALM_B200_V2_BF16, {c.lin_v_heads}, CUDALM_B200_AUX_DT_BIAS);
+    aux("linear_attn.A_log", CUDALM_B200_V2_FP32, {c.lin_v_heads}, CUDALM_B200_AUX_A_LOG);
+    aux("linear_attn.norm.weight", CUDALM_B200_V2_FP32, {c.lin_vd}, CUDALM_B200_AUX_LINEAR_NORM);
+  }
+  return out;
+}
+
+// The reference's expect_tensor: empty string when the tensor is as expected.
+std::string check_tensor(const cudalm_b200_v2_file* f, const std::string& name, int dtype,
+                         const std::vector<long long>& dims, int* index) {
+  const auto it = f->by_name.find(name);
+  if (it == f->by_name.end()) return "missing tensor '" + name + "'";
+  const Entry& e = f->tensors[static_cast<size_t>(it->second)];
+  if (e.dtype != dtype) return "dtype mismatch for '" + name + "' (expected " + dtype_name(dtype) + ")";
+  bool same = e.ndim == static_cast<int>(dims.size());
+  for (int d = 0; same && d < e.ndim; ++d) same = e.dims[d] == dims[static_cast<size_t>(d)];
+  if (!same) return "shape mismatch for '" + name + "' (expected " + std::to_string(dims.size()) + "-D)";
+  if (index) *index = it->second;
+  return std::string();
+}
+
+std::string validate_layer_impl(const cudalm_b200_v2_file* f, int layer, std::vector<int>* indices) {
+  const ModelConfig c = read_config(f);
+  if (layer < 0 || layer >= c.layers) return "layer_idx out of range";
+  const std::vector<Expect> want = layer_expectations(c, layer);
+  if (indices) indices->assign(want.size(), -1);
+  for (size_t i = 0; i < want.size(); ++i) {
+    const std::string why =
+        check_tensor(f, want[i].name, want[i].dtype, want[i].dims, indices ? &(*indices)[i] : nullptr);
+    if (!why.empty()) return why;
+  }
+  return std::string();
+}
+
+constexpr std::uint64_t kSlotAlign = 256;  // as CUDALM's DeviceBuffer (include/cudalm/device_buffer.h:17-68)
+std::uint64_t slot_bytes(std::uint64_t n) { return (n + kSlotAlign - 1) / kSlotAlign * kSlotAlign; }
+
+}  // namespace
+
+extern "C" {
+
+int cudalm_b200_v2_validate_layer(const cudalm_b200_v2_file* f, int layer_idx, char* err, size_t err_cap) {
+  if (!f) return CUDALM_B200_ERR_NULL;
+  const std::string why = validate_layer_impl(f, layer_idx, nullptr);
+  if (why.empty()) return CUDALM_B200_OK;
+  put_error(err, err_cap, why);
+  return CUDALM_B200_ERR_FILE;
+}
+
+int cudalm_b200_v2_validate_full_model(const cudalm_b200_v2_file* f, char* err, size_t err_cap) {
+  if (!f) return CUDALM_B200_ERR_NULL;
+  const ModelConfig c = read_config(f);
+  std::string why = check_tensor(f, "embed_tokens.weight", CUDALM_B200_V2_BF16, {c.vocab, c.hidden}, nullptr);
+  if (why.empty()) why = check_tensor(f, "norm.weight", CUDALM_B200_V2_BF16, {c.hidden}, nullptr);
+  for (int i = 0; why.empty() && i < c.layers; ++i) {
+    why = validate_layer_impl(f, i, nullptr);
+    if (!why.empty()) why = "layer " + std::to_string(i) + ": " + why;
+  }
+  if (why.empty()) {
+    // the vocabulary projection is tied to the embedding in the model this format carries
+    bool tied = false;
+    for (const auto& kv : f->metadata) tied |= kv.first == "tie_word_embeddings" && kv.second == "true";
+    if (!tied) why = "full model: tie_word_embeddings metadata must be \"true\"";
+  }
+  if (why.empty()) return CUDALM_B200_OK;
+  put_error(err, err_cap, why);
+  return CUDALM_B200_ERR_FILE;
+}
+
+size_t cudalm_b200_v2_layer_device_bytes(const cudalm_b200_v2_file* f, int layer_idx) {
+  if (!f) return 0;
+  std::vector<int> idx;
+  if (!validate_layer_impl(f, layer_idx, &idx).empty()) return 0;
+  std::uint64_t total = 0;
+  for (int i : idx) total += slot_bytes(f->tensors[static_cast<size_t>(i)].byte_size);
+  return static_cast<size_t>(total);
+}
+
+int cudalm_b200_v2_load_layer(const cudalm_b200_v2_file* f, int layer_idx, void* device_dst, size_t capacity,
+                              void* stream, cudalm_b200_v2_layer* out, char* err, size_t err_cap) {
+  if (!f || !device_dst || !out) return CUDALM_B200_ERR_NULL;
+  std::vector<int> idx;
+  const std::string why = validate_layer_impl(f, layer_idx, &idx);
+  if (!why.empty()) {
+    put_error(err, err_cap, why);
+    return CUDALM_B200_ERR_FILE;
+  }
+  if ((reinterpret_cast<std::uintptr_t>(device_dst) & (kSlotAlign - 1)) != 0) return CUDALM_B200_ERR_MISALIGNED;
+  const ModelConfig c = read_config(f);
+  const std::vector<Expect> want = layer_expectations(c, layer_idx);
+  std::uint64_t total = 0;
+  for (int i : idx) total += slot_bytes(f->tensors[static_cast<size_t>(i)].byte_size);
+  if (capacity < total) return CUDALM_B200_ERR_TOO_LARGE;
+  std::memset(out, 0, sizeof(*out));
+  out->layer_idx = layer_idx;
+  out->full_attention = is_full_attention(c, layer_idx) ? 1 : 0;
+  std::uint8_t* dst = static_cast<std::uint8_t*>(device_dst);
+  std::uint64_t off = 0;
+  using namespace cb200;
+  for (size_t i = 0; i < want.size(); ++i) {
+    const Entry& e = f->tensors[static_cast<size_t>(idx[i])];
+    CB200_CUDA_TRY(cudaMemcpyAsync(dst + off, f->bytes.data() + f->payload_offset + e.offset, e.byte_size,
+                                   cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream)));
+    if (want[i].proj >= 0) {
+      cudalm_b200_linear& l = out->proj[want[i].proj];
+      if (want[i].part == 0) {
+        l.weight = dst + off;
+        // CUDALM src/runtime/weight_loader_v2.cpp:479-482: N = dim 0, K = 2 * dim 1
+        l.N = static_cast<int32_t>(e.dims[0]);
+        l.K = static_cast<int32_t>(2 * e.dims[1]);
+      } else {
+        l.scales = reinterpret_cast<const uint16_t*>(dst + off);
+      }
+    } else {
+      out->aux[want[i].aux] = dst + off;
+      out->aux_dtype[want[i].aux] = e.dtype;
+      out->aux_bytes[want[i].aux] = e.byte_size;
+    }
+    off += slot_bytes(e.byte_size);
+  }
+  return CUDALM_B200_OK;
+}
+
 }  // extern "C"

@@ -11,6 +11,12 @@
 * ``quantized_tensors`` turns a bf16 matrix on the GPU into the two records of a
   W4A16 projection with the library's quantizer (the GPU form of
   tools/convert_qwen35.py:181-189).
+* ``V2Reader.validate_layer`` / ``validate_full_model`` / ``load_layer`` are the
+  model-level loader: a layer's tensor set checked against the configuration and
+  uploaded, its W4A16 projections returned ready to call
+  (src/runtime/weight_loader_v2.cpp:273-372, 383-408, 416-499).
+* ``convert_safetensors`` walks a bf16 safetensors checkpoint as CUDALM's converter
+  does (tools/convert_qwen35.py:181-264) and writes the v2 file, quantizing on the GPU.
 """
 from __future__ import annotations
 
@@ -33,6 +39,95 @@ PAYLOAD_ALIGN = 16
 
 class V2FormatError(ValueError):
     """A file the reader rejects, or a record the writer cannot emit."""
+
+
+class ModelConfig(NamedTuple):
+    """The 88-byte configuration blob of a v2 file (field order is part of the
+    format: CUDALM include/cudalm/weight_format_v2.h, tools/common/cudalm_v2.py:95-221)."""
+    hidden_size: int
+    num_hidden_layers: int
+    intermediate_size: int
+    vocab_size: int
+    n_heads: int
+    n_kv_heads: int
+    head_dim: int
+    lin_num_k_heads: int
+    lin_num_v_heads: int
+    lin_key_head_dim: int
+    lin_value_head_dim: int
+    lin_conv_kernel_dim: int
+    full_attention_interval: int
+    group_size: int
+    max_seq_len: int
+    eps: float
+    rope_theta: float
+    partial_rotary_factor: float
+    mrope_section: Tuple[int, int, int] = (11, 11, 10)
+
+    def to_blob(self) -> bytes:
+        return struct.pack("<15i3f4i", *self[:15], self.eps, self.rope_theta,
+                           self.partial_rotary_factor, *self.mrope_section, 0)
+
+    @classmethod
+    def from_blob(cls, blob: bytes) -> "ModelConfig":
+        v = struct.unpack("<15i3f4i", blob)
+        if v[21] != 0:
+            raise V2FormatError("config blob reserved word must be 0")
+        return cls(*v[:18], tuple(v[18:21]))
+
+    # derived sizes (CUDALM include/cudalm/qwen35_config.h:55-88)
+    @property
+    def q_proj_out(self) -> int:
+        return self.n_heads * self.head_dim * 2
+
+    @property
+    def kv_proj_out(self) -> int:
+        return self.n_kv_heads * self.head_dim
+
+    @property
+    def o_proj_in(self) -> int:
+        return self.n_heads * self.head_dim
+
+    @property
+    def linear_value_dim(self) -> int:
+        return self.lin_num_v_heads * self.lin_value_head_dim
+
+    @property
+    def linear_conv_dim(self) -> int:
+        return 2 * self.lin_num_k_heads * self.lin_key_head_dim + self.linear_value_dim
+
+    def is_full_attention(self, i: int) -> bool:
+        return 0 <= i < self.num_hidden_layers and (i + 1) % self.full_attention_interval == 0
+
+
+# names of cudalm_b200_v2_layer.proj[] / .aux[] in index order
+PROJECTIONS = ("mlp.gate_proj", "mlp.up_proj", "mlp.down_proj", "self_attn.q_proj", "self_attn.k_proj",
+               "self_attn.v_proj", "self_attn.o_proj", "linear_attn.in_proj_qkv",
+               "linear_attn.in_proj_z", "linear_attn.in_proj_b", "linear_attn.in_proj_a",
+               "linear_attn.out_proj")
+AUX_TENSORS = ("input_layernorm.weight", "post_attention_layernorm.weight", "self_attn.q_norm.weight",
+               "self_attn.k_norm.weight", "linear_attn.conv1d.weight", "linear_attn.dt_bias",
+               "linear_attn.A_log", "linear_attn.norm.weight")
+
+
+class _LayerStruct(ctypes.Structure):
+    _fields_ = [("layer_idx", ctypes.c_int32), ("full_attention", ctypes.c_int32),
+                ("proj", api._LinearStruct * len(PROJECTIONS)),
+                ("aux", ctypes.c_void_p * len(AUX_TENSORS)),
+                ("aux_dtype", ctypes.c_int32 * len(AUX_TENSORS)),
+                ("aux_bytes", ctypes.c_uint64 * len(AUX_TENSORS))]
+
+
+class LayerWeights:
+    """One decoder layer on the GPU (CUDALM's Qwen35LayerWeights,
+    include/cudalm/weight_loader_v2.h:60-110): ``linears`` maps the layer's projection
+    names (``mlp.gate_proj``, ``self_attn.q_proj``, ``linear_attn.in_proj_qkv`` ...) to
+    ``W4A16Linear`` and ``aux`` its other tensors by name; all are views of ``buffer``."""
+
+    def __init__(self, layer_idx: int, full_attention: bool, buffer: torch.Tensor,
+                 linears: Dict[str, "api.W4A16Linear"], aux: Dict[str, torch.Tensor]):
+        self.layer_idx, self.full_attention, self.buffer = layer_idx, full_attention, buffer
+        self.linears, self.aux = linears, aux
 
 
 class TensorInfo(NamedTuple):
@@ -116,6 +211,59 @@ class V2Reader:
         api._check("v2_upload", self._lib.cudalm_b200_v2_upload(
             self._h, i, api._ptr(out), out.numel() * out.element_size(), api._stream()))
         return out
+
+    @property
+    def config(self) -> ModelConfig:
+        return ModelConfig.from_blob(self.config_blob)
+
+    def validate_layer(self, layer_idx: int) -> None:
+        """Raises ``V2FormatError`` with the reference's message unless layer
+        ``layer_idx`` holds its full tensor set with the dtypes and shapes the
+        configuration implies."""
+        err = ctypes.create_string_buffer(512)
+        st = self._lib.cudalm_b200_v2_validate_layer(self._h, int(layer_idx), err, len(err))
+        if st != 0:
+            raise V2FormatError(err.value.decode(errors="replace") or f"status {st}")
+
+    def validate_full_model(self) -> None:
+        """Embedding, final norm, every layer and the tied vocabulary projection."""
+        err = ctypes.create_string_buffer(512)
+        st = self._lib.cudalm_b200_v2_validate_full_model(self._h, err, len(err))
+        if st != 0:
+            raise V2FormatError(err.value.decode(errors="replace") or f"status {st}")
+
+    def load_layer(self, layer_idx: int, device: str = "cuda") -> LayerWeights:
+        """Validates and uploads one layer into a single device buffer."""
+        nbytes = int(self._lib.cudalm_b200_v2_layer_device_bytes(self._h, int(layer_idx)))
+        if nbytes == 0:
+            self.validate_layer(layer_idx)
+            raise V2FormatError(f"layer {layer_idx} is empty")
+        buf = torch.empty(nbytes, dtype=torch.uint8, device=device)  # 512-byte aligned by torch
+        out = _LayerStruct()
+        err = ctypes.create_string_buffer(512)
+        st = self._lib.cudalm_b200_v2_load_layer(self._h, int(layer_idx), api._ptr(buf), nbytes,
+                                                 api._stream(), ctypes.byref(out), err, len(err))
+        if st != 0:
+            raise V2FormatError(err.value.decode(errors="replace") or f"load_layer: status {st}")
+        torch.cuda.current_stream().synchronize()  # the copies read the handle's host bytes
+        base = buf.data_ptr()
+
+        def view(ptr: int, nb: int, dtype: torch.dtype, shape) -> torch.Tensor:
+            return buf[ptr - base:ptr - base + nb].view(dtype).view(shape)
+
+        linears: Dict[str, "api.W4A16Linear"] = {}
+        for name, l in zip(PROJECTIONS, out.proj):
+            if not l.weight:
+                continue
+            n, k = int(l.N), int(l.K)
+            linears[name] = api.W4A16Linear(view(l.weight, n * k // 2, torch.uint8, (n, k // 2)),
+                                            view(l.scales, n * (k // 128) * 2, torch.float16, (n, k // 128)))
+        aux: Dict[str, torch.Tensor] = {}
+        for name, ptr, dt, nb in zip(AUX_TENSORS, out.aux, out.aux_dtype, out.aux_bytes):
+            if ptr:
+                info = self.find(f"layers.{layer_idx}.{name}")
+                aux[name] = view(ptr, int(nb), _TORCH_DTYPE[int(dt)], info.dims)
+        return LayerWeights(int(layer_idx), bool(out.full_attention), buf, linears, aux)
 
     def linear(self, weight_name: str, scale_name: str) -> "api.W4A16Linear":
         """A W4A16 projection stored as int4_packed [N, K/2] + fp16_scale [N, K/128]."""
@@ -216,3 +364,62 @@ def quantized_tensors(weight_name: str, scale_name: str, w_bf16: torch.Tensor) -
     return [Record(weight_name, DT_INT4_PACKED, (n, k // 2), packed.cpu().numpy().tobytes()),
             Record(scale_name, DT_FP16_SCALE, (n, k // 128),
                    scale.cpu().view(torch.uint8).numpy().tobytes())]
+
+
+def convert_safetensors(st_path: str, out_path: str, config: ModelConfig, metadata: Dict[str, str],
+                        layers: Optional[Sequence[int]] = None, full_model: bool = False,
+                        prefix: str = "model.language_model.", device: str = "cuda") -> List[Record]:
+    """bf16 safetensors checkpoint -> ``.cudalm`` v2, the walk of CUDALM's converter
+    (tools/convert_qwen35.py:181-264) with the projections quantized by this library
+    on the GPU: per layer the input layernorm, the attention or DeltaNet tensors, the
+    post-attention layernorm and the MLP, then the final norm and, for a full model,
+    the embedding (to which the vocabulary projection is tied).  Tensor order, names,
+    dtypes and bytes are the reference converter's; ``metadata`` is written as given."""
+    from safetensors import safe_open
+
+    n_layers = config.num_hidden_layers
+    layer_list = list(range(n_layers)) if (full_model or layers is None) else sorted(set(layers))
+    for i in layer_list:
+        if not 0 <= i < n_layers:
+            raise V2FormatError(f"layer {i} out of range")
+    records: List[Record] = []
+
+    with safe_open(st_path, framework="pt") as f:
+        def get(name: str) -> torch.Tensor:
+            return f.get_tensor(prefix + name)
+
+        def plain(name: str, want: torch.dtype) -> None:
+            t = get(name)
+            if t.dtype != want:
+                raise V2FormatError(f"{name}: expected {want} source, got {t.dtype}")
+            records.append(tensor_record(name, t))
+
+        def w4(name: str) -> None:
+            t = get(name + ".weight")
+            if t.dtype != torch.bfloat16 or t.dim() != 2:
+                raise V2FormatError(f"{name}: expected a 2-D bf16 source")
+            records.extend(quantized_tensors(name + ".weight", name + ".scale", t.to(device)))
+
+        for i in layer_list:
+            L = f"layers.{i}."
+            plain(L + "input_layernorm.weight", torch.bfloat16)
+            if config.is_full_attention(i):
+                for p in ("q_proj", "k_proj", "v_proj", "o_proj"):
+                    w4(L + "self_attn." + p)
+                plain(L + "self_attn.q_norm.weight", torch.bfloat16)
+                plain(L + "self_attn.k_norm.weight", torch.bfloat16)
+            else:
+                for p in ("in_proj_qkv", "in_proj_z", "in_proj_b", "in_proj_a", "out_proj"):
+                    w4(L + "linear_attn." + p)
+                plain(L + "linear_attn.conv1d.weight", torch.bfloat16)
+                plain(L + "linear_attn.dt_bias", torch.bfloat16)
+                plain(L + "linear_attn.A_log", torch.float32)
+                plain(L + "linear_attn.norm.weight", torch.float32)
+            plain(L + "post_attention_layernorm.weight", torch.bfloat16)
+            for p in ("gate_proj", "up_proj", "down_proj"):
+                w4(L + "mlp." + p)
+        plain("norm.weight", torch.bfloat16)
+        if full_model:
+            plain("embed_tokens.weight", torch.bfloat16)
+    write_v2(out_path, config.to_blob(), metadata, records)
+    return records

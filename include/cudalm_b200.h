@@ -322,6 +322,53 @@ CUDALM_B200_API int cudalm_b200_v2_linear(const cudalm_b200_v2_file* file, const
                              const char* scale_name, int* weight_index, int* scale_index,
                              int* N, int* K);
 
+/* ---- model-level loading ----------------------------------------------------------
+ * The tensor set of one decoder layer, checked against the file's configuration
+ * and uploaded: CUDALM's WeightFileV2::validate_layer / validate_full_model and
+ * Qwen35LayerWeights::load (src/runtime/weight_loader_v2.cpp:273-372, 383-408,
+ * 416-499; include/cudalm/weight_loader_v2.h:39,83-84).  A layer is a gated-
+ * DeltaNet layer or, every full_attention_interval-th one, a full-attention layer
+ * (include/cudalm/qwen35_config.h:82-88); both hold the MLP.  validate_* return
+ * CUDALM_B200_ERR_FILE with the reference's message in `err` ("missing tensor
+ * '...'", "dtype mismatch for '...'", "shape mismatch for '...'").
+ *
+ * load_layer uploads the layer's 24 tensors into caller-owned device memory
+ * (`device_dst`, 256-byte aligned, at least cudalm_b200_v2_layer_device_bytes();
+ * every tensor starts on a 256-byte boundary, as CUDALM's DeviceBuffer gives) with
+ * one copy per tensor on `stream`, and fills `out`: proj[] holds the layer's W4A16
+ * projections with weight, scales, N = dim 0 and K = 2 * dim 1 set and x, y, M left
+ * zero for the caller; projections the layer type lacks stay all-zero.  The file
+ * handle must stay open until the copies have completed. */
+enum {
+  CUDALM_B200_PROJ_GATE = 0, CUDALM_B200_PROJ_UP, CUDALM_B200_PROJ_DOWN,
+  CUDALM_B200_PROJ_Q, CUDALM_B200_PROJ_K, CUDALM_B200_PROJ_V, CUDALM_B200_PROJ_O,
+  CUDALM_B200_PROJ_IN_QKV, CUDALM_B200_PROJ_IN_Z, CUDALM_B200_PROJ_IN_B,
+  CUDALM_B200_PROJ_IN_A, CUDALM_B200_PROJ_OUT,
+  CUDALM_B200_LAYER_PROJECTIONS
+};
+enum {
+  CUDALM_B200_AUX_INPUT_LAYERNORM = 0, CUDALM_B200_AUX_POST_ATTENTION_LAYERNORM,
+  CUDALM_B200_AUX_Q_NORM, CUDALM_B200_AUX_K_NORM, CUDALM_B200_AUX_CONV1D,
+  CUDALM_B200_AUX_DT_BIAS, CUDALM_B200_AUX_A_LOG, CUDALM_B200_AUX_LINEAR_NORM,
+  CUDALM_B200_LAYER_AUX
+};
+typedef struct cudalm_b200_v2_layer {
+  int32_t layer_idx;
+  int32_t full_attention; /* 1: q, k, v, o; 0: in_proj_qkv, z, b, a and out_proj */
+  cudalm_b200_linear proj[CUDALM_B200_LAYER_PROJECTIONS];
+  const void* aux[CUDALM_B200_LAYER_AUX];     /* the layer's other tensors (device) */
+  int32_t aux_dtype[CUDALM_B200_LAYER_AUX];   /* CUDALM_B200_V2_* */
+  uint64_t aux_bytes[CUDALM_B200_LAYER_AUX];
+} cudalm_b200_v2_layer;
+CUDALM_B200_API int cudalm_b200_v2_validate_layer(const cudalm_b200_v2_file* file, int layer_idx,
+                             char* err, size_t err_cap);
+CUDALM_B200_API int cudalm_b200_v2_validate_full_model(const cudalm_b200_v2_file* file, char* err,
+                             size_t err_cap);
+CUDALM_B200_API size_t cudalm_b200_v2_layer_device_bytes(const cudalm_b200_v2_file* file, int layer_idx);
+CUDALM_B200_API int cudalm_b200_v2_load_layer(const cudalm_b200_v2_file* file, int layer_idx,
+                             void* device_dst, size_t capacity, void* stream,
+                             cudalm_b200_v2_layer* out, char* err, size_t err_cap);
+
 /* ---- quantize + pack --------------------------------------------------------
  * GPU form of CUDALM's offline quantizer quantize_w4a16
  * (CUDALM tools/common/w4a16_quant.py:25-60): bf16 W [N, K] ->
@@ -338,6 +385,14 @@ CUDALM_B200_API int cudalm_b200_quantize_w4a16(const uint16_t* w_bf16, int N, in
  * batch kernel is the M = 1 kernel with blockIdx.y = b,
  * src/kernels/batch_decode.cu:95-190.) */
 CUDALM_B200_API int cudalm_b200_set_tensor_path_min_rows(int min_rows);
+/* Single calls (int4_gemv_bf16, batch_int4_gemv_bf16, linear_multi, gate_up*,
+ * linear_residual) with at most 8 activation rows whose weights total at most
+ * max_bytes take the lean kernel, which has no set-up cost and answers a call of a
+ * few megabytes in about one memory round trip; larger ones stream through the
+ * persistent kernel.  0 switches the lean kernel off.  Returns the previous value.
+ * (CUDALM's counterpart is its one kernel per call,
+ * src/kernels/int4_gemv_bf16.cu:221-243.) */
+CUDALM_B200_API int64_t cudalm_b200_set_direct_path_max_bytes(int64_t max_bytes);
 
 /* ---- introspection ---------------------------------------------------------
  * Registers per thread / static+dynamic shared memory of the named kernel

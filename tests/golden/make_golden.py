@@ -2,7 +2,7 @@
 
 Run where the reference tree is mounted (it is not present on GPU boxes):
 
-    python tests/golden/make_golden.py [--ref <reference tree>]
+    python tests/golden/make_golden.py [--ref <reference tree>] [--only model]
 
 What is recorded, and which reference code produced it:
 
@@ -16,6 +16,10 @@ What is recorded, and which reference code produced it:
 * pick.npz       bf16 logit rows with the reference's ``argmax_bf16``
                  (include/cudalm/greedy.h:28-39) result and the keep-set of its
                  top-k filter (include/cudalm/sampling.h:152-166).
+
+* tiny_model_v2.cudalm  a whole two-layer model converted the way the reference's
+                 converter does it (tools/convert_qwen35.py:181-264), written by the
+                 reference's container writer (tools/common/cudalm_v2.py).
 
 All inputs are seeded; the files are a few hundred KB in total.
 """
@@ -251,13 +255,80 @@ def v2_file_case(ref_root, quantize_w4a16):
     return cases
 
 
+def model_v2_file(ref_root, quantize_w4a16):
+    """A whole two-layer model (tests/helpers.py: tiny_model_tensors) converted the way
+    the reference's converter does it (tools/convert_qwen35.py:181-264: its tensor walk,
+    its quantizer, its container writer), for the model-level loader and the
+    safetensors conversion to be checked against."""
+    import torch
+    sys.path.insert(0, os.path.join(ref_root, "tools", "common"))
+    sys.path.insert(0, os.path.join(os.path.dirname(HERE)))
+    import cudalm_v2 as ref_v2
+    from helpers import CHECKPOINT_PREFIX, TINY_MODEL, TINY_MODEL_META, tiny_model_tensors
+
+    conf = ref_v2.Qwen35Config(**TINY_MODEL)
+    assert conf.valid()
+    src = tiny_model_tensors()
+    tensors = []
+
+    def raw(t):
+        return t.contiguous().view(torch.uint8).reshape(-1).numpy().tobytes()
+
+    def plain(name, dtype):
+        t = src[CHECKPOINT_PREFIX + name]
+        tensors.append(ref_v2.V2Tensor(name, dtype, tuple(t.shape), raw(t)))
+
+    def w4(name):
+        t = src[CHECKPOINT_PREFIX + name + ".weight"]
+        packed, scale16, _q, _s32 = quantize_w4a16(t)
+        n, k = t.shape
+        tensors.append(ref_v2.V2Tensor(name + ".weight", ref_v2.DT_INT4_PACKED, (n, k // 2), raw(packed)))
+        tensors.append(ref_v2.V2Tensor(name + ".scale", ref_v2.DT_FP16_SCALE, (n, k // 128), raw(scale16)))
+
+    for i in range(conf.num_hidden_layers):
+        L = f"layers.{i}."
+        plain(L + "input_layernorm.weight", ref_v2.DT_BF16)
+        if conf.is_full_attention(i):
+            for p in ("q_proj", "k_proj", "v_proj", "o_proj"):
+                w4(L + "self_attn." + p)
+            plain(L + "self_attn.q_norm.weight", ref_v2.DT_BF16)
+            plain(L + "self_attn.k_norm.weight", ref_v2.DT_BF16)
+        else:
+            for p in ("in_proj_qkv", "in_proj_z", "in_proj_b", "in_proj_a", "out_proj"):
+                w4(L + "linear_attn." + p)
+            plain(L + "linear_attn.conv1d.weight", ref_v2.DT_BF16)
+            plain(L + "linear_attn.dt_bias", ref_v2.DT_BF16)
+            plain(L + "linear_attn.A_log", ref_v2.DT_FP32)
+            plain(L + "linear_attn.norm.weight", ref_v2.DT_FP32)
+        plain(L + "post_attention_layernorm.weight", ref_v2.DT_BF16)
+        for p in ("gate_proj", "up_proj", "down_proj"):
+            w4(L + "mlp." + p)
+    plain("norm.weight", ref_v2.DT_BF16)
+    plain("embed_tokens.weight", ref_v2.DT_BF16)
+    data = ref_v2.V2File(conf, dict(TINY_MODEL_META), tensors).to_bytes()
+    ref_v2.V2File.from_bytes(data)  # the reference's reader accepts it
+    with open(os.path.join(HERE, "tiny_model_v2.cudalm"), "wb") as f:
+        f.write(data)
+    return len(data)
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("CUDALM_REFERENCE") or
+                    os.path.join(os.path.dirname(ROOT), "reference"),
+                    help="root of the CUDALM source tree (default: $CUDALM_REFERENCE, else a "
+                         "directory 'reference' beside this repository)")
+    ap.add_argument("--only", default="all", choices=["all", "model"],
+                    help="'model': regenerate only tiny_model_v2.cudalm")
     args = ap.parse_args()
+    if not os.path.isdir(os.path.join(args.ref, "tools")):
+        raise SystemExit(f"no CUDALM source tree at {args.ref!r}")
     sys.path.insert(0, os.path.join(args.ref, "tools"))
     from common.w4a16_quant import quantize_w4a16  # the reference's quantizer
 
+    if args.only == "model":
+        print("tiny_model_v2.cudalm", model_v2_file(args.ref, quantize_w4a16), "bytes")
+        return
     orc.build(force=True)
     if not orc.have_ref():
         raise SystemExit("oracle/_ref/libcudalm_ref.so was not built")
@@ -266,7 +337,9 @@ def main():
     np.savez_compressed(os.path.join(HERE, "pick.npz"), **pick_cases())
     np.savez_compressed(os.path.join(HERE, "sample.npz"), **sample_cases())
     np.savez_compressed(os.path.join(HERE, "tiny_v2.npz"), **v2_file_case(args.ref, quantize_w4a16))
-    for f in ("quantize.npz", "gemv.npz", "pick.npz", "sample.npz", "tiny_v2.npz", "tiny_v2.cudalm"):
+    model_v2_file(args.ref, quantize_w4a16)
+    for f in ("quantize.npz", "gemv.npz", "pick.npz", "sample.npz", "tiny_v2.npz", "tiny_v2.cudalm",
+              "tiny_model_v2.cudalm"):
         print(f, os.path.getsize(os.path.join(HERE, f)), "bytes")
 
 

@@ -107,3 +107,64 @@ def check_close(orc, got_bits, want_bits, label="", max_flip_fraction=2e-3):
             f"{label}: {over.sum()} of {over.size} outputs are one ulp off and over the gate"
     assert np.all(err <= 1e-2 + 1e-2 * np.abs(want)), label
     return int((gb != wb).sum())
+
+
+# --- a two-layer model small enough to commit ------------------------------------------
+TINY_MODEL = dict(hidden_size=128, num_hidden_layers=2, intermediate_size=128, vocab_size=256,
+                  n_heads=2, n_kv_heads=1, head_dim=64, lin_num_k_heads=1, lin_num_v_heads=2,
+                  lin_key_head_dim=64, lin_value_head_dim=64, lin_conv_kernel_dim=4,
+                  full_attention_interval=2, group_size=128, max_seq_len=1024, eps=1e-6,
+                  rope_theta=1e7, partial_rotary_factor=0.25, mrope_section=(3, 3, 2))
+TINY_MODEL_META = {"arch": "qwen3.5-text", "source_dtype": "bf16", "generator": "make_golden.py",
+                   "tie_word_embeddings": "true"}
+CHECKPOINT_PREFIX = "model.language_model."
+
+
+def tiny_model_tensors():
+    """The source checkpoint of the two-layer model (layer 0 gated DeltaNet, layer 1 full
+    attention), as {checkpoint tensor name: torch CPU tensor}: bf16 matrices ~N(0, 0.02)
+    and the small fp32 / bf16 vectors, drawn from one seeded CPU generator in a fixed
+    order.  Names and dtypes are those CUDALM's converter reads
+    (tools/convert_qwen35.py:181-236)."""
+    import torch
+    c = TINY_MODEL
+    H, I = c["hidden_size"], c["intermediate_size"]
+    cv = c["lin_num_v_heads"] * c["lin_value_head_dim"]
+    cd = 2 * c["lin_num_k_heads"] * c["lin_key_head_dim"] + cv
+    qo, kvo, oin = c["n_heads"] * c["head_dim"] * 2, c["n_kv_heads"] * c["head_dim"], c["n_heads"] * c["head_dim"]
+    g = torch.Generator().manual_seed(BASE_SEED + 77)
+    out = {}
+
+    def mat(name, n, k):
+        out[CHECKPOINT_PREFIX + name] = (torch.randn(n, k, generator=g) * 0.02).to(torch.bfloat16)
+
+    def vec(name, shape, dtype=torch.bfloat16):
+        out[CHECKPOINT_PREFIX + name] = torch.randn(*shape, generator=g).to(dtype)
+
+    for i in range(c["num_hidden_layers"]):
+        L = f"layers.{i}."
+        vec(L + "input_layernorm.weight", (H,))
+        if (i + 1) % c["full_attention_interval"] == 0:
+            mat(L + "self_attn.q_proj.weight", qo, H)
+            mat(L + "self_attn.k_proj.weight", kvo, H)
+            mat(L + "self_attn.v_proj.weight", kvo, H)
+            mat(L + "self_attn.o_proj.weight", H, oin)
+            vec(L + "self_attn.q_norm.weight", (c["head_dim"],))
+            vec(L + "self_attn.k_norm.weight", (c["head_dim"],))
+        else:
+            mat(L + "linear_attn.in_proj_qkv.weight", cd, H)
+            mat(L + "linear_attn.in_proj_z.weight", cv, H)
+            mat(L + "linear_attn.in_proj_b.weight", c["lin_num_v_heads"], H)
+            mat(L + "linear_attn.in_proj_a.weight", c["lin_num_v_heads"], H)
+            mat(L + "linear_attn.out_proj.weight", H, cv)
+            vec(L + "linear_attn.conv1d.weight", (cd, 1, c["lin_conv_kernel_dim"]))
+            vec(L + "linear_attn.dt_bias", (c["lin_num_v_heads"],))
+            vec(L + "linear_attn.A_log", (c["lin_num_v_heads"],), torch.float32)
+            vec(L + "linear_attn.norm.weight", (c["lin_value_head_dim"],), torch.float32)
+        vec(L + "post_attention_layernorm.weight", (H,))
+        mat(L + "mlp.gate_proj.weight", I, H)
+        mat(L + "mlp.up_proj.weight", I, H)
+        mat(L + "mlp.down_proj.weight", H, I)
+    vec("norm.weight", (H,))
+    mat("embed_tokens.weight", c["vocab_size"], H)
+    return out
