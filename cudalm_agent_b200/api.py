@@ -86,6 +86,7 @@ SIGNATURES = {
     "cudalm_b200_gate_up_silu_bf16": (_ci, [_vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _vp]),
     "cudalm_b200_linear_residual_bf16": (_ci, [_vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _vp]),
     "cudalm_b200_lm_head_workspace_bytes": (ctypes.c_size_t, [_ci, _ci, _ci, _ci, _ci]),
+    "cudalm_b200_lm_head_workspace_init": (_ci, [_vp, ctypes.c_size_t, _vp]),
     "cudalm_b200_lm_head_topk": (_ci, [_vp, _vp, _vp, _ci, _ci, _ci, _ci, _ci, _vp, _vp, _vp,
                                       _vp, _vp, ctypes.c_size_t, _vp]),
     "cudalm_b200_lm_head_static_scratch_bytes": (ctypes.c_size_t, []),
@@ -94,6 +95,7 @@ SIGNATURES = {
     "cudalm_b200_topk_merge": (_ci, [_vp, _vp, _ci, _ci, _ci, _vp, _vp, _vp, _vp]),
     "cudalm_b200_topk_merge_packed": (_ci, [_vp, _ci, _ci, _ci, _ci, _ci, _vp, _vp, _vp, _vp]),
     "cudalm_b200_exchange_bytes": (ctypes.c_size_t, [_ci, _ci]),
+    "cudalm_b200_set_exchange_timeout_ns": (ctypes.c_int64, [ctypes.c_int64]),
     "cudalm_b200_exchange_create": (_ci, [ctypes.c_size_t, ctypes.POINTER(_vp), _vp]),
     "cudalm_b200_exchange_open": (_ci, [_vp, ctypes.POINTER(_vp)]),
     "cudalm_b200_exchange_close": (_ci, [_vp]),
@@ -159,6 +161,24 @@ def _need(t: torch.Tensor, dtype: torch.dtype, name: str) -> None:
         raise ValueError(f"{name} must be {dtype}, got {t.dtype}")
     if not t.is_contiguous():
         raise ValueError(f"{name} must be contiguous")
+    # the library works on the current device (its per-device caches, status word and
+    # scratch): a tensor of another device would be read through the wrong context
+    if t.device.index != torch.cuda.current_device():
+        raise ValueError(f"{name} is on cuda:{t.device.index}, the current device is "
+                         f"cuda:{torch.cuda.current_device()}")
+
+
+def _need_sizes(weight: torch.Tensor, scales: torch.Tensor, x: torch.Tensor, y: torch.Tensor,
+                N: int, K: int, B: int) -> None:
+    """The buffers must hold what the kernel reads and writes."""
+    if K <= 0 or K % GROUP_SIZE != 0 or N < 1 or B < 1:
+        raise ValueError(f"bad shape N={N} K={K} B={B} (K must be a positive multiple of {GROUP_SIZE})")
+    if weight.numel() < N * (K // 2) or scales.numel() < N * (K // GROUP_SIZE):
+        raise ValueError("weight must hold [N, K/2] bytes and scales [N, K/128] values")
+    if x.numel() != B * K:
+        raise ValueError(f"x holds {x.numel()} values, expected B * K = {B * K}")
+    if y.numel() < B * N:
+        raise ValueError(f"y holds {y.numel()} values, needs B * N = {B * N}")
 
 
 def device_status() -> int:
@@ -178,6 +198,12 @@ def set_direct_path_max_bytes(max_bytes: int) -> int:
     """Single calls with at most 8 rows and at most this many weight bytes take
     the lean kernel (0: never); returns the previous value."""
     return int(load_library().cudalm_b200_set_direct_path_max_bytes(int(max_bytes)))
+
+
+def set_exchange_timeout_ns(ns: int) -> int:
+    """Limit of the device-side wait for the other ranks' candidates (default 2 s);
+    returns the previous value."""
+    return int(load_library().cudalm_b200_set_exchange_timeout_ns(int(ns)))
 
 
 def launch_count() -> int:
@@ -219,6 +245,7 @@ def int4_gemv_bf16(weight: torch.Tensor, scales: torch.Tensor, x: torch.Tensor,
     if y is None:
         y = torch.empty(N, dtype=torch.bfloat16, device=x.device)
     _need(y, torch.bfloat16, "y")
+    _need_sizes(weight, scales, x, y, N, K, 1)
     st = load_library().cudalm_b200_int4_gemv_bf16(_ptr(weight), _ptr(scales), _ptr(x), _ptr(y),
                                                    N, K, _stream())
     _check("int4_gemv_bf16", st)
@@ -239,6 +266,7 @@ def batch_int4_gemv_bf16(weight: torch.Tensor, scales: torch.Tensor, x: torch.Te
     if y is None:
         y = torch.empty((B, N), dtype=torch.bfloat16, device=x.device)
     _need(y, torch.bfloat16, "y")
+    _need_sizes(weight, scales, x, y, N, K, B)
     st = load_library().cudalm_b200_batch_int4_gemv_bf16(_ptr(weight), _ptr(scales), _ptr(x),
                                                          _ptr(y), N, K, B, _stream())
     _check("batch_int4_gemv_bf16", st)
@@ -429,8 +457,9 @@ class LmHead:
                        if keep_logits else None)
         nbytes = int(load_library().cudalm_b200_lm_head_workspace_bytes(
             rows.N, rows.K, max_rows, top_k, 0 if keep_logits else 1))
-        # 256-byte aligned by the caching allocator (512-byte granularity)
-        self.workspace = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        # 256-byte aligned by the caching allocator (512-byte granularity); zeroed once:
+        # the pick's counters start at zero and every call leaves them there
+        self.workspace = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
         self.argmax = torch.empty(max_rows, dtype=torch.int32, device=dev)
         # ids and values share one buffer so that a vocabulary-parallel caller can
         # send both with a single all-gather: int32 [R][k] then bf16 [R][k]
@@ -444,6 +473,8 @@ class LmHead:
         M = 1 if x.dim() == 1 else int(x.shape[0])
         if M > self.max_rows:
             raise ValueError(f"M={M} exceeds max_rows={self.max_rows}")
+        if x.numel() != M * self.rows.K:
+            raise ValueError(f"x holds {x.numel()} values, expected M * K = {M * self.rows.K}")
         st = load_library().cudalm_b200_lm_head_topk(
             _ptr(self.rows.weight), _ptr(self.rows.scale), _ptr(x), self.rows.N, self.rows.K, M,
             self.top_k, self.id_offset, _ptr(self.logits), _ptr(self.argmax),

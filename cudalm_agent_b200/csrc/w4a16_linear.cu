@@ -15,8 +15,7 @@ namespace cb200 {
 // tensor-memory path for batched rows (w4a16_tc.cu)
 bool tc_eligible(const cudalm_b200_linear& l);
 int run_tc(const cudalm_b200_linear* ls, int count, cudaStream_t stream);
-int run_tc_with_cta_max(const cudalm_b200_linear& l, float* cta_max, int* grid_out,
-                        cudaStream_t stream, int* clear_words, int clear_count);
+int run_tc_with_pick(const cudalm_b200_linear& l, const PickTail& pick, cudaStream_t stream);
 int run_tc_extra(const cudalm_b200_linear& l, const std::uint8_t* weight2,
                  const std::uint16_t* scales2, const std::uint16_t* residual, cudaStream_t stream);
 struct TcGroup;
@@ -220,8 +219,9 @@ int launch_stream(StreamParams& p, int kmax, int mmax, cudaStream_t stream,
   if (grid > p.total_mt) grid = p.total_mt;
   if (grid < 1) grid = 1;
   if (forced_grid > 0) grid = forced_grid;  // a group's per-CTA ranges were cut for this grid
+  const bool want_max = p.pick.slots != nullptr;
+  if (want_max && grid > kTailMaxCtas) grid = kTailMaxCtas;  // one slot per CTA in the pick's table
   if (grid_out) *grid_out = grid;
-  const bool want_max = p.cta_max != nullptr;
   if (extra) {
     // launches with an MLP epilogue: at most 16 rows, no per-CTA maxima
     if (pl.nt == 1 && pl.nwarps == 12) return launch_instance<1, 12, false, true>(p, pl, grid, stream);
@@ -477,14 +477,16 @@ int run_extra(cudalm_b200_linear l, const LinearExtra& ex, cudaStream_t stream) 
 
 }  // namespace
 
-// Used by the vocabulary projection: one staged launch of a single projection
-// (M rows in one pass) that also records the per-CTA maxima.  Returns
-// ERR_UNSUPPORTED when the projection cannot take the staged path in one pass.
-int run_linear_with_cta_max(const cudalm_b200_linear& l, float* cta_max, int* grid_out,
-                            cudaStream_t stream, int* clear_words, int clear_count) {
+// Used by the vocabulary projection: one staged launch of a single projection (M rows
+// in one pass) whose CTAs also collect the candidates of the token pick and, for a few
+// rows, rank them.  Returns ERR_UNSUPPORTED when the projection cannot take the staged
+// path in one pass.
+int run_linear_with_pick(const cudalm_b200_linear& l, const PickTail& pick, cudaStream_t stream) {
   if (int rc = validate(l)) return rc;
-  if (l.M >= g_tc_min_rows.load(std::memory_order_relaxed) && tc_eligible(l))
-    return run_tc_with_cta_max(l, cta_max, grid_out, stream, clear_words, clear_count);
+  if (l.M >= g_tc_min_rows.load(std::memory_order_relaxed) && tc_eligible(l)) {
+    if (pick.inline_pick) return CUDALM_B200_ERR_UNSUPPORTED;
+    return run_tc_with_pick(l, pick, stream);
+  }
   if (!stream_eligible(l)) return CUDALM_B200_ERR_UNSUPPORTED;
   if (max_rows_per_pass(l.K) < l.M) return CUDALM_B200_ERR_UNSUPPORTED;
   StreamParams p;
@@ -493,10 +495,18 @@ int run_linear_with_cta_max(const cudalm_b200_linear& l, float* cta_max, int* gr
   p.n_desc = 1;
   p.total_mt = mtiles(l.N);
   p.total_cost = p.total_mt * chunks_per_mtile(l.K);
-  p.cta_max = cta_max;
-  p.clear_words = clear_words;
-  p.clear_count = clear_count;
-  return launch_stream(p, l.K, l.M, stream, grid_out);
+  p.pick = pick;
+  return launch_stream(p, l.K, l.M, stream, nullptr);
+}
+
+// True when run_linear_with_pick would take the projection (the same tests, no launch).
+bool linear_with_pick_eligible(const cudalm_b200_linear& l) {
+  if (validate(l) != CUDALM_B200_OK) return false;
+  if (l.M >= g_tc_min_rows.load(std::memory_order_relaxed) && tc_eligible(l)) return true;
+  return stream_eligible(l) && max_rows_per_pass(l.K) >= l.M;
+}
+bool linear_with_pick_on_tensor_path(const cudalm_b200_linear& l) {
+  return l.M >= g_tc_min_rows.load(std::memory_order_relaxed) && tc_eligible(l);
 }
 
 int stream_rows_per_pass(int K) {

@@ -33,6 +33,7 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "lm_head_pick.cuh"
 
 namespace cb200 {
 
@@ -41,7 +42,7 @@ constexpr int kMaxDepth = 4;
 constexpr int kMaxWarps = 16;
 // shared-memory header: "full" mbarriers [kMaxWarps][kMaxDepth], CtaControl, and in
 // its last 512 bytes the "empty" mbarriers [kMaxWarps][kMaxDepth] of the producer form
-constexpr int kHeaderBytes = 2048;
+constexpr int kHeaderBytes = 2304;
 // projections of a CTA's range whose descriptors are kept in shared memory
 constexpr int kDescCache = 8;
 // largest M*K one warp refills on its own (the barrier-free change of projection)
@@ -82,11 +83,9 @@ struct StreamParams {
   int x_bytes;      // one activation buffer
   int x_buffers;    // 1, or 2 for the barrier-free change of projection
   int* status;      // device status word
-  float* cta_max;   // [gridDim.x][M] when the kernel is built with CTA_MAX
-  // CTA_MAX only: words that CTA 0 clears once it is past the wait on the previous
-  // grid (the candidate counters of the token pick that follows), or nullptr
-  int* clear_words;
-  int clear_count;
+  // CTA_MAX only (the vocabulary projection, one projection per launch): the token
+  // pick that the kernel's CTAs finish after their rows (lm_head_pick.cuh)
+  PickTail pick;
   // Optional, for launches with a device table: per CTA {first m-tile, its
   // projection}, gridDim.x + 1 entries, so that a CTA finds its range with two
   // loads instead of a chain of dependent table look-ups.
@@ -151,6 +150,8 @@ struct CtaControl {
   int fill_done;            // every projection before this one has its activations in place
   int fill_parts;           // warps that have converted their share of the refill under way
   int abort;                // a bounded wait ran out somewhere in the CTA
+  // CTA_MAX: per activation row, key + 1 of the largest output this CTA has produced
+  std::uint32_t row_key[kMaxPassRows];
   int issued[kMaxWarps];    // producer form: stages issued so far for each consumer warp
   int cur_desc[kMaxWarps];  // projection each warp is consuming (INT_MAX when done)
   // The CTA's first projections.  Under load a dependent load from global
@@ -608,9 +609,11 @@ __device__ __forceinline__ void consume_chunk(const std::uint8_t* stage, const s
 }
 
 // ---------------------------------------------------------------------------
-// Streaming kernel.  CTA_MAX additionally records, per CTA and activation row,
-// the largest bf16-rounded output the CTA produced (used by the vocabulary
-// projection to bound its top-k search): p.cta_max[blockIdx.x * M + m].
+// Streaming kernel.  CTA_MAX (the vocabulary projection) additionally keeps, per
+// activation row, the largest bf16-rounded output the CTA has produced so far,
+// publishes it for the other CTAs, and finishes with the token pick's tail
+// (lm_head_pick.cuh): candidates from the CTA's own rows, and in the launch's last
+// CTA the ranking.
 // ---------------------------------------------------------------------------
 
 // Shared-memory address of activation buffer b.  The offset goes through an
@@ -819,6 +822,7 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
     mbar_init_fence();
   }
   if (tid < NWARPS) ctl->cur_desc[tid] = d_first;
+  if (CTA_MAX && tid < kMaxPassRows) ctl->row_key[tid] = 0u;
   if (tid < kDescCache) {
     // descriptors are written when a launch is set up, never by a kernel, so
     // they may be read before the wait on the previous grid
@@ -955,6 +959,27 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
   float vmax[NT][2];
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) vmax[nt][0] = vmax[nt][1] = -INFINITY;
+
+  int tiles_done = 0;
+  // CTA_MAX: the warp's maxima (over the eight row-lanes that share a column pair) into
+  // the CTA's per-row keys
+  auto publish_maxima = [&]() {
+    const int M = desc_table(p)->M;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        float v = vmax[nt][c];
+        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
+        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
+        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
+        const int col = nt * 8 + 2 * lane + c;
+        if (lane < 4 && col < M && col < kMaxPassRows)
+          atomicMax(&ctl->row_key[col], order_key(float_to_bf16_bits(v)) + 1u);
+      }
+    }
+    __syncwarp();
+  };
 
   bool dead = false;     // a wait ran out: stop computing, keep attending barriers
   XFill xf{d_first};
@@ -1129,6 +1154,15 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
             }
           }
         }
+        if (CTA_MAX) {
+          // the warp's first two m-tiles and then every fourth one: fold the warp's maxima
+          // into the CTA's and publish them, so that CTAs that finish early find bounds
+          ++tiles_done;
+          if (tiles_done <= 2 || (tiles_done & 3) == 0) {
+            publish_maxima();
+            tail_publish(p.pick, ctl->row_key, lane);
+          }
+        }
       }
     }
   }
@@ -1163,36 +1197,17 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
   }
 
   if (CTA_MAX) {
-    if (blockIdx.x == 0 && p.clear_words != nullptr)
-      for (int i = tid; i < p.clear_count; i += NWARPS * 32) p.clear_words[i] = 0;
-    // reduce over the eight row-lanes that share a column pair, then over warps
-    const int M = desc_table(p)->M;
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        float v = vmax[nt][c];
-        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
-        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
-        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
-        vmax[nt][c] = v;
-      }
-    }
-    consumer_sync();  // the activation region is free again; reuse it as scratch
-    float* red = reinterpret_cast<float*>(xs0);  // [NWARPS][NT*8]
-    if (lane < 4) {
-#pragma unroll
-      for (int nt = 0; nt < NT; ++nt) {
-        red[warp * (NT * 8) + nt * 8 + 2 * lane] = vmax[nt][0];
-        red[warp * (NT * 8) + nt * 8 + 2 * lane + 1] = vmax[nt][1];
-      }
-    }
-    consumer_sync();
-    if (tid < M && tid < NT * 8) {
-      float v = -INFINITY;
-      for (int w = 0; w < NWARPS; ++w) v = fmaxf(v, red[w * (NT * 8) + tid]);
-      p.cta_max[static_cast<std::size_t>(blockIdx.x) * M + tid] = v;
-    }
+    // final maxima of this CTA in its slots, then the pick's tail
+    publish_maxima();
+    consumer_sync();  // every warp has folded its maxima in; rings and activations are free
+    tail_publish(p.pick, ctl->row_key, tid);
+    if (tid < 32) __threadfence();
+    TailSmem& ts = *reinterpret_cast<TailSmem*>(rings);
+    const int LN = desc_table(p)->N;
+    const int row_lo = min(LN, mt_lo * kMTileRows), row_hi = min(LN, mt_hi * kMTileRows);
+    const bool last = tail_collect(p.pick, mt_lo < mt_hi ? row_lo : 0, mt_lo < mt_hi ? row_hi : 0, ts, tid,
+                                   NWARPS * 32, 1);
+    if (last && p.pick.inline_pick && tid < kSelectThreads) tail_pick_rows(p.pick, tid, ts.sel);
   }
 }
 

@@ -37,6 +37,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "lm_head_pick.cuh"
 
 namespace cb200 {
 
@@ -98,14 +99,10 @@ struct TcParams {
   int total_items;
   int total_cost;
   int* status;
-  // Optional (vocabulary projection, one projection per launch): per CTA and
-  // activation row the largest bf16-rounded output the CTA produced,
-  // cta_max[blockIdx.x * M + m].
-  float* cta_max;
-  // with cta_max: words that CTA 0 clears at its end (the candidate counters of the
-  // token pick that follows), or nullptr
-  int* clear_words;
-  int clear_count;
+  // Optional (vocabulary projection, one projection per launch; pick.slots non-null):
+  // the CTAs keep per activation row the largest bf16-rounded output they have
+  // produced, publish it, and finish with the token pick's tail (lm_head_pick.cuh).
+  PickTail pick;
 };
 
 // ---------------------------------------------------------------------------
@@ -635,7 +632,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
         mbar_arrive(&sm->d_free[tile][buf]);
       }
       if (!alive) break;
-      if (p.cta_max != nullptr) {
+      if (p.pick.slots != nullptr) {
         // Maxima over the warp's 32 weight rows for every activation row at once: the
         // outputs are rounded to bf16 two to a word, and a butterfly of packed bf16
         // maxima that halves the words a lane holds at each step leaves every word
@@ -675,6 +672,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
           const int n = 2 * word + copy;
           if (n < LM) atomicMax(&sm->row_max[n], bf16_key(copy ? (kv[0] >> 16) : (kv[0] & 0xFFFFu)));
         }
+        // publish the CTA's maxima so far (key + 1) for CTAs that finish earlier
+        __syncwarp();
+        for (int n = lane; n < LM && n < kMaxPassRows; n += 32)
+          reinterpret_cast<volatile std::uint32_t*>(p.pick.slots)[static_cast<std::size_t>(blockIdx.x) * LM + n] =
+              *reinterpret_cast<volatile std::uint32_t*>(&sm->row_max[n]) + 1u;
       }
       if (direct) {
         // outputs the TMA unit cannot address: plain stores, one row per thread
@@ -807,14 +809,24 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
         ++n_stores;
       }
       asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+      // the stored outputs are re-read with ordinary loads by the pick's tail
+      asm volatile("fence.proxy.async;" ::: "memory");
     }
   }
 
   __syncthreads();
-  if (p.cta_max != nullptr && tid < tbl[0].M)
-    p.cta_max[static_cast<std::size_t>(blockIdx.x) * tbl[0].M + tid] = key_float(sm->row_max[tid]);
-  if (p.cta_max != nullptr && blockIdx.x == 0 && p.clear_words != nullptr)
-    for (int i = tid; i < p.clear_count; i += kTcThreads) p.clear_words[i] = 0;
+  if (p.pick.slots != nullptr) {
+    // final maxima of this CTA in its slots, then the pick's tail on the CTA's own rows
+    const int LM = tbl[0].M, LN = tbl[0].N;
+    if (tid < LM && tid < kMaxPassRows) {
+      p.pick.slots[static_cast<std::size_t>(blockIdx.x) * LM + tid] = sm->row_max[tid] + 1u;
+      __threadfence();
+    }
+    TailSmem& ts = *reinterpret_cast<TailSmem*>(stages);
+    const bool mine = it_lo < it_hi;
+    (void)tail_collect(p.pick, mine ? min(LN, it_lo * kTcItemRows) : 0, mine ? min(LN, it_hi * kTcItemRows) : 0,
+                       ts, tid, kTcThreads, 1);
+  }
   if (*abort_flag && tid == 0) atomicExch(p.status, CUDALM_B200_ERR_TIMEOUT);
   tc_fence_after();
   if (warp == 0) tmem_dealloc(tmem_base, 512);
@@ -903,7 +915,7 @@ int tc_encode(const void* base, int inner, int outer, int box_inner, int box_out
 int tc_ntok(int M) { return M <= 16 ? 16 : (M <= 32 ? 32 : 64); }
 
 template <int NTOK, bool EXTRA = false>
-int tc_launch(const TcParams& p_in, cudaStream_t stream, int* grid_out = nullptr) {
+int tc_launch(const TcParams& p_in, cudaStream_t stream, int* grid_out = nullptr, int max_grid = 0) {
   auto kern = w4a16_tc_kernel<NTOK, EXTRA>;
   constexpr int kFixed = 1024 + kTcHeaderBytes + kTcTiles * tc_out_bytes(NTOK);
   int n_stages = (kMaxSmemBytes - kFixed) / tc_stage_bytes(NTOK);
@@ -928,6 +940,7 @@ int tc_launch(const TcParams& p_in, cudaStream_t stream, int* grid_out = nullptr
   }
   int grid = num_sms();
   if (grid > p.total_items) grid = p.total_items;
+  if (max_grid > 0 && grid > max_grid) grid = max_grid;
   if (grid_out) *grid_out = grid;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(grid));
@@ -996,12 +1009,12 @@ int tc_describe(const cudalm_b200_linear* ls, int count, TcDesc* out, int* items
   return CUDALM_B200_OK;
 }
 
-int tc_run_params(TcParams& p, int ntok, cudaStream_t stream, int* grid_out = nullptr) {
+int tc_run_params(TcParams& p, int ntok, cudaStream_t stream, int* grid_out = nullptr, int max_grid = 0) {
   p.status = device_status_word();
   if (!p.status) return CUDALM_B200_ERR_CUDA;
-  if (ntok == 16) return tc_launch<16>(p, stream, grid_out);
-  if (ntok == 32) return tc_launch<32>(p, stream, grid_out);
-  return tc_launch<64>(p, stream, grid_out);
+  if (ntok == 16) return tc_launch<16>(p, stream, grid_out, max_grid);
+  if (ntok == 32) return tc_launch<32>(p, stream, grid_out, max_grid);
+  return tc_launch<64>(p, stream, grid_out, max_grid);
 }
 
 // One projection with an MLP epilogue: weight2/scales2 non-null -> out = silu(W x) * (W2 x),
@@ -1036,18 +1049,16 @@ int run_tc_extra(const cudalm_b200_linear& l, const std::uint8_t* weight2,
   return tc_launch<64, true>(p, stream);
 }
 
-// One projection that also records the per-CTA maxima (vocabulary projection).
-int run_tc_with_cta_max(const cudalm_b200_linear& l, float* cta_max, int* grid_out,
-                        cudaStream_t stream, int* clear_words, int clear_count) {
+// The vocabulary projection: one projection whose CTAs also collect the candidates of
+// the token pick.  The grid is bounded by the pick's slot table before anything is enqueued.
+int run_tc_with_pick(const cudalm_b200_linear& l, const PickTail& pick, cudaStream_t stream) {
   TcParams p;
   std::memset(&p, 0, sizeof(p));
   int ntok = 0;
   if (int rc = tc_describe(&l, 1, p.inl, &p.total_items, &p.total_cost, &ntok)) return rc;
   p.n_desc = 1;
-  p.cta_max = cta_max;
-  p.clear_words = clear_words;
-  p.clear_count = clear_count;
-  return tc_run_params(p, ntok, stream, grid_out);
+  p.pick = pick;
+  return tc_run_params(p, ntok, stream, nullptr, kTailMaxCtas);
 }
 
 // Up to CUDALM_B200_MAX_INLINE_LINEARS projections in one launch.

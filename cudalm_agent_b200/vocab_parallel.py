@@ -223,14 +223,17 @@ class VocabParallelLmHead:
 
     def forward(self, x: torch.Tensor):
         from .api import topk_merge_packed
-        if self.peer is not None:
+        M = 1 if x.dim() == 1 else int(x.shape[0])
+        # the peer exchange takes up to 32 rows per call; more rows go through the all-gather
+        use_peer = self.peer is not None and M <= 32
+        if use_peer:
             fused = self.peer.forward(self.local, x)
             if fused is not None:
                 return fused
         argmax, idx, val = self.local.forward(x)
         if self.world == 1:
             return argmax, idx, val
-        if self.peer is not None:
+        if use_peer:
             return self.peer.merge(self.local.packed, idx.shape[0])
         dist.all_gather_into_tensor(self._gathered.view(-1), self.local.packed, group=self.group)
         return topk_merge_packed(self._gathered, self.local.max_rows, idx.shape[0], self.local.top_k)

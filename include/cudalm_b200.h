@@ -169,9 +169,17 @@ CUDALM_B200_API int cudalm_b200_linear_residual_bf16(const uint8_t* weight,
  * id; when N < top_k the tail is filled with id -1.  logits_out (may be null) is
  * the full bf16 logits [M, N], as CUDALM's call produces.  top_k <= 64.
  * workspace: device memory, 256-byte aligned, of at least
- * cudalm_b200_lm_head_workspace_bytes(..., need_logits = logits_out == NULL). */
+ * cudalm_b200_lm_head_workspace_bytes(..., need_logits = logits_out == NULL), zeroed
+ * once before its first use (cudalm_b200_lm_head_workspace_init, or a memset of the
+ * whole of it): it holds the counters of the pick, which every call leaves at zero
+ * for the next one.  Calls that share a workspace must not overlap on the GPU; after
+ * a CUDALM_B200_ERR_TIMEOUT in the device status word, zero it again.
+ * Up to 4 activation rows the call is ONE launch: the projection's CTAs collect the
+ * candidates of their own rows and the last of them ranks; more rows add one launch. */
 CUDALM_B200_API size_t cudalm_b200_lm_head_workspace_bytes(int N, int K, int M, int top_k,
                                                            int need_logits);
+CUDALM_B200_API int cudalm_b200_lm_head_workspace_init(void* workspace, size_t workspace_bytes,
+                                                       void* stream);
 CUDALM_B200_API int cudalm_b200_lm_head_topk(
     const uint8_t* weight, const uint16_t* scales, const uint16_t* x, int N, int K,
     int M, int top_k, int id_offset, uint16_t* logits_out, int32_t* argmax_out,
@@ -188,7 +196,8 @@ CUDALM_B200_API int cudalm_b200_lm_head_topk(
  * synchronises the device, a binding with no device allocator.  The scratch is
  * a fixed array of cudalm_b200_lm_head_static_scratch_bytes() (about 640 KB)
  * inside the library's device image; every GPU that loads the library holds it
- * until the process exits.  The call itself allocates nothing.
+ * until the process exits.  The call itself allocates nothing, and the array needs
+ * no initialisation by the caller.
  *
  * Limits: M <= 32 activation rows per call (more: CUDALM_B200_ERR_TOO_LARGE);
  * logits_out is required (CUDALM_B200_ERR_NULL when null).
@@ -226,10 +235,14 @@ CUDALM_B200_API int cudalm_b200_topk_merge_packed(const int32_t* gathered, int n
  * For vocabulary-parallel ranks on one node (up to 8): instead of an all-gather
  * followed by cudalm_b200_topk_merge_packed, ONE kernel per rank stores the rank's
  * packed candidates (the layout above, `local_packed`) into every rank's exchange
- * buffer over NVLink, publishes a per-row flag, waits (2 s limit, then status
- * TIMEOUT in cudalm_b200_device_status and no merge) for every rank's flag and
- * merges what has arrived.  There is no counterpart in CUDALM, whose lm_head is
- * single-GPU (src/runtime/qwen35_model.cpp:290-292).
+ * buffer over NVLink -- one 8-byte word per candidate that carries id, value and the
+ * call's epoch, so no flag and no fence follow the data -- waits for every rank's
+ * words and merges what has arrived.  The wait is limited (2 s by default,
+ * cudalm_b200_set_exchange_timeout_ns); when it runs out the status word reads
+ * CUDALM_B200_ERR_TIMEOUT (cudalm_b200_device_status) and the affected rows' outputs
+ * are ids -1 with values -inf, so a miss shows in the data.  After a TIMEOUT the ranks'
+ * epochs may differ: destroy the buffers and create new ones.  There is no counterpart
+ * in CUDALM, whose lm_head is single-GPU (src/runtime/qwen35_model.cpp:290-292).
  *
  * Every rank creates a buffer of cudalm_b200_exchange_bytes(world, words_per_list)
  * (zeroed; `handle64` receives its 64-byte CUDA IPC handle), sends the handle to
@@ -238,6 +251,9 @@ CUDALM_B200_API int cudalm_b200_topk_merge_packed(const int32_t* gathered, int n
  * all buffers before the first call, make the same sequence of calls (same M), and
  * keep the calls of one rank on one stream.  M <= 32 rows per call. */
 CUDALM_B200_API size_t cudalm_b200_exchange_bytes(int world, int words_per_list);
+/* Limit of the wait for the other ranks' candidates, for calls made from now on
+ * (at least 1000 ns).  Returns the previous value. */
+CUDALM_B200_API int64_t cudalm_b200_set_exchange_timeout_ns(int64_t ns);
 CUDALM_B200_API int cudalm_b200_exchange_create(size_t bytes, void** local, unsigned char* handle64);
 CUDALM_B200_API int cudalm_b200_exchange_open(const unsigned char* handle64, void** peer);
 CUDALM_B200_API int cudalm_b200_exchange_close(void* peer);
@@ -248,11 +264,12 @@ CUDALM_B200_API int cudalm_b200_topk_exchange_merge(const int32_t* local_packed,
                                                     int32_t* argmax_out, int32_t* topk_idx,
                                                     uint16_t* topk_val, void* stream);
 
-/* The whole vocabulary-parallel step of one rank in two launches: the projection of
- * this rank's rows, then the scan whose last CTA per row picks the row's local
- * candidates (into `local_packed`: ids int32 [rows_cap][top_k], then values bf16),
- * sends them to the other ranks and merges theirs as cudalm_b200_topk_exchange_merge
- * does; argmax_out / topk_idx / topk_val receive the merged pick.  Arguments as
+/* The whole vocabulary-parallel step of one rank in one launch (up to 4 rows; two
+ * launches for more): the projection of this rank's rows, whose CTAs collect the rows'
+ * local candidates; the threads that rank them (into `local_packed`: ids int32
+ * [rows_cap][top_k], then values bf16) send them to the other ranks and merge theirs as
+ * cudalm_b200_topk_exchange_merge does; argmax_out / topk_idx / topk_val receive the
+ * merged pick.  Arguments as
  * cudalm_b200_lm_head_topk and cudalm_b200_topk_exchange_merge; M must fit one pass
  * (UNSUPPORTED otherwise: call the two entries one after the other). */
 CUDALM_B200_API int cudalm_b200_lm_head_topk_exchange(

@@ -747,3 +747,102 @@ def test_peer_exchange_merge_with_one_rank(eng, orc):
     finally:
         torch.cuda.synchronize()
         assert lib.cudalm_b200_exchange_destroy(local) == 0
+
+
+def _two_rank_setup(eng, orc, k=50, rows_cap=8):
+    """Two vocabulary shards on this one GPU, each with its own exchange buffer (both
+    local allocations), as ranks 0 and 1 of a world of 2 would hold them."""
+    import ctypes
+    import torch
+    from cudalm_agent_b200 import api
+    lib = api.load_library()
+    N, K = 6000, 1024
+    _, W, S = make_weights(orc, N, K, BASE_SEED + 970)
+    half = 3008  # a multiple of 16
+    heads = [eng.LmHead(eng.W4A16Linear(to_dev(W[:half]), to_dev(S[:half], torch.float16)), top_k=k,
+                        id_offset=0, max_rows=rows_cap),
+             eng.LmHead(eng.W4A16Linear(to_dev(W[half:]), to_dev(S[half:], torch.float16)), top_k=k,
+                        id_offset=half, max_rows=rows_cap)]
+    words = heads[0].packed.numel()
+    nbytes = lib.cudalm_b200_exchange_bytes(2, words)
+    locals_ = []
+    for _ in range(2):
+        local, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+        assert lib.cudalm_b200_exchange_create(nbytes, ctypes.byref(local), handle) == 0
+        locals_.append(local)
+    bufs = (ctypes.c_void_p * 2)(locals_[0].value, locals_[1].value)
+    full = eng.LmHead(eng.W4A16Linear(to_dev(W), to_dev(S, torch.float16)), top_k=k, max_rows=rows_cap)
+    return lib, api, heads, full, bufs, locals_, words, K
+
+
+def _rank_call(lib, api, head, x, bufs, rank, words, rows_cap, k):
+    import torch
+    M = x.shape[0]
+    out = (torch.full((M,), -7, dtype=torch.int32, device="cuda"),
+           torch.full((M, k), -7, dtype=torch.int32, device="cuda"),
+           torch.zeros((M, k), dtype=torch.bfloat16, device="cuda"))
+    st = lib.cudalm_b200_lm_head_topk_exchange(
+        api._ptr(head.rows.weight), api._ptr(head.rows.scale), api._ptr(x), head.rows.N, head.rows.K, M, k,
+        head.id_offset, None, api._ptr(head.packed), rows_cap, api._ptr(head.workspace),
+        head.workspace.numel(), bufs, rank, 2, words, api._ptr(out[0]), api._ptr(out[1]), api._ptr(out[2]),
+        api._stream())
+    assert st == 0
+    torch.cuda.synchronize()
+    return out
+
+
+@pytest.mark.parametrize("M", [1, 3, 8])
+def test_exchange_wait_runs_out_and_shows_in_status_and_data(eng, orc, M):
+    """A rank whose peer never sends: the bounded wait gives up after the (shortened)
+    limit, the kernel returns, the status word reads TIMEOUT and the outputs are ids -1
+    with values -inf.  Nothing faults and the context stays usable."""
+    import torch
+    k, rows_cap = 50, 8
+    lib, api, heads, full, bufs, locals_, words, K = _two_rank_setup(eng, orc, k, rows_cap)
+    prev = eng.set_exchange_timeout_ns(3_000_000)  # 3 ms
+    try:
+        x = to_dev(make_x(orc, (M, K), BASE_SEED + 971, "rmsnorm"), torch.bfloat16)
+        argmax, idx, val = _rank_call(lib, api, heads[0], x, bufs, 0, words, rows_cap, k)
+        assert eng.device_status() == api.ERR_TIMEOUT
+        assert eng.device_status() == 0  # reading it cleared it
+        assert torch.all(argmax == -1) and torch.all(idx == -1)
+        assert np.all(from_dev(val) == 0xFF80)
+        # the rank's own pick was made and sent before the wait: it is in its packed buffer
+        want = full.forward(x)  # (a plain call still works after the timeout)
+        torch.cuda.synchronize()
+        assert eng.device_status() == 0
+    finally:
+        eng.set_exchange_timeout_ns(prev)
+        torch.cuda.synchronize()
+        for loc in locals_:
+            assert lib.cudalm_b200_exchange_destroy(loc) == 0
+
+
+@pytest.mark.parametrize("M", [1, 4, 8])
+def test_two_rank_exchange_one_after_the_other(eng, orc, M):
+    """The two-rank protocol on one GPU without two kernels waiting on one another:
+    rank 1 runs first with a short limit (its words reach both buffers, its own wait
+    for rank 0 runs out), then rank 0 runs and finds rank 1's words already there, so
+    its merge must equal the pick over the whole vocabulary.  Twice, so that both
+    parities of the double buffer and the per-row epochs are exercised."""
+    import torch
+    k, rows_cap = 50, 8
+    lib, api, heads, full, bufs, locals_, words, K = _two_rank_setup(eng, orc, k, rows_cap)
+    prev = eng.set_exchange_timeout_ns(2_000_000)
+    try:
+        for trial in range(3):
+            x = to_dev(make_x(orc, (M, K), BASE_SEED + 980 + trial, "rmsnorm"), torch.bfloat16)
+            _rank_call(lib, api, heads[1], x, bufs, 1, words, rows_cap, k)
+            assert eng.device_status() == api.ERR_TIMEOUT  # rank 1 waited for rank 0 in vain
+            eng.set_exchange_timeout_ns(2_000_000_000)
+            argmax, idx, val = _rank_call(lib, api, heads[0], x, bufs, 0, words, rows_cap, k)
+            eng.set_exchange_timeout_ns(2_000_000)
+            assert eng.device_status() == 0
+            want = full.forward(x)
+            torch.cuda.synchronize()
+            assert torch.equal(argmax, want[0]) and torch.equal(idx, want[1]) and torch.equal(val, want[2])
+    finally:
+        eng.set_exchange_timeout_ns(prev)
+        torch.cuda.synchronize()
+        for loc in locals_:
+            assert lib.cudalm_b200_exchange_destroy(loc) == 0

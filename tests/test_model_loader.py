@@ -191,7 +191,7 @@ def test_safetensors_conversion_reproduces_the_reference_converters_file(v2, tmp
     out = tmp_path / "converted.cudalm"
     recs = v2.convert_safetensors(str(st), str(out), v2.ModelConfig(**TINY_MODEL), dict(TINY_MODEL_META),
                                   full_model=True, prefix=CHECKPOINT_PREFIX)
-    assert len(recs) == 47
+    assert len(recs) == 42
     with open(GOLD, "rb") as f:
         assert out.read_bytes() == f.read()
     with v2.V2Reader(str(out)) as r:

@@ -38,7 +38,24 @@ def test_static_scratch_matches_workspace_entry_twice():
     idx = torch.empty((M, k), dtype=torch.int32, device="cuda")
     val = torch.empty((M, k), dtype=torch.bfloat16, device="cuda")
 
-    mem_before = torch.cuda.memory_allocated()
+    # one warm-up call: the first call on a device looks up the array's address (and loads
+    # the kernels), which is allowed to cost memory; the calls after it are not
+    x0 = to_dev(make_x(orc, (M, K), 9, "rmsnorm"), torch.bfloat16)
+    eng.lm_head_topk_static(lin, x0, logits, argmax, idx, val, id_offset=7)
+    big = torch.empty((32, N), dtype=torch.bfloat16, device="cuda")  # logits of the 32-row call below
+    x32 = to_dev(make_x(orc, (32, K), 10, "rmsnorm"), torch.bfloat16)
+    i32 = torch.empty((32, k), dtype=torch.int32, device="cuda")
+    v32 = torch.empty((32, k), dtype=torch.bfloat16, device="cuda")
+    a32 = torch.empty(32, dtype=torch.int32, device="cuda")
+    eng.lm_head_topk_static(lin, x32, big, a32, i32, v32, id_offset=7)  # the tensor-memory kernel's first use
+    torch.cuda.synchronize()
+    # free device memory as the driver sees it: a cudaMalloc inside the library would show
+    # here, which torch's own allocator statistics cannot see
+    free_before = torch.cuda.mem_get_info()[0]
+    eng.lm_head_topk_static(lin, x0, logits, argmax, idx, val, id_offset=7)
+    eng.lm_head_topk_static(lin, x32, big, a32, i32, v32, id_offset=7)
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] >= free_before, "the allocation-free entry allocated device memory"
     for call, (seed, rows) in enumerate(((1, M), (2, 3))):
         x = to_dev(make_x(orc, (rows, K), seed, "rmsnorm"), torch.bfloat16)
         want = [from_dev(t).copy() for t in ref_head.forward(x)]
@@ -56,8 +73,6 @@ def test_static_scratch_matches_workspace_entry_twice():
             wi, wv = orc.topk_bf16(want_logits[m], k)
             assert np.array_equal(from_dev(idx)[m] - 7, wi)
     assert eng.device_status() == 0
-    del x
-    assert torch.cuda.memory_allocated() <= mem_before + 64 * 1024  # only this test's small x
 
 
 def test_static_entry_rejects_what_it_cannot_hold():
