@@ -47,9 +47,9 @@ VOCAB, HIDDEN, TOP_K = 248320, 1024, 50
 SEED = 20250922
 METRIC = "w4a16_gemv_hbm_gbps_m1_projection_set"
 UNIT = "GB/s"
-# dram__bytes_read.sum + dram__bytes_write.sum of one grouped launch, from the
-# ncu capture summarised in profiles/ (None until a capture exists)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 242_465_024  # profiles/w4a16_stream_kernel_m1_projection_set.md
+# dram__bytes_read.sum + dram__bytes_write.sum of one grouped launch, from an ncu
+# capture of this command with --only set (None until a capture exists)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 242_465_024
 
 
 def set_bytes(M: int = 1) -> int:

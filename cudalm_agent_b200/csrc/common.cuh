@@ -93,18 +93,6 @@ __device__ __forceinline__ bool mbar_try_wait(std::uint64_t* bar,
       : "memory");
   return ok != 0;
 }
-// Bounded wait: gives up after `limit` polls (each poll itself blocks for a
-// hardware-defined short time) and returns false; the caller then records a
-// timeout instead of spinning forever.
-__device__ __forceinline__ bool mbar_wait_bounded(std::uint64_t* bar,
-                                                  std::uint32_t parity,
-                                                  std::uint32_t limit) {
-  for (std::uint32_t i = 0; i < limit; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-  }
-  return false;
-}
-
 // ---- bulk async copy global -> shared (TMA engine, untiled form) -----------
 // dst and src 16-byte aligned, bytes a multiple of 16.  Completion is
 // signalled on `bar` as `bytes` of transaction count.
@@ -114,17 +102,6 @@ __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src,
       "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes "
       "[%0], [%1], %2, [%3];" ::"r"(smem_u32(smem_dst)),
       "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
-      : "memory");
-}
-// Same, with an L2 eviction-priority hint (weights are streamed once).
-__device__ __forceinline__ void bulk_g2s_hint(void* smem_dst, const void* gmem_src,
-                                              std::uint32_t bytes,
-                                              std::uint64_t* bar,
-                                              std::uint64_t policy) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes"
-      ".L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(smem_u32(smem_dst)),
-      "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
       : "memory");
 }
 __device__ __forceinline__ std::uint64_t policy_evict_first() {
@@ -148,13 +125,10 @@ __device__ __forceinline__ std::uint16_t lds16(const std::uint8_t* p) {
 }
 
 // ---- int4 -> bf16 dequantisation --------------------------------------------
-// For a 32-bit word holding eight 4-bit two's-complement values n0..n7 (n_i at
-// bits 4i), produces four bf16x2 registers: out[i] = { q(n_i), q(n_{i+4}) }
-// (low half, high half), exact integers in [-8, 7].
-//
-// (n ^ 8) is q + 8 in [0, 15]; OR-ing it under the bf16 pattern 0x4300 (128.0,
-// whose ulp is 1) gives the bf16 number 136 + q; subtracting 136.0 (0x4308)
-// is exact.  One LOP3 computes (w & 0x000F000F) ^ 0x43084308 for two nibbles.
+// Building blocks: for a 4-bit two's-complement value n, (n ^ 8) is q + 8 in
+// [0, 15]; OR-ing it under the bf16 pattern 0x4300 (128.0, whose ulp is 1) gives
+// the bf16 number 136 + q; subtracting 136.0 (0x4308) is exact.  One LOP3 computes
+// (w & 0x000F000F) ^ 0x43084308 for two nibbles of a word.
 __device__ __forceinline__ std::uint32_t lop3_and_xor(std::uint32_t a,
                                                       std::uint32_t b,
                                                       std::uint32_t c) {
@@ -167,16 +141,6 @@ __device__ __forceinline__ std::uint32_t sub_bf16x2(std::uint32_t a, std::uint32
   asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
   return d;
 }
-__device__ __forceinline__ void dequant_word_bf16x2(std::uint32_t w,
-                                                    std::uint32_t (&out)[4]) {
-  constexpr std::uint32_t kMask = 0x000F000Fu;
-  constexpr std::uint32_t kMagic = 0x43084308u;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    out[i] = sub_bf16x2(lop3_and_xor(w >> (4 * i), kMask, kMagic), kMagic);
-  }
-}
-
 // ---- legacy-path tensor-core MMA (m16n8k16, bf16 x bf16 -> fp32) -------------
 __device__ __forceinline__ void mma_m16n8k16_bf16(float (&c)[4], std::uint32_t a0,
                                                   std::uint32_t a1, std::uint32_t a2,

@@ -4,12 +4,11 @@
 // vocabulary-parallel ranks) is in lm_head_pick.cuh; this file holds the host entry
 // points and the stand-alone kernels.
 //
-// One call is one launch for up to kInlinePickRows activation rows (the projection's
-// CTAs collect the candidates of their own rows and the launch's last CTA ranks them
-// and, when the vocabulary is split over ranks, exchanges them), two launches for more
-// rows (the ranking then runs with one CTA per row).  A projection the staged kernels
-// do not take (a weight base off 16 bytes, K above the staged limit) goes through the
-// general kernels: projection, then a scan of the logits whose last CTA per row ranks.
+// One call is two launches: the projection, whose CTAs leave their largest outputs in a
+// table, and the scan of the logits with several CTAs per activation row, whose last CTA
+// per row ranks the candidates and, when the vocabulary is split over ranks, exchanges
+// them.  A projection the staged kernels do not take (a weight base off 16 bytes, K above
+// the staged limit) goes through the general kernels and the same scan without a table.
 #include <atomic>
 #include <cstring>
 
@@ -17,7 +16,8 @@
 
 namespace cb200 {
 
-int run_linear_with_pick(const cudalm_b200_linear& l, const PickTail& pick, cudaStream_t stream);
+int run_linear_with_pick(const cudalm_b200_linear& l, const PickTail& pick, cudaStream_t stream,
+                         int* grid_out);
 bool linear_with_pick_eligible(const cudalm_b200_linear& l);
 bool linear_with_pick_on_tensor_path(const cudalm_b200_linear& l);
 int stream_rows_per_pass(int K);
@@ -25,6 +25,7 @@ int run_linear_any(const cudalm_b200_linear& l, cudaStream_t stream);
 
 // limit of the wait for the other ranks' candidates (cudalm_b200_set_exchange_timeout_ns)
 std::atomic<long long> g_exchange_wait_ns{2000000000ll};
+
 
 namespace {
 
@@ -53,33 +54,27 @@ size_t workspace_layout(int N, int rows, bool need_logits, unsigned char* base, 
 }
 
 // ---------------------------------------------------------------------------
-// The scan of one CTA of grid (slices, rows): the row's bound from the per-CTA
-// maxima (smax: kMaxCtas floats of shared memory), then the CTA's slice of the
-// row's logits; values at or above the bound become candidates.
+// The scan of one CTA of grid (slices, rows): the row's bound from the table of per-CTA
+// maxima the projection left (`slots`: kSlotReplicas copies of [rows][ncta] keys + 1;
+// ncta == 0: no table, everything is a candidate), then the CTA's slice of the row's
+// logits; values at or above the bound become candidates.
 // ---------------------------------------------------------------------------
 __device__ void scan_slice(const std::uint16_t* __restrict__ logits, int N, int rows,
-                           const float* __restrict__ cta_max, int ncta, int k, int id_offset,
-                           int* counts, std::uint64_t* cand, float* smax) {
-  __shared__ float bound;
+                           const std::uint32_t* __restrict__ slots, int ncta, int k, int id_offset,
+                           int* counts, std::uint64_t* cand) {
+  __shared__ std::uint32_t bound;
   const int m = blockIdx.y;
   const int tid = threadIdx.x;
-  for (int i = tid; i < ncta; i += blockDim.x) smax[i] = cta_max[static_cast<size_t>(i) * rows + m];
-  if (tid == 0) bound = -INFINITY;
-  __syncthreads();
-  if (ncta >= k) {
-    // the entry with exactly k-1 entries ahead of it (value desc, index asc)
-    for (int i = tid; i < ncta; i += blockDim.x) {
-      const float v = smax[i];
-      int ahead = 0;
-      for (int j = 0; j < ncta; ++j) {
-        const float u = smax[j];
-        ahead += (u > v) || (u == v && j < i);
-      }
-      if (ahead == k - 1) bound = v;
+  if (tid < 32) {
+    std::uint32_t T = 0;
+    if (ncta > 0) {
+      const std::uint32_t* copy = slots + static_cast<size_t>(blockIdx.x % kSlotReplicas) * ncta * rows;
+      T = row_bound(copy + static_cast<size_t>(m) * ncta, ncta, k, tid);
     }
+    if (tid == 0) bound = T == 0u ? 0u : T - 1u;  // a slot holds key + 1
   }
   __syncthreads();
-  const float b = bound;
+  const std::uint32_t b = bound;
   const std::uint16_t* row = logits + static_cast<size_t>(m) * N;
   // slices are whole 16-byte vectors of the row, so that a row on a 16-byte
   // boundary is read eight values at a time, several loads in flight per thread
@@ -90,7 +85,7 @@ __device__ void scan_slice(const std::uint16_t* __restrict__ logits, int N, int 
   if (hi > N) hi = N;
   if (lo >= hi) return;  // (uniform over the CTA)
   auto offer = [&](std::uint16_t bits, long long i) {
-    if (bf16_bits_to_float(bits) >= b) {
+    if (order_key(bits) >= b) {
       const int pos = atomicAdd(&counts[m], 1);
       if (pos < kCandCap)
         cand[static_cast<size_t>(m) * kCandCap + pos] =
@@ -158,21 +153,21 @@ topk_exchange_merge_kernel(const ExchangeArgs e) {
   exchange_recv_row(e, blockIdx.x, threadIdx.x, sm);
 }
 
-// scan + pick of the general path: grid (slices, rows).  Each CTA scans its slice of the
-// row's logits for candidates (every logit is one when there are no per-CTA maxima); the
-// CTA that finishes a row's scan last (a ticket per row) picks the row's tokens.
+// scan + pick: grid (slices, rows).  Each CTA scans its slice of the row's logits for
+// candidates; the CTA that finishes a row's scan last (a ticket per row) picks the row's
+// tokens, exchanges them when the vocabulary is split, and leaves the row's counter,
+// ticket and slots cleared for the next call.
 __global__ void __launch_bounds__(kSelectThreads)
-lm_head_scan_pick_kernel(const std::uint16_t* __restrict__ logits, int N, int rows,
-                         const float* __restrict__ cta_max, int ncta, int k, int id_offset,
-                         int* counts, int* tickets, std::uint64_t* cand, const SelectArgs a,
-                         const ExchangeArgs e) {
+lm_head_scan_pick_kernel(const std::uint16_t* __restrict__ logits, int N, int rows, std::uint32_t* slots,
+                         int ncta, int k, int id_offset, int* counts, int* tickets, std::uint64_t* cand,
+                         const SelectArgs a, const ExchangeArgs e) {
   __shared__ SelectSmem sm;
   __shared__ int s_last;
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
   const int m = blockIdx.y;
   const int tid = threadIdx.x;
-  scan_slice(logits, N, rows, cta_max, ncta, k, id_offset, counts, cand, reinterpret_cast<float*>(sm.buf));
+  scan_slice(logits, N, rows, slots, ncta, k, id_offset, counts, cand);
   __syncthreads();
   if (tid == 0) {
     __threadfence();
@@ -182,6 +177,11 @@ lm_head_scan_pick_kernel(const std::uint16_t* __restrict__ logits, int N, int ro
   __syncthreads();
   if (!s_last) return;
   if (tid == 0) tickets[m] = 0;
+  // every CTA of the row is past the table: clear the row's slots in every copy
+  for (int i = tid; i < kSlotReplicas * ncta; i += kSelectThreads) {
+    const int r = i / ncta, c = i - r * ncta;
+    slots[(static_cast<size_t>(r) * rows + m) * ncta + c] = 0u;
+  }
   select_row(a, m, tid, sm);
   if (e.world >= 1) {
     pick_sync();
@@ -299,29 +299,27 @@ static int lm_head_topk_impl(const uint8_t* weight, const uint16_t* scales, cons
     a.topk_val = topk_val + static_cast<size_t>(m0) * top_k;
 
     if (linear_with_pick_eligible(l)) {
+      // the projection leaves the table of per-CTA maxima; many CTAs per row then scan the
+      // logits, and the last one of a row ranks
       PickTail t;
-      std::memset(&t, 0, sizeof(t));
       t.slots = reinterpret_cast<std::uint32_t*>(ws.cta_max);
-      t.counts = ws.counts;
-      t.ticket = reinterpret_cast<unsigned int*>(ws.counts + kMaxPassRows);
-      t.cand = ws.cand;
-      t.logits = logits;
-      t.N = N;
       t.M = rows;
-      t.k = top_k;
-      t.id_offset = id_offset;
-      t.inline_pick = (rows <= kInlinePickRows && !linear_with_pick_on_tensor_path(l)) ? 1 : 0;
-      t.sel = a;
-      t.ex = e;
-      if (int rc = run_linear_with_pick(l, t, st)) return rc;
-      if (!t.inline_pick)
-        if (int rc = launch_after(lm_head_select_kernel, dim3(rows), dim3(kSelectThreads), st, a, e)) return rc;
+      int grid = 0;
+      if (int rc = run_linear_with_pick(l, t, st, &grid)) return rc;
+      int slices = (N + 4095) / 4096;
+      const int cap = (2 * num_sms() + rows - 1) / rows;
+      if (slices > cap) slices = cap;
+      if (slices < 1) slices = 1;
+      if (int rc = launch_after(lm_head_scan_pick_kernel, dim3(slices, rows), dim3(kSelectThreads), st,
+                                static_cast<const std::uint16_t*>(logits), N, rows, t.slots, grid, top_k,
+                                id_offset, ws.counts, ws.counts + kMaxPassRows, ws.cand, a, e))
+        return rc;
       continue;
     }
 
     // general path: no per-CTA maxima, so every logit is a candidate and a row longer
     // than the candidate list takes the exact search
-    zero_counts_kernel<<<1, 64, 0, st>>>(ws.counts, 2 * kMaxPassRows);
+    zero_counts_kernel<<<1, 64, 0, st>>>(ws.counts, kMaxPassRows);
     if (int rc = check_launch()) return rc;
     if (int rc = run_linear_any(l, st)) return rc;
     int slices = (N + 4095) / 4096;
@@ -330,7 +328,7 @@ static int lm_head_topk_impl(const uint8_t* weight, const uint16_t* scales, cons
     if (slices < 1) slices = 1;
     if (int rc = launch_after(lm_head_scan_pick_kernel, dim3(slices, rows), dim3(kSelectThreads), st,
                               static_cast<const std::uint16_t*>(logits), N, rows,
-                              static_cast<const float*>(ws.cta_max), 0, top_k, id_offset, ws.counts,
+                              reinterpret_cast<std::uint32_t*>(ws.cta_max), 0, top_k, id_offset, ws.counts,
                               ws.counts + kMaxPassRows, ws.cand, a, e))
       return rc;
   }

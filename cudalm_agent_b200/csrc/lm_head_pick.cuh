@@ -13,21 +13,26 @@
 // logit's original bits, so that one unsigned compare implements the ordering
 // rule and the value can be reported unchanged.
 //
-// How a call finds its candidates without a second pass over the vocabulary:
-//   * while a CTA of the projection streams its rows it keeps, per activation row,
-//     the largest logit it has produced so far and publishes it (as key + 1; 0 means
-//     "nothing yet") in a table of one slot per CTA;
-//   * a CTA that has finished its rows reads the table.  The k-th largest slot is a
-//     lower bound on the k-th largest logit of the whole vocabulary, because every
-//     slot is at most the largest logit of a different set of rows.  The CTA re-reads
-//     its own logits (a few KB, still in L2) and appends those at or above the bound
-//     to the row's candidate list (typically 50-150 entries out of 248,320);
-//   * the CTA that takes the launch's last ticket ranks the candidates of every row
-//     (up to kInlinePickRows rows; more rows go to a follow-up launch with one CTA
-//     per row), exchanges them with the other ranks when the vocabulary is split,
-//     and leaves counters, tickets and slots cleared for the next call.
+// How a call finds its candidates:
+//   * every CTA of the projection keeps, per activation row, the largest logit it has
+//     produced and leaves it (as key + 1; 0 means "nothing") in a table of one slot per
+//     CTA at its end;
+//   * the follow-up launch, several CTAs per activation row, takes the k-th largest slot
+//     of the row as a bound: it is a lower bound on the k-th largest logit of the whole
+//     vocabulary, because every slot is the largest logit of a different set of rows.
+//     Each CTA scans its slice of the row's logits (still in L2) and appends those at or
+//     above the bound to the row's candidate list (typically 50-150 entries out of
+//     248,320); the CTA that finishes a row's scan last ranks the candidates, exchanges
+//     them with the other ranks when the vocabulary is split, and leaves the row's
+//     counter, ticket and slots cleared for the next call.
 // A row whose candidate list overflows (e.g. all logits equal) is redone by an exact
 // search over the full row.
+//
+// (Finishing the pick inside the projection kernel -- candidates from each CTA's own
+// rows, ranked by one CTA of the same launch -- was built and measured: 39-40 us per call
+// at M = 1 against 38-39 us with the follow-up launch, because every step of that tail is
+// a dependent round trip to L2 of about a microsecond on the critical path of the last
+// CTA, while the follow-up launch spreads the same steps over many CTAs.)
 #pragma once
 
 #include "common.cuh"
@@ -37,16 +42,23 @@ namespace cb200 {
 constexpr int kMaxTopK = 64;
 constexpr int kCandCap = 2048;     // candidate slots per row
 constexpr int kMaxPassRows = 32;   // activation rows per pass
-constexpr int kMaxCtas = 1024;     // per-CTA maxima slots (unstaged path)
+constexpr int kMaxCtas = 2048;     // words per activation row in the table of per-CTA maxima
 constexpr int kTailMaxCtas = 256;  // largest grid whose CTAs pick in the projection kernel
+// The table of maxima is kept in several copies, each on lines of its own: every CTA
+// reads the whole table at about the same time, and requests for one line of L2 are
+// served one after the other (about 45 ns each), so one copy would cost every call
+// 148 x 45 ns.  A CTA writes all copies and reads copy blockIdx % kSlotReplicas.  Inside
+// a copy the slots of one activation row are contiguous, so that the warp that works out
+// a row's bound touches a handful of lines.
+constexpr int kSlotReplicas = kMaxCtas / kTailMaxCtas;
 constexpr int kSelectThreads = 256;
-constexpr int kInlinePickRows = 4;  // rows the projection's last CTA ranks itself
 constexpr int kMaxPeers = 8;
 
 struct SelectArgs {
-  // candidate source A: composites collected during or after the projection
+  // candidate source A: composites collected by the scan, cand[m][0 .. counts[m]) (a
+  // count above kCandCap: overflow); the count is cleared once read
   const std::uint64_t* cand;
-  int* counts;  // read, then cleared for the next call
+  int* counts;
   // candidate source B: lists[l][m][k] of ids and values (ids < 0 are padding)
   const std::int32_t* list_idx;
   const std::uint16_t* list_val;
@@ -83,17 +95,10 @@ struct ExchangeArgs {
   int* status;
 };
 
-// What a projection kernel needs to finish the pick (see the head of this file).
+// What a projection kernel needs to leave its maxima for the pick.
 struct PickTail {
-  std::uint32_t* slots;   // [grid][M]: key + 1 of each CTA's largest logit per row so far
-  int* counts;            // [kMaxPassRows] candidates per row
-  unsigned int* ticket;   // CTAs that have finished their scan
-  std::uint64_t* cand;    // [M][kCandCap]
-  const std::uint16_t* logits;  // [M][N], as the projection writes them
-  int N, M, k, id_offset;
-  int inline_pick;        // the last CTA ranks the rows itself (M <= kInlinePickRows)
-  SelectArgs sel;
-  ExchangeArgs ex;        // ex.world == 0: no exchange
+  std::uint32_t* slots;   // [kSlotReplicas][M][grid]: key + 1 of each CTA's largest logit per row
+  int M;
 };
 
 #ifdef __CUDACC__
@@ -119,6 +124,12 @@ __device__ __forceinline__ std::uint16_t composite_bits(std::uint64_t c) {
 // a projection CTA, or a whole CTA of the stand-alone kernels).
 __device__ __forceinline__ void pick_sync() {
   asm volatile("bar.sync 2, %0;" ::"n"(kSelectThreads) : "memory");
+}
+
+__device__ __forceinline__ long long global_ns() {
+  long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
 }
 
 struct SelectSmem {
@@ -202,7 +213,7 @@ __device__ inline void select_row(const SelectArgs& a, int m, int tid, SelectSme
   int n = 0;
   bool overflow = false;
   if (a.cand) {
-    // written by other CTAs of this or the previous launch: read from L2
+    // written by other CTAs of this launch: read from L2
     n = __ldcg(a.counts + m);
     overflow = n > kCandCap;
     if (!overflow)
@@ -284,11 +295,6 @@ __device__ __forceinline__ unsigned long long ld_word_sys(const unsigned long lo
   asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ long long global_ns() {
-  long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
 __device__ __forceinline__ std::uint32_t* exchange_epochs(const ExchangeArgs& e) {
   return reinterpret_cast<std::uint32_t*>(e.bufs[e.rank] + 2ull * e.world * e.slot_words);
 }
@@ -363,63 +369,27 @@ __device__ inline void exchange_recv_row(const ExchangeArgs& e, int m, int tid, 
   rank_and_write(a, m, n, tid, sm);
 }
 
-// ---- the tail of a projection kernel --------------------------------------------------
-// Scratch the tail needs in shared memory (the projection's stage memory is free by then).
-struct TailSmem {
-  std::uint32_t bound[kMaxPassRows];  // per activation row: smallest key that can still be in the top-k
-  int last;
-  SelectSmem sel;
-};
-
-// Publishes this CTA's current maxima (shared-memory keys + 1) in its slots.
+// ---- the table of per-CTA maxima ---------------------------------------------------------
+// Publishes a CTA's maxima (shared-memory keys + 1) in its slots of every copy of the
+// table; called by a whole warp.
 __device__ __forceinline__ void tail_publish(const PickTail& t, const std::uint32_t* row_key, int lane) {
-  if (lane < t.M)
-    reinterpret_cast<volatile std::uint32_t*>(t.slots)[static_cast<size_t>(blockIdx.x) * t.M + lane] =
-        *reinterpret_cast<const volatile std::uint32_t*>(row_key + lane);
-}
-
-// Candidates of rows [row_lo, row_hi) of activation row m: logits whose key is at least `bound`.
-__device__ inline void tail_scan_rows(const PickTail& t, int m, int row_lo, int row_hi,
-                                      std::uint32_t bound, int tid, int nthreads) {
-  const std::uint16_t* row = t.logits + static_cast<size_t>(m) * t.N;
-  auto offer = [&](std::uint16_t bits, int i) {
-    if (order_key(bits) >= bound) {
-      const int pos = atomicAdd(&t.counts[m], 1);
-      if (pos < kCandCap)
-        t.cand[static_cast<size_t>(m) * kCandCap + pos] =
-            make_composite(bits, static_cast<std::uint32_t>(t.id_offset) + static_cast<std::uint32_t>(i));
-    }
-  };
-  // head up to a 16-byte boundary, whole 16-byte vectors, tail
-  const std::uintptr_t addr = reinterpret_cast<std::uintptr_t>(row + row_lo);
-  int head = static_cast<int>(((16u - (addr & 15u)) & 15u) >> 1);
-  if (head > row_hi - row_lo) head = row_hi - row_lo;
-  for (int i = row_lo + tid; i < row_lo + head; i += nthreads) offer(__ldcg(row + i), i);
-  const int v_lo = row_lo + head;
-  const int nv = (row_hi - v_lo) >> 3;
-  const uint4* vrow = reinterpret_cast<const uint4*>(row + v_lo);
-  for (int v = tid; v < nv; v += nthreads) {
-    const uint4 q = __ldcg(vrow + v);
-    const std::uint32_t w[4] = {q.x, q.y, q.z, q.w};
-    const int i0 = v_lo + (v << 3);
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      offer(static_cast<std::uint16_t>(w[e] & 0xFFFFu), i0 + 2 * e);
-      offer(static_cast<std::uint16_t>(w[e] >> 16), i0 + 2 * e + 1);
-    }
+  const int grid = static_cast<int>(gridDim.x);
+  for (int i = lane; i < kSlotReplicas * t.M; i += 32) {
+    const int r = i / t.M, m = i - r * t.M;
+    t.slots[(static_cast<size_t>(r) * t.M + m) * grid + blockIdx.x] = row_key[m];
   }
-  for (int i = v_lo + (nv << 3) + tid; i < row_hi; i += nthreads) offer(__ldcg(row + i), i);
 }
 
-// The k-th largest of the `grid` slots of activation row m, by one warp (keys + 1; 0 when
-// fewer than k slots hold a value, which lets everything pass).
-__device__ inline std::uint32_t tail_row_bound(const PickTail& t, int m, int grid, int lane) {
+// The k-th largest of the `grid` slots of one activation row (`row_slots`, a row of one
+// copy of the table), by one warp.  Slot values are keys + 1; the result is 0 when fewer
+// than k slots hold a value, which lets everything pass.
+__device__ inline std::uint32_t row_bound(const std::uint32_t* row_slots, int grid, int k, int lane) {
   constexpr int kPerLane = kTailMaxCtas / 32;
   std::uint32_t key[kPerLane];
 #pragma unroll
   for (int j = 0; j < kPerLane; ++j) {
     const int c = lane + 32 * j;
-    key[j] = c < grid ? __ldcg(t.slots + static_cast<size_t>(c) * t.M + m) : 0u;
+    key[j] = c < grid ? __ldcg(row_slots + c) : 0u;
   }
   std::uint32_t T = 0;
   for (int bit = 16; bit >= 0; --bit) {
@@ -428,70 +398,9 @@ __device__ inline std::uint32_t tail_row_bound(const PickTail& t, int m, int gri
 #pragma unroll
     for (int j = 0; j < kPerLane; ++j) c += key[j] >= trial;
     c = __reduce_add_sync(0xffffffffu, c);
-    if (c >= t.k) T = trial;
+    if (c >= k) T = trial;
   }
-  return T;  // a slot value is key + 1, so "key >= T - 1", i.e. key + 1 >= T
-}
-
-// Called by all `nthreads` threads of a projection CTA (barrier `bar_id` spans exactly
-// them) once its logits of rows [row_lo, row_hi) are written and its final maxima are in
-// its slots.  Returns true in the CTA that took the launch's last ticket.
-static __device__ __noinline__ bool tail_collect(const PickTail& t, int row_lo, int row_hi, TailSmem& ts, int tid,
-                                    int nthreads, int bar_id) {
-  const int warp = tid >> 5, lane = tid & 31, nwarps = nthreads >> 5;
-  const int grid = static_cast<int>(gridDim.x);
-  auto cta_sync = [&]() { asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(nthreads) : "memory"); };
-  if (warp == 0) {
-    // A CTA that finishes before another one has published anything would find an empty
-    // slot and so a useless bound: give the others a few microseconds (they publish
-    // after their first m-tile).  Not needed for correctness.
-    const long long t0 = global_ns();
-    for (;;) {
-      int filled = 0;
-      for (int c = lane; c < grid; c += 32) filled += __ldcg(t.slots + static_cast<size_t>(c) * t.M) != 0u;
-      filled = __reduce_add_sync(0xffffffffu, filled);
-      if (filled >= grid || global_ns() - t0 > 4000) break;
-      __nanosleep(200);
-    }
-  }
-  cta_sync();
-  for (int m = warp; m < t.M; m += nwarps) {
-    const std::uint32_t T = tail_row_bound(t, m, grid, lane);
-    if (lane == 0) ts.bound[m] = T == 0u ? 0u : T - 1u;
-  }
-  cta_sync();
-  if (row_lo < row_hi)
-    for (int m = 0; m < t.M; ++m) tail_scan_rows(t, m, row_lo, row_hi, ts.bound[m], tid, nthreads);
-  // candidates and counts are visible before the ticket: the barrier orders them before
-  // thread 0's fence, which is cumulative
-  cta_sync();
-  if (tid == 0) {
-    __threadfence();
-    ts.last = atomicInc(t.ticket, static_cast<unsigned int>(grid - 1)) == static_cast<unsigned int>(grid - 1);
-    __threadfence();
-  }
-  cta_sync();
-  const bool last = ts.last != 0;
-  if (last) {
-    // every CTA is past the slots: clear them for the next call (the ticket has wrapped to 0)
-    for (int i = tid; i < grid * t.M; i += nthreads) t.slots[i] = 0u;
-  }
-  return last;
-}
-
-// The last CTA's pick of all rows (kSelectThreads threads): local pick, then, when the
-// vocabulary is split over ranks, all rows are sent before any is awaited.
-static __device__ __noinline__ void tail_pick_rows(const PickTail& t, int tid, SelectSmem& sm) {
-  for (int m = 0; m < t.M; ++m) {
-    select_row(t.sel, m, tid, sm);
-    if (t.ex.world >= 1) {
-      pick_sync();  // the row's pick is in local_packed
-      exchange_send_row(t.ex, m, tid);
-    }
-    pick_sync();
-  }
-  if (t.ex.world >= 1)
-    for (int m = 0; m < t.M; ++m) exchange_recv_row(t.ex, m, tid, sm);
+  return T;
 }
 
 #endif  // __CUDACC__

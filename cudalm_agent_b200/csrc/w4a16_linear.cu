@@ -15,7 +15,7 @@ namespace cb200 {
 // tensor-memory path for batched rows (w4a16_tc.cu)
 bool tc_eligible(const cudalm_b200_linear& l);
 int run_tc(const cudalm_b200_linear* ls, int count, cudaStream_t stream);
-int run_tc_with_pick(const cudalm_b200_linear& l, const PickTail& pick, cudaStream_t stream);
+int run_tc_with_pick(const cudalm_b200_linear& l, const PickTail& pick, cudaStream_t stream, int* grid_out);
 int run_tc_extra(const cudalm_b200_linear& l, const std::uint8_t* weight2,
                  const std::uint16_t* scales2, const std::uint16_t* residual, cudaStream_t stream);
 struct TcGroup;
@@ -478,15 +478,14 @@ int run_extra(cudalm_b200_linear l, const LinearExtra& ex, cudaStream_t stream) 
 }  // namespace
 
 // Used by the vocabulary projection: one staged launch of a single projection (M rows
-// in one pass) whose CTAs also collect the candidates of the token pick and, for a few
-// rows, rank them.  Returns ERR_UNSUPPORTED when the projection cannot take the staged
-// path in one pass.
-int run_linear_with_pick(const cudalm_b200_linear& l, const PickTail& pick, cudaStream_t stream) {
+// in one pass) whose CTAs also leave their largest outputs per activation row in the
+// pick's table.  Returns ERR_UNSUPPORTED when the projection cannot take the staged path
+// in one pass.
+int run_linear_with_pick(const cudalm_b200_linear& l, const PickTail& pick, cudaStream_t stream,
+                         int* grid_out) {
   if (int rc = validate(l)) return rc;
-  if (l.M >= g_tc_min_rows.load(std::memory_order_relaxed) && tc_eligible(l)) {
-    if (pick.inline_pick) return CUDALM_B200_ERR_UNSUPPORTED;
-    return run_tc_with_pick(l, pick, stream);
-  }
+  if (l.M >= g_tc_min_rows.load(std::memory_order_relaxed) && tc_eligible(l))
+    return run_tc_with_pick(l, pick, stream, grid_out);
   if (!stream_eligible(l)) return CUDALM_B200_ERR_UNSUPPORTED;
   if (max_rows_per_pass(l.K) < l.M) return CUDALM_B200_ERR_UNSUPPORTED;
   StreamParams p;
@@ -496,7 +495,7 @@ int run_linear_with_pick(const cudalm_b200_linear& l, const PickTail& pick, cuda
   p.total_mt = mtiles(l.N);
   p.total_cost = p.total_mt * chunks_per_mtile(l.K);
   p.pick = pick;
-  return launch_stream(p, l.K, l.M, stream, nullptr);
+  return launch_stream(p, l.K, l.M, stream, grid_out);
 }
 
 // True when run_linear_with_pick would take the projection (the same tests, no launch).

@@ -42,7 +42,7 @@ constexpr int kMaxDepth = 4;
 constexpr int kMaxWarps = 16;
 // shared-memory header: "full" mbarriers [kMaxWarps][kMaxDepth], CtaControl, and in
 // its last 512 bytes the "empty" mbarriers [kMaxWarps][kMaxDepth] of the producer form
-constexpr int kHeaderBytes = 2304;
+constexpr int kHeaderBytes = 2176;
 // projections of a CTA's range whose descriptors are kept in shared memory
 constexpr int kDescCache = 8;
 // largest M*K one warp refills on its own (the barrier-free change of projection)
@@ -83,8 +83,8 @@ struct StreamParams {
   int x_bytes;      // one activation buffer
   int x_buffers;    // 1, or 2 for the barrier-free change of projection
   int* status;      // device status word
-  // CTA_MAX only (the vocabulary projection, one projection per launch): the token
-  // pick that the kernel's CTAs finish after their rows (lm_head_pick.cuh)
+  // CTA_MAX only (the vocabulary projection, one projection per launch): the table the
+  // CTAs leave their maxima in for the token pick (lm_head_pick.cuh)
   PickTail pick;
   // Optional, for launches with a device table: per CTA {first m-tile, its
   // projection}, gridDim.x + 1 entries, so that a CTA finds its range with two
@@ -610,10 +610,8 @@ __device__ __forceinline__ void consume_chunk(const std::uint8_t* stage, const s
 
 // ---------------------------------------------------------------------------
 // Streaming kernel.  CTA_MAX (the vocabulary projection) additionally keeps, per
-// activation row, the largest bf16-rounded output the CTA has produced so far,
-// publishes it for the other CTAs, and finishes with the token pick's tail
-// (lm_head_pick.cuh): candidates from the CTA's own rows, and in the launch's last
-// CTA the ranking.
+// activation row, the largest bf16-rounded output the CTA has produced and leaves it in
+// the table that the token pick derives its bounds from (lm_head_pick.cuh).
 // ---------------------------------------------------------------------------
 
 // Shared-memory address of activation buffer b.  The offset goes through an
@@ -960,27 +958,6 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) vmax[nt][0] = vmax[nt][1] = -INFINITY;
 
-  int tiles_done = 0;
-  // CTA_MAX: the warp's maxima (over the eight row-lanes that share a column pair) into
-  // the CTA's per-row keys
-  auto publish_maxima = [&]() {
-    const int M = desc_table(p)->M;
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        float v = vmax[nt][c];
-        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
-        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
-        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
-        const int col = nt * 8 + 2 * lane + c;
-        if (lane < 4 && col < M && col < kMaxPassRows)
-          atomicMax(&ctl->row_key[col], order_key(float_to_bf16_bits(v)) + 1u);
-      }
-    }
-    __syncwarp();
-  };
-
   bool dead = false;     // a wait ran out: stop computing, keep attending barriers
   XFill xf{d_first};
   // last projection of this CTA's range
@@ -1154,15 +1131,6 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
             }
           }
         }
-        if (CTA_MAX) {
-          // the warp's first two m-tiles and then every fourth one: fold the warp's maxima
-          // into the CTA's and publish them, so that CTAs that finish early find bounds
-          ++tiles_done;
-          if (tiles_done <= 2 || (tiles_done & 3) == 0) {
-            publish_maxima();
-            tail_publish(p.pick, ctl->row_key, lane);
-          }
-        }
       }
     }
   }
@@ -1197,17 +1165,25 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
   }
 
   if (CTA_MAX) {
-    // final maxima of this CTA in its slots, then the pick's tail
-    publish_maxima();
-    consumer_sync();  // every warp has folded its maxima in; rings and activations are free
-    tail_publish(p.pick, ctl->row_key, tid);
-    if (tid < 32) __threadfence();
-    TailSmem& ts = *reinterpret_cast<TailSmem*>(rings);
-    const int LN = desc_table(p)->N;
-    const int row_lo = min(LN, mt_lo * kMTileRows), row_hi = min(LN, mt_hi * kMTileRows);
-    const bool last = tail_collect(p.pick, mt_lo < mt_hi ? row_lo : 0, mt_lo < mt_hi ? row_hi : 0, ts, tid,
-                                   NWARPS * 32, 1);
-    if (last && p.pick.inline_pick && tid < kSelectThreads) tail_pick_rows(p.pick, tid, ts.sel);
+    // This CTA's largest outputs per activation row into its slots of the table that the
+    // follow-up launch derives the rows' bounds from: reduce over the eight row-lanes
+    // that share a column pair, then over the warps (shared-memory maxima of keys).
+    const int M = desc_table(p)->M;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        float v = vmax[nt][c];
+        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
+        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
+        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
+        const int col = nt * 8 + 2 * lane + c;
+        if (lane < 4 && col < M && col < kMaxPassRows)
+          atomicMax(&ctl->row_key[col], order_key(float_to_bf16_bits(v)) + 1u);
+      }
+    }
+    consumer_sync();
+    if (tid < 32) tail_publish(p.pick, ctl->row_key, tid);
   }
 }
 

@@ -100,8 +100,8 @@ struct TcParams {
   int total_cost;
   int* status;
   // Optional (vocabulary projection, one projection per launch; pick.slots non-null):
-  // the CTAs keep per activation row the largest bf16-rounded output they have
-  // produced, publish it, and finish with the token pick's tail (lm_head_pick.cuh).
+  // the CTAs keep per activation row the largest bf16-rounded output they have produced
+  // and leave it in the table the token pick derives its bounds from (lm_head_pick.cuh).
   PickTail pick;
 };
 
@@ -672,11 +672,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
           const int n = 2 * word + copy;
           if (n < LM) atomicMax(&sm->row_max[n], bf16_key(copy ? (kv[0] >> 16) : (kv[0] & 0xFFFFu)));
         }
-        // publish the CTA's maxima so far (key + 1) for CTAs that finish earlier
-        __syncwarp();
-        for (int n = lane; n < LM && n < kMaxPassRows; n += 32)
-          reinterpret_cast<volatile std::uint32_t*>(p.pick.slots)[static_cast<std::size_t>(blockIdx.x) * LM + n] =
-              *reinterpret_cast<volatile std::uint32_t*>(&sm->row_max[n]) + 1u;
       }
       if (direct) {
         // outputs the TMA unit cannot address: plain stores, one row per thread
@@ -809,23 +804,19 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
         ++n_stores;
       }
       asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-      // the stored outputs are re-read with ordinary loads by the pick's tail
-      asm volatile("fence.proxy.async;" ::: "memory");
     }
   }
 
   __syncthreads();
   if (p.pick.slots != nullptr) {
-    // final maxima of this CTA in its slots, then the pick's tail on the CTA's own rows
-    const int LM = tbl[0].M, LN = tbl[0].N;
-    if (tid < LM && tid < kMaxPassRows) {
-      p.pick.slots[static_cast<std::size_t>(blockIdx.x) * LM + tid] = sm->row_max[tid] + 1u;
-      __threadfence();
+    // final maxima of this CTA in its slots (every copy of the table); the follow-up launch
+    // derives the rows' bounds from them and scans the logits
+    const int LM = tbl[0].M;
+    for (int i = tid; i < kSlotReplicas * LM; i += kTcThreads) {
+      const int r = i / LM, n = i - r * LM;
+      if (n < kMaxPassRows)
+        p.pick.slots[(static_cast<std::size_t>(r) * LM + n) * gridDim.x + blockIdx.x] = sm->row_max[n] + 1u;
     }
-    TailSmem& ts = *reinterpret_cast<TailSmem*>(stages);
-    const bool mine = it_lo < it_hi;
-    (void)tail_collect(p.pick, mine ? min(LN, it_lo * kTcItemRows) : 0, mine ? min(LN, it_hi * kTcItemRows) : 0,
-                       ts, tid, kTcThreads, 1);
   }
   if (*abort_flag && tid == 0) atomicExch(p.status, CUDALM_B200_ERR_TIMEOUT);
   tc_fence_after();
@@ -1051,14 +1042,14 @@ int run_tc_extra(const cudalm_b200_linear& l, const std::uint8_t* weight2,
 
 // The vocabulary projection: one projection whose CTAs also collect the candidates of
 // the token pick.  The grid is bounded by the pick's slot table before anything is enqueued.
-int run_tc_with_pick(const cudalm_b200_linear& l, const PickTail& pick, cudaStream_t stream) {
+int run_tc_with_pick(const cudalm_b200_linear& l, const PickTail& pick, cudaStream_t stream, int* grid_out) {
   TcParams p;
   std::memset(&p, 0, sizeof(p));
   int ntok = 0;
   if (int rc = tc_describe(&l, 1, p.inl, &p.total_items, &p.total_cost, &ntok)) return rc;
   p.n_desc = 1;
   p.pick = pick;
-  return tc_run_params(p, ntok, stream, nullptr, kTailMaxCtas);
+  return tc_run_params(p, ntok, stream, grid_out, kTailMaxCtas);
 }
 
 // Up to CUDALM_B200_MAX_INLINE_LINEARS projections in one launch.
@@ -1116,3 +1107,4 @@ void tc_group_destroy(TcGroup* g) {
 }
 
 }  // namespace cb200
+

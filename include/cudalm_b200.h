@@ -174,8 +174,8 @@ CUDALM_B200_API int cudalm_b200_linear_residual_bf16(const uint8_t* weight,
  * whole of it): it holds the counters of the pick, which every call leaves at zero
  * for the next one.  Calls that share a workspace must not overlap on the GPU; after
  * a CUDALM_B200_ERR_TIMEOUT in the device status word, zero it again.
- * Up to 4 activation rows the call is ONE launch: the projection's CTAs collect the
- * candidates of their own rows and the last of them ranks; more rows add one launch. */
+ * A call is two launches: the projection, then the scan of the logits (still in L2)
+ * whose last CTA per activation row ranks the candidates. */
 CUDALM_B200_API size_t cudalm_b200_lm_head_workspace_bytes(int N, int K, int M, int top_k,
                                                            int need_logits);
 CUDALM_B200_API int cudalm_b200_lm_head_workspace_init(void* workspace, size_t workspace_bytes,
@@ -264,12 +264,11 @@ CUDALM_B200_API int cudalm_b200_topk_exchange_merge(const int32_t* local_packed,
                                                     int32_t* argmax_out, int32_t* topk_idx,
                                                     uint16_t* topk_val, void* stream);
 
-/* The whole vocabulary-parallel step of one rank in one launch (up to 4 rows; two
- * launches for more): the projection of this rank's rows, whose CTAs collect the rows'
- * local candidates; the threads that rank them (into `local_packed`: ids int32
- * [rows_cap][top_k], then values bf16) send them to the other ranks and merge theirs as
- * cudalm_b200_topk_exchange_merge does; argmax_out / topk_idx / topk_val receive the
- * merged pick.  Arguments as
+/* The whole vocabulary-parallel step of one rank in two launches: the projection of
+ * this rank's rows, then the scan whose last CTA per row picks the row's local
+ * candidates (into `local_packed`: ids int32 [rows_cap][top_k], then values bf16),
+ * sends them to the other ranks and merges theirs as cudalm_b200_topk_exchange_merge
+ * does; argmax_out / topk_idx / topk_val receive the merged pick.  Arguments as
  * cudalm_b200_lm_head_topk and cudalm_b200_topk_exchange_merge; M must fit one pass
  * (UNSUPPORTED otherwise: call the two entries one after the other). */
 CUDALM_B200_API int cudalm_b200_lm_head_topk_exchange(
