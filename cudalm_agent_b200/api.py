@@ -161,11 +161,15 @@ def _need(t: torch.Tensor, dtype: torch.dtype, name: str) -> None:
         raise ValueError(f"{name} must be {dtype}, got {t.dtype}")
     if not t.is_contiguous():
         raise ValueError(f"{name} must be contiguous")
-    # the library works on the current device (its per-device caches, status word and
-    # scratch): a tensor of another device would be read through the wrong context
-    if t.device.index != torch.cuda.current_device():
-        raise ValueError(f"{name} is on cuda:{t.device.index}, the current device is "
-                         f"cuda:{torch.cuda.current_device()}")
+
+
+def _need_current_device(*tensors: torch.Tensor) -> None:
+    """The library works on the current device (its per-device caches, status word and
+    scratch): a tensor of another device would be read through the wrong context."""
+    cur = torch.cuda.current_device()
+    for t in tensors:
+        if t.device.index != cur:
+            raise ValueError(f"a tensor is on cuda:{t.device.index}, the current device is cuda:{cur}")
 
 
 def _need_sizes(weight: torch.Tensor, scales: torch.Tensor, x: torch.Tensor, y: torch.Tensor,
@@ -245,6 +249,7 @@ def int4_gemv_bf16(weight: torch.Tensor, scales: torch.Tensor, x: torch.Tensor,
     if y is None:
         y = torch.empty(N, dtype=torch.bfloat16, device=x.device)
     _need(y, torch.bfloat16, "y")
+    _need_current_device(weight, scales, x, y)
     _need_sizes(weight, scales, x, y, N, K, 1)
     st = load_library().cudalm_b200_int4_gemv_bf16(_ptr(weight), _ptr(scales), _ptr(x), _ptr(y),
                                                    N, K, _stream())
@@ -266,6 +271,7 @@ def batch_int4_gemv_bf16(weight: torch.Tensor, scales: torch.Tensor, x: torch.Te
     if y is None:
         y = torch.empty((B, N), dtype=torch.bfloat16, device=x.device)
     _need(y, torch.bfloat16, "y")
+    _need_current_device(weight, scales, x, y)
     _need_sizes(weight, scales, x, y, N, K, B)
     st = load_library().cudalm_b200_batch_int4_gemv_bf16(_ptr(weight), _ptr(scales), _ptr(x),
                                                          _ptr(y), N, K, B, _stream())
@@ -475,6 +481,7 @@ class LmHead:
             raise ValueError(f"M={M} exceeds max_rows={self.max_rows}")
         if x.numel() != M * self.rows.K:
             raise ValueError(f"x holds {x.numel()} values, expected M * K = {M * self.rows.K}")
+        _need_current_device(x, self.rows.weight)
         st = load_library().cudalm_b200_lm_head_topk(
             _ptr(self.rows.weight), _ptr(self.rows.scale), _ptr(x), self.rows.N, self.rows.K, M,
             self.top_k, self.id_offset, _ptr(self.logits), _ptr(self.argmax),
