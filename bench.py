@@ -338,25 +338,33 @@ def lm_head_timings(eng, torch, dist, lins, lo, x, M, mode, steps, warmup, in_fl
     streams = [torch.cuda.Stream() for _ in range(in_flight)]
     torch.cuda.synchronize()
 
-    def round_of_calls(i):
-        for j in range(in_flight):
-            with torch.cuda.stream(streams[j]):
-                pipe[j].forward(x)
+    width = [in_flight]
 
     def region(i):
         cur = torch.cuda.current_stream()
-        for st in streams:
+        for st in streams[:width[0]]:
             st.wait_stream(cur)
-        round_of_calls(i)
-        for st in streams:
+        for j in range(width[0]):
+            with torch.cuda.stream(streams[j]):
+                pipe[j].forward(x)
+        for st in streams[:width[0]]:
             cur.wait_stream(st)
 
     rounds = max(2, steps // in_flight)
     pipe_ms, _ = time_steps(torch, region, rounds, 2, dist, min_seconds=0.05)
+    best = (pipe_ms / (rounds * in_flight), in_flight)
+    if in_flight > 2:
+        # fewer calls in flight: more of them does not always help, since their kernels share the SMs
+        width[0] = 2
+        rounds2 = max(2, steps // 2)
+        pipe2_ms, _ = time_steps(torch, region, rounds2, 2, dist, min_seconds=0.05)
+        width[0] = in_flight
+        if pipe2_ms / (rounds2 * 2) < best[0]:
+            best = (pipe2_ms / (rounds2 * 2), 2)
     for h in heads + pipe:
         if vp:
             h.close()
-    return lat_ms / steps, pipe_ms / (rounds * in_flight), out, in_flight
+    return lat_ms / steps, best[0], out, best[1]
 
 
 def bench_lm_head(eng, torch, dist, rank, world, steps, warmup):

@@ -12,9 +12,9 @@
 //   * each of 256 "row" threads turns its row's 64 bytes into 64 registers of
 //     exact bf16 pairs (k, k + 1) and writes them to tensor memory (tcgen05.st)
 //     as the A operand of eight K=16 MMAs: lane = row, 8 columns per MMA;
-//   * one thread per tile issues the eight tcgen05.mma (A from tensor memory,
-//     B = the activations in the stage) into a per-group accumulator in tensor
-//     memory and commits to mbarriers;
+//   * one thread per tile and buffer issues the eight tcgen05.mma (A from tensor
+//     memory, B = the activations in the stage) into a per-group accumulator in
+//     tensor memory and commits to an mbarrier;
 //   * the row threads of the read-back warps fetch the accumulator
 //     (tcgen05.ld) and fold it into registers: acc[n] += scale[row, group] * sum[n].
 //
@@ -52,18 +52,25 @@ __host__ __device__ constexpr int tc_stage_bytes(int ntok) { return kTcWeightByt
 __host__ __device__ constexpr int tc_out_bytes(int ntok) { return ntok * kTcRowsPerTile * 2; }
 // Warp roles.  Dequantisation and read-back are separate warps so that the
 // threads that feed the tensor core never wait for its results.
+// Consecutive groups alternate between two A and two D buffers per tile.  Issuing eight
+// small MMAs and a commit keeps a single thread busy for longer than the tensor pipe needs
+// for them (it competes for issue slots with the arithmetic warps), so every (tile,
+// buffer) pair has an issuer of its own: four threads share the issue work, and one
+// issuer's waits and commits run while the others' MMAs occupy the pipe.
 //   warps 0..7   dequantise: tile = warp >> 2, rows 32 (warp & 3) .. +31 of the tile
+//                (a warp reaches only its own quarter of tensor memory)
 //   warps 8..15  read the accumulators back and fold them in: same row mapping
 //   warp 16      TMA producer
-//   warps 17,18  MMA issuers, one per tile
-//   warp 19      output stores: lane 0 for tile 0, lane 1 for tile 1 (so that no
+//   warps 17..20 MMA issuers: buffer = (warp - 17) >> 1, tile = (warp - 17) & 1
+//   warp 21      output stores: lane 0 for tile 0, lane 1 for tile 1 (so that no
 //                read-back thread waits on a store)
+//   warps 22,23  idle (register reallocation works on groups of four warps)
 constexpr int kTcDequantWarps = 8;
 constexpr int kTcFoldWarp0 = 8;
 constexpr int kTcProducerWarp = 16;
 constexpr int kTcMmaWarp = 17;
-constexpr int kTcStoreWarp = 19;  // lanes 0 and 1 issue the TMA stores of tiles 0 and 1
-constexpr int kTcThreads = 640;   // 20 warps: one more would cut the register budget per thread
+constexpr int kTcStoreWarp = 21;  // lanes 0 and 1 issue the TMA stores of tiles 0 and 1
+constexpr int kTcThreads = 768;   // 24 warps, 80 registers each at launch
 constexpr unsigned long long kTcWaitNs = 400000000ull;
 
 struct alignas(64) TcDesc {
@@ -188,32 +195,37 @@ __device__ __forceinline__ void tmem_st16(std::uint32_t taddr, const std::uint32
       "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
-__device__ __forceinline__ void tmem_ld16(std::uint32_t taddr, float* f) {
-  std::uint32_t r[16];
+__device__ __forceinline__ void tmem_ld16_nowait(std::uint32_t taddr, std::uint32_t* r) {
   asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-        "=r"(r[14]), "=r"(r[15])
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
       : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 16; ++i) f[i] = __uint_as_float(r[i]);
 }
-
-__device__ __forceinline__ void tmem_ld8(std::uint32_t taddr, float* f) {
-  std::uint32_t r[8];
+__device__ __forceinline__ void tmem_ld32_nowait(std::uint32_t taddr, std::uint32_t* r) {
   asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-        "=r"(r[7])
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr)
       : "memory");
+}
+__device__ __forceinline__ void tmem_ld64_nowait(std::uint32_t taddr, std::uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x64.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63}, [%64];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(r[i]);
+}
+// NCOL consecutive accumulator columns of this thread's lane, one instruction, one wait
+template <int NCOL>
+__device__ __forceinline__ void tmem_ld_cols(std::uint32_t taddr, std::uint32_t* r) {
+  if (NCOL == 64) tmem_ld64_nowait(taddr, r);
+  else if (NCOL == 32) tmem_ld32_nowait(taddr, r);
+  else tmem_ld16_nowait(taddr, r);
+  tmem_ld_wait();
 }
 
 // Shared-memory matrix descriptor of one K=16 slice of the B operand inside an
@@ -280,10 +292,11 @@ __device__ __forceinline__ void dequant_word_natural(std::uint32_t w, std::uint3
 struct TcSmem {
   std::uint64_t full[kTcMaxStages];
   std::uint64_t empty[kTcMaxStages];
+  // [tile][buffer]: the A buffer holds the group (128 dequantising threads) and its D
+  // buffer has been read back (128 read-back threads, which arrive once at the start)
   std::uint64_t a_full[kTcTiles][2];
   // the group's MMAs have completed: its A buffer is free again, its D buffer is full
   std::uint64_t mma_done[kTcTiles][2];
-  std::uint64_t d_free[kTcTiles][2];
   std::uint64_t g_full;   // pair: tile 0's gate outputs are in its buffer
   std::uint64_t g_free;   // pair: tile 1 has taken them
   std::uint64_t res_full[kTcTiles];  // residual: the tile's residual values are in its buffer
@@ -370,14 +383,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
   if (tid == 0) {
     for (int s = 0; s < kTcStages; ++s) {
       mbar_init(&sm->full[s], 1);
-      // the row threads have taken the weights out, both issuers' MMAs have read the activations
-      mbar_init(&sm->empty[s], kTcDequantWarps * 32 + kTcTiles);
+      // every dequantising thread has taken its bytes out, and the MMAs that read the
+      // activations are done (one arrival per read-back warp and group, two groups)
+      mbar_init(&sm->empty[s], kTcDequantWarps * 32 + 16);
     }
     for (int t = 0; t < kTcTiles; ++t) {
       for (int b = 0; b < 2; ++b) {
-        mbar_init(&sm->a_full[t][b], kTcRowsPerTile);
+        mbar_init(&sm->a_full[t][b], 2 * kTcRowsPerTile);
         mbar_init(&sm->mma_done[t][b], 1);
-        mbar_init(&sm->d_free[t][b], kTcRowsPerTile);
       }
       if (t == 0) {
         mbar_init(&sm->g_full, kTcRowsPerTile);
@@ -424,102 +437,161 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
   TcWalk wk;
   wk.start(tbl, p.n_desc, d_first);
 
-  if (warp == kTcProducerWarp) {
-    // ---------------- TMA producer ----------------
-    if (lane == 0) {
-      const std::uint64_t policy = policy_evict_first();
-      bool ok = true;
-      const TcDesc* L = nullptr;
-      int G = 0, item_begin = 0;
-      bool pair = false;
-      int ps = 0;                  // stage to fill next
-      std::uint32_t ps_phase = 0;  // phase its `full` barrier completes next
-      bool ps_round = false;       // every stage has been used at least once
-      for (int item = it_lo; item < it_hi && ok && !*abort_flag; ++item) {
-        if (wk.seek(item) || L == nullptr) {
-          L = tbl + wk.d;
-          G = L->K >> 7;
-          item_begin = L->item_begin;
-          pair = L->mode == kTcPair;
-        }
-        const int j = item - item_begin;
-        // plain: tiles are consecutive 128-row blocks of one matrix; pair: the same
-        // 128 rows of the gate (tile 0) and up (tile 1) matrices
-        const int row0 = pair ? j * kTcRowsPerTile : j * kTcItemRows;
-        const int tile_step = pair ? 0 : kTcRowsPerTile;
-        for (int c = 0; c < (G + 1) / 2; ++c) {
-          // second and later uses of a stage wait until its previous content is done with
-          if (ps_round && !tc_wait(&sm->empty[ps], ps_phase ^ 1u, abort_flag)) {
-            ok = false;
-            break;
+  // Registers follow the roles (warp groups of four warps; every warp of a group executes
+  // the same reallocation before the group's roles part): the read-back warps keep a row
+  // of accumulators and half a fetched group sum in registers, the dequantising warps
+  // work in chunks of 16 registers, the copy, issue and store warps need next to none.
+  // 256 x 56 + 256 x 144 + 256 x 40 is the 768 x 80 the CTA was launched with.
+  if (warp >= kTcProducerWarp) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;" ::: "memory");
+    if (warp == kTcProducerWarp) {
+      // ---------------- TMA producer ----------------
+      if (lane == 0) {
+        const std::uint64_t policy = policy_evict_first();
+        bool ok = true;
+        const TcDesc* L = nullptr;
+        int G = 0, item_begin = 0;
+        bool pair = false;
+        int ps = 0;                  // stage to fill next
+        std::uint32_t ps_phase = 0;  // phase its `full` barrier completes next
+        bool ps_round = false;       // every stage has been used at least once
+        for (int item = it_lo; item < it_hi && ok && !*abort_flag; ++item) {
+          if (wk.seek(item) || L == nullptr) {
+            L = tbl + wk.d;
+            G = L->K >> 7;
+            item_begin = L->item_begin;
+            pair = L->mode == kTcPair;
           }
-          const int s = ps;
-          std::uint8_t* st = stages + s * kStageBytes;
-          mbar_arrive_expect_tx(&sm->full[s], kStageBytes);
-          for (int t = 0; t < kTcTiles; ++t) {
-            asm volatile(
-                "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
-                ".L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;" ::"r"(
-                    smem_u32(st + t * kTcRowsPerTile * 128)),
-                "l"((pair && t == 1) ? &L->tmap2 : &L->tmap), "r"(c * 32), "r"(row0 + t * tile_step),
-                "r"(smem_u32(&sm->full[s])), "l"(policy)
-                : "memory");
-          }
-          // four boxes of 64 k each; k past K and rows past M arrive as zeros
-          for (int q = 0; q < 4; ++q) {
-            asm volatile(
-                "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
-                " [%0], [%1, {%2, %3}], [%4];" ::"r"(smem_u32(st + kTcWeightBytes + q * kBoxBytes)),
-                "l"(&L->xmap), "r"(c * 256 + q * 64), "r"(0), "r"(smem_u32(&sm->full[s]))
-                : "memory");
-          }
-          if (++ps == kTcStages) {
-            ps = 0;
-            ps_phase ^= 1u;
-            ps_round = true;
-          }
-        }
-      }
-    }
-  } else if (warp >= kTcMmaWarp && warp < kTcStoreWarp) {
-    // ---------------- MMA issuer, one per tile ----------------
-    if (lane == 0) {
-      const int t = warp - kTcMmaWarp;
-      const std::uint32_t tile_base = tmem_base + t * kColsPerTile;
-      const std::uint32_t desc_hi = static_cast<std::uint32_t>(tc_b_desc(0) >> 32);
-      const std::uint32_t desc_lo0 = static_cast<std::uint32_t>(tc_b_desc(0));
-      bool ok = true;
-      int G = 0;
-      int s = 0;                   // stage of the current group
-      std::uint32_t s_phase = 0;   // phase of that stage's barriers
-      for (int item = it_lo; item < it_hi && ok && !*abort_flag; ++item) {
-        if (wk.seek(item) || G == 0) G = tbl[wk.d].K >> 7;
-        for (int g = 0; g < G; ++g, ++git) {
-          const int buf = git & 1;
-          const std::uint32_t use = git >> 1;
-          ok = tc_wait(&sm->a_full[t][buf], use & 1u, abort_flag);
-          if (ok && use >= 1) ok = tc_wait(&sm->d_free[t][buf], (use - 1) & 1u, abort_flag);
-          // the stage's activations (its barrier has completed by now: the row
-          // threads waited for it before they signalled a_full)
-          if (ok && (g & 1) == 0) ok = tc_wait(&sm->full[s], s_phase, abort_flag);
-          if (!ok) break;
-          tc_fence_after();
-          const std::uint32_t b_addr =
-              smem_u32(stages + s * kStageBytes + kTcWeightBytes) + (g & 1) * 2 * kBoxBytes;
-          tc_mma_group(tile_base + 128 + buf * NTOK, tile_base + buf * 64,
-                       desc_lo0 | ((b_addr & 0x3FFFFu) >> 4), desc_hi, kBoxBytes >> 4, kIdesc);
-          tc_commit(&sm->mma_done[t][buf]);
-          if ((g & 1) || g == G - 1) {
-            tc_commit(&sm->empty[s]);  // these MMAs were the last readers of the stage's activations
-            if (++s == kTcStages) {
-              s = 0;
-              s_phase ^= 1u;
+          const int j = item - item_begin;
+          // plain: tiles are consecutive 128-row blocks of one matrix; pair: the same
+          // 128 rows of the gate (tile 0) and up (tile 1) matrices
+          const int row0 = pair ? j * kTcRowsPerTile : j * kTcItemRows;
+          const int tile_step = pair ? 0 : kTcRowsPerTile;
+          for (int c = 0; c < (G + 1) / 2; ++c) {
+            // second and later uses of a stage wait until its previous content is done with
+            if (ps_round && !tc_wait(&sm->empty[ps], ps_phase ^ 1u, abort_flag)) {
+              ok = false;
+              break;
+            }
+            const int s = ps;
+            std::uint8_t* st = stages + s * kStageBytes;
+            mbar_arrive_expect_tx(&sm->full[s], kStageBytes);
+            for (int t = 0; t < kTcTiles; ++t) {
+              asm volatile(
+                  "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+                  ".L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;" ::"r"(
+                      smem_u32(st + t * kTcRowsPerTile * 128)),
+                  "l"((pair && t == 1) ? &L->tmap2 : &L->tmap), "r"(c * 32), "r"(row0 + t * tile_step),
+                  "r"(smem_u32(&sm->full[s])), "l"(policy)
+                  : "memory");
+            }
+            // four boxes of 64 k each; k past K and rows past M arrive as zeros
+            for (int q = 0; q < 4; ++q) {
+              asm volatile(
+                  "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+                  " [%0], [%1, {%2, %3}], [%4];" ::"r"(smem_u32(st + kTcWeightBytes + q * kBoxBytes)),
+                  "l"(&L->xmap), "r"(c * 256 + q * 64), "r"(0), "r"(smem_u32(&sm->full[s]))
+                  : "memory");
+            }
+            if (++ps == kTcStages) {
+              ps = 0;
+              ps_phase ^= 1u;
+              ps_round = true;
             }
           }
         }
       }
+    } else if (warp >= kTcMmaWarp && warp < kTcStoreWarp) {
+      // ---------------- MMA issuer, one per buffer and tile ----------------
+      if (lane == 0) {
+        const std::uint32_t buf = static_cast<std::uint32_t>(warp - kTcMmaWarp) >> 1;  // A and D buffer
+        const int t = (warp - kTcMmaWarp) & 1;
+        const std::uint32_t desc_hi = static_cast<std::uint32_t>(tc_b_desc(0) >> 32);
+        const std::uint32_t desc_lo0 = static_cast<std::uint32_t>(tc_b_desc(0));
+        const std::uint32_t stage0 = smem_u32(stages) + kTcWeightBytes;
+        const std::uint32_t d_tmem = tmem_base + t * kColsPerTile + 128 + buf * NTOK;
+        const std::uint32_t a_tmem = tmem_base + t * kColsPerTile + buf * 64;
+        std::uint64_t* const a_full = &sm->a_full[t][buf];
+        std::uint64_t* const mma_done = &sm->mma_done[t][buf];
+        bool ok = true;
+        int G = 0;
+        int s = 0;  // stage of the current group
+        for (int item = it_lo; item < it_hi && ok && !*abort_flag; ++item) {
+          if (wk.seek(item) || G == 0) G = tbl[wk.d].K >> 7;
+          for (int g = 0; g < G; ++g, ++git) {
+            if ((git & 1u) == buf) {
+              const std::uint32_t b_addr = stage0 + s * kStageBytes + (g & 1) * 2 * kBoxBytes;
+              // the A buffer holds the group and the D buffer has been read back; the
+              // stage's activations have landed (the row threads saw its barrier
+              // complete before they arrived here)
+              ok = tc_wait(a_full, (git >> 1) & 1u, abort_flag);
+              if (!ok) break;
+              tc_fence_after();
+              tc_mma_group(d_tmem, a_tmem, desc_lo0 | ((b_addr & 0x3FFFFu) >> 4), desc_hi,
+                           kBoxBytes >> 4, kIdesc);
+              tc_commit(mma_done);
+            }
+            if (((g & 1) || g == G - 1) && ++s == kTcStages) s = 0;
+          }
+        }
+      }
+    } else if (warp == kTcStoreWarp) {
+      // ---------------- output stores, one lane per tile ----------------
+      if (lane < kTcTiles) {
+        const int tile = lane;
+        const TcDesc* L = nullptr;
+        int LN = 0, item_begin = 0;
+        bool direct = false, pair = false;
+        std::uint32_t n_stores = 0;  // items of this tile that went through the output buffer
+        bool ok = true;
+        for (int item = it_lo; item < it_hi && ok && !*abort_flag; ++item) {
+          if (wk.seek(item) || L == nullptr) {
+            L = tbl + wk.d;
+            LN = L->N;
+            item_begin = L->item_begin;
+            direct = L->direct_store != 0;
+            pair = L->mode == kTcPair;
+          }
+          if (direct) continue;  // the read-back threads store these rows themselves
+          const int j = item - item_begin;
+          if (pair && tile == 0) continue;  // a pair's outputs all leave through tile 1's buffer
+          const int row0 = pair ? j * kTcRowsPerTile : j * kTcItemRows + tile * kTcRowsPerTile;
+          if (EXTRA && L->mode == kTcResidual) {
+            // the buffer is free here (the previous store has read it): fetch the tile's
+            // residual values into it while the item is being computed
+            std::uint8_t* buf = outsm + tile * tc_out_bytes(NTOK);
+            if (row0 < LN) {
+              mbar_arrive_expect_tx(&sm->res_full[tile], tc_out_bytes(NTOK));
+              asm volatile(
+                  "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+                  " [%0], [%1, {%2, %3}], [%4];" ::"r"(smem_u32(buf)),
+                  "l"(&L->rmap), "r"(row0), "r"(0), "r"(smem_u32(&sm->res_full[tile]))
+                  : "memory");
+            } else {
+              mbar_arrive_expect_tx(&sm->res_full[tile], 0);
+            }
+          }
+          if (!tc_wait(&sm->out_full[tile], n_stores & 1u, abort_flag)) {
+            ok = false;
+            break;
+          }
+          if (row0 < LN) {
+            asm volatile(
+                "cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(
+                    &L->ymap),
+                "r"(row0), "r"(0), "r"(smem_u32(outsm + tile * tc_out_bytes(NTOK)))
+                : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          }
+          mbar_arrive(&sm->out_free[tile]);
+          ++n_stores;
+        }
+        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+      }
     }
   } else if (warp < kTcDequantWarps) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;" ::: "memory");
     // ---------------- dequantise and feed the A operand ----------------
     const int tile = warp >> 2;
     const int lrow = (warp & 3) * 32 + lane;  // row inside the tile
@@ -539,22 +611,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
           if (!alive) break;
         }
         const std::uint8_t* rowp = stages + s * kStageBytes + tile * kTcRowsPerTile * 128 + lrow * 128;
-        std::uint32_t regs[64];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const uint4 v = lds128(rowp + (((4 * half + q) ^ (lrow & 7)) << 4));
-          dequant_word_natural(v.x, regs + 16 * q);
-          dequant_word_natural(v.y, regs + 16 * q + 4);
-          dequant_word_natural(v.z, regs + 16 * q + 8);
-          dequant_word_natural(v.w, regs + 16 * q + 12);
-        }
-        if (half == 1 || g == G - 1) {
-          mbar_arrive(&sm->empty[s]);  // this thread has taken its bytes out of the stage
-          if (++s == kTcStages) {
-            s = 0;
-            s_phase ^= 1u;
-          }
-        }
+        // The A buffer of this group is free once the MMAs of two groups ago are done,
+        // which in a kernel bound by this very loop is long past: wait first, then
+        // dequantise and store 16 registers at a time.
         const int buf = git & 1;
         const std::uint32_t use = git >> 1;
         if (use >= 1) {
@@ -565,16 +624,35 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
         tc_fence_after();
         const std::uint32_t a_addr = tile_base + buf * 64;
 #pragma unroll
-        for (int q = 0; q < 4; ++q) tmem_st16(a_addr + 16 * q, regs + 16 * q);
+        for (int q = 0; q < 4; ++q) {
+          std::uint32_t regs[16];
+          const uint4 v = lds128(rowp + (((4 * half + q) ^ (lrow & 7)) << 4));
+          dequant_word_natural(v.x, regs);
+          dequant_word_natural(v.y, regs + 4);
+          dequant_word_natural(v.z, regs + 8);
+          dequant_word_natural(v.w, regs + 12);
+          tmem_st16(a_addr + 16 * q, regs);
+        }
+        if (half == 1 || g == G - 1) {
+          mbar_arrive(&sm->empty[s]);  // this thread has taken its bytes out of the stage
+          if (++s == kTcStages) {
+            s = 0;
+            s_phase ^= 1u;
+          }
+        }
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         tc_fence_before();
         mbar_arrive(&sm->a_full[tile][buf]);
       }
     }
-  } else if (warp < kTcProducerWarp) {
+  } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 144;" ::: "memory");
     // ---------------- read the accumulators back: acc += scale * sum ----------------
     const int fw = warp - kTcFoldWarp0;
     const int tile = fw >> 2;
+    // both of the tile's accumulator buffers start out free
+    mbar_arrive(&sm->a_full[tile][0]);
+    mbar_arrive(&sm->a_full[tile][1]);
     const int lrow = (fw & 3) * 32 + lane;
     const std::uint32_t lane_base = static_cast<std::uint32_t>((fw & 3) * 32) << 16;
     const std::uint32_t tile_base = tmem_base + tile * kColsPerTile + lane_base;
@@ -583,6 +661,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
     std::uint32_t n_pairs = 0;  // pair items finished
     std::uint32_t n_res = 0;    // residual items finished
     bool alive = true;
+    int fs = 0;  // stage of the current group
     const TcDesc* L = nullptr;
     std::uint16_t* y = nullptr;
     int LN = 0, LM = 0, G = 0, item_begin = 0, mode = kTcPlain;
@@ -620,16 +699,29 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
         alive = __all_sync(0xffffffffu, ok);
         if (!alive) break;
         tc_fence_after();
-        const std::uint32_t d_addr = tile_base + 128 + buf * NTOK;
-#pragma unroll
-        for (int c = 0; c < NTOK / 16; ++c) {
-          float f[16];
-          tmem_ld16(d_addr + c * 16, f);
-#pragma unroll
-          for (int i = 0; i < 16; ++i) acc[c * 16 + i] = fmaf(sc, f[i], acc[c * 16 + i]);
+        // the group's MMAs were the last readers of its activations in the stage; a stage
+        // that holds one group only gets both of its arrivals from that group
+        if (lane == 0) {
+          mbar_arrive(&sm->empty[fs]);
+          if (g == G - 1 && (g & 1) == 0) mbar_arrive(&sm->empty[fs]);
         }
-        tc_fence_before();
-        mbar_arrive(&sm->d_free[tile][buf]);
+        if (((g & 1) || g == G - 1) && ++fs == kTcStages) fs = 0;
+        const std::uint32_t d_addr = tile_base + 128 + buf * NTOK;
+        // at most 32 columns per load (two loads for 64 rows of activations: the register
+        // budget does not hold a whole 64-column group sum beside the 64 accumulators)
+        constexpr int kCols = NTOK < 32 ? NTOK : 32;
+#pragma unroll
+        for (int c = 0; c < NTOK / kCols; ++c) {
+          std::uint32_t d[kCols];
+          tmem_ld_cols<kCols>(d_addr + c * kCols, d);
+          if (c == NTOK / kCols - 1) {
+            // the accumulator is in registers: hand the buffer back before the arithmetic
+            tc_fence_before();
+            mbar_arrive(&sm->a_full[tile][buf]);
+          }
+#pragma unroll
+          for (int i = 0; i < kCols; ++i) acc[c * kCols + i] = fmaf(sc, __uint_as_float(d[i]), acc[c * kCols + i]);
+        }
       }
       if (!alive) break;
       if (p.pick.slots != nullptr) {
@@ -750,60 +842,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       mbar_arrive(&sm->out_full[tile]);
       ++eit;
-    }
-  } else if (warp >= kTcStoreWarp) {
-    // ---------------- output stores, one lane per tile ----------------
-    if (lane < kTcTiles) {
-      const int tile = lane;
-      const TcDesc* L = nullptr;
-      int LN = 0, item_begin = 0;
-      bool direct = false, pair = false;
-      std::uint32_t n_stores = 0;  // items of this tile that went through the output buffer
-      bool ok = true;
-      for (int item = it_lo; item < it_hi && ok && !*abort_flag; ++item) {
-        if (wk.seek(item) || L == nullptr) {
-          L = tbl + wk.d;
-          LN = L->N;
-          item_begin = L->item_begin;
-          direct = L->direct_store != 0;
-          pair = L->mode == kTcPair;
-        }
-        if (direct) continue;  // the read-back threads store these rows themselves
-        const int j = item - item_begin;
-        if (pair && tile == 0) continue;  // a pair's outputs all leave through tile 1's buffer
-        const int row0 = pair ? j * kTcRowsPerTile : j * kTcItemRows + tile * kTcRowsPerTile;
-        if (EXTRA && L->mode == kTcResidual) {
-          // the buffer is free here (the previous store has read it): fetch the tile's
-          // residual values into it while the item is being computed
-          std::uint8_t* buf = outsm + tile * tc_out_bytes(NTOK);
-          if (row0 < LN) {
-            mbar_arrive_expect_tx(&sm->res_full[tile], tc_out_bytes(NTOK));
-            asm volatile(
-                "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
-                " [%0], [%1, {%2, %3}], [%4];" ::"r"(smem_u32(buf)),
-                "l"(&L->rmap), "r"(row0), "r"(0), "r"(smem_u32(&sm->res_full[tile]))
-                : "memory");
-          } else {
-            mbar_arrive_expect_tx(&sm->res_full[tile], 0);
-          }
-        }
-        if (!tc_wait(&sm->out_full[tile], n_stores & 1u, abort_flag)) {
-          ok = false;
-          break;
-        }
-        if (row0 < LN) {
-          asm volatile(
-              "cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(
-                  &L->ymap),
-              "r"(row0), "r"(0), "r"(smem_u32(outsm + tile * tc_out_bytes(NTOK)))
-              : "memory");
-          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-          asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-        }
-        mbar_arrive(&sm->out_free[tile]);
-        ++n_stores;
-      }
-      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
   }
 
