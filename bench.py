@@ -49,7 +49,7 @@ METRIC = "w4a16_gemv_hbm_gbps_m1_projection_set"
 UNIT = "GB/s"
 # dram__bytes_read.sum + dram__bytes_write.sum of one grouped launch, from an ncu
 # capture of this command with --only set (None until a capture exists)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 242_465_024
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 241_729_536
 
 
 def set_bytes(M: int = 1) -> int:
@@ -312,8 +312,11 @@ def lm_head_timings(eng, torch, dist, lins, lo, x, M, mode, steps, warmup, in_fl
     back on one stream) and pipelined throughput (`in_flight` calls under way at once, each
     on its own stream with its own workspace and exchange buffers, as a server with several
     decode steps in flight issues them; the next call's projection overlaps the previous
-    call's exchange and merge).  Returns (latency ms per call, pipelined ms per call, last
-    outputs)."""
+    call's exchange and merge) and the latency again with the calls replayed from a CUDA
+    graph (two calls per graph, one per weight copy), which takes the host's issue time out
+    of it: with the vocabulary split over eight GPUs a call is shorter than the time the
+    host needs to issue its two launches through Python.  Returns (latency ms per call,
+    pipelined ms per call, last outputs, calls in flight, graph latency ms per call)."""
     vp = dist is not None and mode is not None
     if in_flight is None:
         # With the peer exchange every activation row of a call in flight may hold a CTA that
@@ -333,6 +336,16 @@ def lm_head_timings(eng, torch, dist, lins, lo, x, M, mode, steps, warmup, in_fl
 
     lat_ms, _ = time_steps(torch, step, steps, warmup, dist, min_seconds=0.05)
     out = [t.clone() for t in res["out"]]
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step(0)
+        step(1)
+    replays = max(2, steps // 2)
+    graph_ms, _ = time_steps(torch, lambda i: graph.replay(), replays, 2, dist, min_seconds=0.05)
+    graph_ms /= replays * 2
+    if not all(torch.equal(a, b) for a, b in zip(out, res["out"])):
+        raise RuntimeError("the graph replay of the vocabulary projection picked different tokens")
+    del graph
     # pipelined: in_flight streams, each with its own head; weights alternate between the copies
     pipe = [make_head(i) for i in range(in_flight)]
     streams = [torch.cuda.Stream() for _ in range(in_flight)]
@@ -364,7 +377,7 @@ def lm_head_timings(eng, torch, dist, lins, lo, x, M, mode, steps, warmup, in_fl
     for h in heads + pipe:
         if vp:
             h.close()
-    return lat_ms / steps, best[0], out, best[1]
+    return lat_ms / steps, best[0], out, best[1], graph_ms
 
 
 def bench_lm_head(eng, torch, dist, rank, world, steps, warmup):
@@ -391,8 +404,8 @@ def bench_lm_head(eng, torch, dist, rank, world, steps, warmup):
         entry, picks = {}, {}
         for mode in list(modes):
             try:
-                lat, pipe, res, in_flight = lm_head_timings(eng, torch, dist if world > 1 else None, lins,
-                                                            lo, x, M, mode, steps, warmup)
+                lat, pipe, res, in_flight, glat = lm_head_timings(eng, torch, dist if world > 1 else None,
+                                                                  lins, lo, x, M, mode, steps, warmup)
                 failed, why = 0, ""
             except Exception as exc:  # e.g. the ranks' GPUs cannot map one another's memory
                 if mode != "peer":
@@ -404,10 +417,12 @@ def bench_lm_head(eng, torch, dist, rank, world, steps, warmup):
                 continue
             lat = max_over_ranks(torch, dist, lat)
             pipe = max_over_ranks(torch, dist, pipe)
+            glat = max_over_ranks(torch, dist, glat)
             picks[mode] = res
             if mode == modes[0]:
                 entry.update({
                     "us_per_call": lat * 1e3, "rows_per_s": M / (lat * 1e-3),
+                    "graph_us_per_call": glat * 1e3,
                     "pipelined_us_per_call": pipe * 1e3, "pipelined_rows_per_s": M / (pipe * 1e-3),
                     "calls_in_flight": in_flight, "shard_rows": hi - lo,
                     "shard_gbps": (lin.N * lin.K // 2 + lin.N * 16) / (lat * 1e-3) / 1e9,
@@ -416,6 +431,7 @@ def bench_lm_head(eng, torch, dist, rank, world, steps, warmup):
                                  else "none")})
             else:
                 entry["collective_us_per_call"] = lat * 1e3
+                entry["collective_graph_us_per_call"] = glat * 1e3
                 entry["collective_pipelined_us_per_call"] = pipe * 1e3
                 same = all(torch.equal(a, b) for a, b in zip(picks[modes[0]], picks[mode]))
                 if not same:
@@ -423,17 +439,20 @@ def bench_lm_head(eng, torch, dist, rank, world, steps, warmup):
                 entry["same_pick_as_collective"] = True
         if world > 1:
             # the whole vocabulary on rank 0's GPU alone, inside this run
-            one = torch.zeros(3, device="cuda", dtype=torch.float64)
+            one = torch.zeros(4, device="cuda", dtype=torch.float64)
             if rank == 0:
-                lat1, pipe1, res1, _ = lm_head_timings(eng, torch, None, full, 0, x, M, None, steps, warmup,
-                                                       in_flight=entry.get("calls_in_flight"))
-                one = torch.tensor([lat1, pipe1, float(res1[0][0].item())], device="cuda", dtype=torch.float64)
+                lat1, pipe1, res1, _, glat1 = lm_head_timings(eng, torch, None, full, 0, x, M, None, steps,
+                                                              warmup, in_flight=entry.get("calls_in_flight"))
+                one = torch.tensor([lat1, pipe1, float(res1[0][0].item()), glat1], device="cuda",
+                                   dtype=torch.float64)
             dist.broadcast(one, 0)
-            lat1, pipe1, arg1 = (float(v) for v in one.tolist())
+            lat1, pipe1, arg1, glat1 = (float(v) for v in one.tolist())
             entry["one_gpu_us_per_call"] = lat1 * 1e3
             entry["one_gpu_pipelined_us_per_call"] = pipe1 * 1e3
+            entry["one_gpu_graph_us_per_call"] = glat1 * 1e3
             entry["efficiency_vs_1gpu"] = {"latency": lat1 / (entry["us_per_call"] * 1e-3) / world,
-                                           "pipelined": pipe1 / (entry["pipelined_us_per_call"] * 1e-3) / world}
+                                           "pipelined": pipe1 / (entry["pipelined_us_per_call"] * 1e-3) / world,
+                                           "graph_latency": glat1 / (entry["graph_us_per_call"] * 1e-3) / world}
             if int(arg1) != entry["argmax_row0"]:
                 raise RuntimeError("the vocabulary-parallel argmax differs from the single-GPU one")
             entry["same_argmax_as_one_gpu"] = True
