@@ -332,8 +332,14 @@ def test_topk_merge_equals_host_merge(eng, orc):
     assert np.array_equal(from_dev(argmax), h_arg.numpy())
 
 
-def test_lm_head_full_vocabulary_argmax(eng, orc):
-    # the benchmark's vocabulary configuration: K=1024 -> N=248320, M=1 and M=32, RMS-normalised x
+def test_lm_head_full_vocabulary_argmax(eng, orc, record_property):
+    """The benchmark's vocabulary configuration: K=1024 -> N=248320, M=1 and M=32,
+    RMS-normalised x.  The argmax must be the CPU reference's on every row.  The top-50
+    list is held to the ordering rule on the device's own logits; how far it is from the
+    rule applied to the CPU's logits (two fp32 sums in different orders may round to
+    neighbouring bf16 values, which can swap neighbours in the list or move the 50th entry)
+    is counted and reported: ids of the device list that the CPU list does not hold, and
+    positions that hold another id."""
     import torch
     N, K = 248320, 1024
     threads = orc.lib().orc_max_threads()
@@ -348,8 +354,19 @@ def test_lm_head_full_vocabulary_argmax(eng, orc):
         logits = from_dev(head.logits[:M])
         check_close(orc, logits, want, f"full vocab M={M}")
         _check_pick(orc, logits, from_dev(argmax), from_dev(idx), from_dev(val), 50)
+        dev_idx = from_dev(idx)
+        other_ids = other_pos = 0
         for m in range(M):
             assert from_dev(argmax)[m] == orc.argmax_bf16(want[m]), f"M={M} row {m}"
+            cpu_ids, _ = orc.topk_bf16(want[m], 50)
+            other_ids += len(set(dev_idx[m].tolist()) - set(cpu_ids.tolist()))
+            other_pos += int((dev_idx[m] != cpu_ids).sum())
+        print(f"lm_head M={M}: {other_ids} of {50 * M} top-50 ids are not in the CPU rule's list on "
+              f"CPU logits; {other_pos} of {50 * M} positions hold another id")
+        record_property(f"top50_ids_not_in_cpu_list_M{M}", other_ids)
+        record_property(f"top50_positions_differing_M{M}", other_pos)
+        # a few entries around the 50th value per row at most: anything more is a defect
+        assert other_ids <= 2 * M, (M, other_ids)
 
 
 def test_second_opinion_reference_cuda_kernel(eng, orc):
