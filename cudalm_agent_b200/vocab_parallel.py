@@ -102,7 +102,12 @@ class PeerExchange:
     """This rank's exchange buffer and its peers' buffers mapped over CUDA IPC, for
     ``cudalm_b200_topk_exchange_merge``: the candidate lists cross NVLink as plain
     stores from the kernel that also merges them, with no collective launch.  All
-    ranks of ``group`` must sit on one node, each on its own GPU."""
+    ranks of ``group`` must sit on one node, each on its own GPU.
+
+    The device-side wait for the peers is bounded (``set_exchange_timeout_ns``).  When it
+    runs out, ``device_status()`` reads 5 and the affected rows come back as id -1 and
+    value -inf.  After that the ranks' epochs no longer agree: ``close()`` this object
+    on every rank and build a new one before the next call."""
 
     def __init__(self, words_per_list: int, rows_cap: int, top_k: int,
                  group: Optional[dist.ProcessGroup] = None):
