@@ -119,7 +119,7 @@ bool make_plan(int kmax, int mmax, Plan* out, bool several = false) {
   // at least 4 KB: the region doubles as reduction scratch at the kernel's end
   // activations, + the all-zero row, + the per-group offset sums [K/128][8*nt]
   // ... + the out-of-range flag word in the buffer's last bytes
-  int x_bytes = round_up((mmax + 1) * (2 * kmax + 32) + (kmax / 128) * nt * 8 * 4, 128) + kXFlagBytes;
+  int x_bytes = round_up((mmax + 1) * (2 * kmax + kXRowPad) + (kmax / 128) * nt * 8 * 4, 128) + kXFlagBytes;
   if (x_bytes < 4096) x_bytes = 4096;
 #ifdef CB200_WARPS
   for (int nwarps : {CB200_WARPS}) {

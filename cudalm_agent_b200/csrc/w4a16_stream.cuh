@@ -326,23 +326,25 @@ __device__ __forceinline__ bool wait_stage(std::uint64_t* bar, std::uint32_t par
 #define CB200_X_SCALE_EVEN 0x1p64f
 #define CB200_X_SCALE_ODD 0x1p60f
 #define CB200_OUT_SCALE 0x1p69f
+constexpr int kXRowPad = 64;  // bytes between the end of one activation row and the next
 
 // Activation layout in shared memory for the MMA fragments: row n at stride
-// rsx = 2K + 32 bytes; inside a row the values are permuted so that the four
-// values a lane needs for one MMA are 8 contiguous bytes:
+// rsx = 2K + 64 bytes (kXRowPad: rows alternate between the two halves of the banks);
+// inside a row the values are permuted so that the eight values a lane needs for the
+// two MMAs of one weight word are 16 contiguous bytes, one load:
 //   k = 128 g + 32 t + 8 w + i   (t = lane & 3, w = word of the lane's 16 weight
-//   bytes, i = nibble in the word) goes to slot ((g*8 + j)*4 + t)*4 + e with
-//   j = 2w + ((i & 3) >> 1), e = 2*(i & 1) + (i >> 2).
+//   bytes, i = nibble in the word) goes to slot (((g*4 + w)*4 + t)*2 + h)*4 + e with
+//   h = (i & 3) >> 1 (the MMA j = 2w + h), e = 2*(i & 1) + (i >> 2).
 // Values are stored times 2^64 (even i) or 2^60 (odd i); both are exact in bf16
 // for |x| < 2^63.  Row M (one past the real rows) is all zeros: MMA columns
 // beyond M read it, so the fragment loads need no predicate.
 __device__ __forceinline__ void store_x_value(std::uint8_t* xs, int rsx, int n, int k,
                                               std::uint16_t bits) {
   const int g = k >> 7, r = k & 127, t = r >> 5, q = r & 31, w = q >> 3, i = q & 7;
-  const int j = 2 * w + ((i & 3) >> 1);
+  const int h = (i & 3) >> 1;
   const int e = 2 * (i & 1) + (i >> 2);
   const float f = bf16_bits_to_float(bits) * ((i & 1) ? CB200_X_SCALE_ODD : CB200_X_SCALE_EVEN);
-  *reinterpret_cast<std::uint16_t*>(xs + n * rsx + ((((g * 8 + j) * 4 + t) * 4 + e) * 2)) =
+  *reinterpret_cast<std::uint16_t*>(xs + n * rsx + ((((((g * 4 + w) * 4 + t) * 2 + h) * 4) + e) * 2)) =
       float_to_bf16_bits(f);
 }
 
@@ -505,7 +507,7 @@ __device__ __forceinline__ void build_bias(const std::uint8_t* xs, float* bias, 
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
     const int n = nt * 8 + r8;
-    xrow[nt] = xs + (n < M ? n : M) * rsx + t * 8;
+    xrow[nt] = xs + (n < M ? n : M) * rsx + t * 16;
   }
   for (int g = warp; g < G; g += nwarps) {
     constexpr int kC = chains_per_group(NT);
@@ -518,14 +520,10 @@ __device__ __forceinline__ void build_bias(const std::uint8_t* xs, float* bias, 
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int j = 2 * w + h;
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          const uint2 b = lds64(xrow[nt] + g * 256 + j * 32);
-          mma_m16n8k16_bf16(part[nt][chain_of(kC, w, h)], kBiasEven, kBiasEven, kBiasOdd, kBiasOdd,
-                            b.x, b.y);
-        }
+      for (int nt = 0; nt < NT; ++nt) {
+        const uint4 b = lds128(xrow[nt] + g * 256 + w * 64);
+        mma_m16n8k16_bf16(part[nt][chain_of(kC, w, 0)], kBiasEven, kBiasEven, kBiasOdd, kBiasOdd, b.x, b.y);
+        mma_m16n8k16_bf16(part[nt][chain_of(kC, w, 1)], kBiasEven, kBiasEven, kBiasOdd, kBiasOdd, b.z, b.w);
       }
     }
     if (r8 == 0) {
@@ -555,12 +553,14 @@ __device__ __forceinline__ void consume_chunk(const std::uint8_t* stage, const s
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
     const int n = nt * 8 + r8;
-    xrow[nt] = xs + (n < M ? n : M) * rsx + g0 * 256 + t * 8;
+    xrow[nt] = xs + (n < M ? n : M) * rsx + g0 * 256 + t * 16;
   }
   const float* brow = bias + g0 * (NT * 8) + 2 * t;
   auto one_group = [&](int g) {
     const uint4 qa = lds128(wa + g * 64);
     const uint4 qb = lds128(wb + g * 64);
+    // (one 8-byte load for four groups' scales was measured slower: the sixteen values
+    // that then live across the unrolled groups cost more than the loads they save)
     const float s_lo = __half2float(__ushort_as_half(lds16(sa + 2 * g)));
     const float s_hi = __half2float(__ushort_as_half(lds16(sb + 2 * g)));
     const std::uint32_t wordA[4] = {qa.x, qa.y, qa.z, qa.w};
@@ -579,14 +579,10 @@ __device__ __forceinline__ void consume_chunk(const std::uint8_t* stage, const s
       dequant_word(wordA[w], A);
       dequant_word(wordB[w], B);
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int j = 2 * w + h;
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          const uint2 b = lds64(xrow[nt] + g * 256 + j * 32);
-          mma_m16n8k16_bf16(part[nt][chain_of(kC, w, h)], A[2 * h], B[2 * h], A[2 * h + 1],
-                            B[2 * h + 1], b.x, b.y);
-        }
+      for (int nt = 0; nt < NT; ++nt) {
+        const uint4 b = lds128(xrow[nt] + g * 256 + w * 64);
+        mma_m16n8k16_bf16(part[nt][chain_of(kC, w, 0)], A[0], B[0], A[1], B[1], b.x, b.y);
+        mma_m16n8k16_bf16(part[nt][chain_of(kC, w, 1)], A[2], B[2], A[3], B[3], b.z, b.w);
       }
     }
 #pragma unroll
@@ -604,7 +600,18 @@ __device__ __forceinline__ void consume_chunk(const std::uint8_t* stage, const s
 #pragma unroll kUnroll
     for (int g = 0; g < CG; ++g) one_group(g);
   } else {
-    for (int g = 0; g < cg; ++g) one_group(g);
+    // a partial chunk (K = 3584: the last four of 28 groups): four groups at a time, so
+    // that their loads and MMAs overlap as in a full chunk
+    int g = 0;
+    if (NT <= 2) {
+      for (; g + 4 <= cg; g += 4) {
+        one_group(g);
+        one_group(g + 1);
+        one_group(g + 2);
+        one_group(g + 3);
+      }
+    }
+    for (; g < cg; ++g) one_group(g);
   }
 }
 
@@ -683,7 +690,7 @@ __device__ __forceinline__ bool service_fill(const DescSource& ds, CtaControl* c
     if (!mbar_try_wait(bar, static_cast<std::uint32_t>(e - d_first - 1) & 1u)) return false;
     const DescLite L = get_desc(ds, e);
     const int LK = L.K, LM = L.M, G = LK >> 7;
-    const int rsx = 2 * LK + 32;
+    const int rsx = 2 * LK + kXRowPad;
     std::uint8_t* xb = x_buffer(xs0, ds.p->x_bytes, e & 1);
     const bool staged = (reinterpret_cast<std::uintptr_t>(L.x) & 15u) == 0;
     bool bad = false;
@@ -967,7 +974,7 @@ w4a16_stream_kernel(const __grid_constant__ StreamParams p) {
     const DescLite L = get_desc(ds, d);
     if (L.mt_begin >= mt_hi) break;
     const int LN = L.N, LK = L.K, LM = L.M;
-    const int rsx = 2 * LK + 32;
+    const int rsx = 2 * LK + kXRowPad;
     const int G = LK >> 7;
     std::uint16_t* y = L.y;
     std::uint8_t* xs;
