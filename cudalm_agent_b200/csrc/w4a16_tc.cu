@@ -34,6 +34,7 @@
 
 #include <cstring>
 #include <mutex>
+#include <utility>
 #include <vector>
 
 #include "common.cuh"
@@ -84,8 +85,16 @@ struct alignas(64) TcDesc {
   const std::uint16_t* res;  // mode kTcResidual: residual [M][N]
   std::uint16_t* y;
   int N, K, M;
-  int item_begin;   // first item of this projection in the launch
+  int item_begin;   // first unit of this projection in the launch (a unit: one K-slice of one item)
   int cost_begin;   // stage loads before this projection
+  // Split K: an item's stages are cut into `split` slices of `slice_stages` stages (the
+  // last one may be shorter), each a unit of its own, so that projections with few items
+  // still occupy every SM.  The units leave their fp32 sums in `partial`
+  // ([item][slice][tile][NTOK][row]); a small follow-up kernel adds the slices up in
+  // slice order, applies the residual and stores the outputs (tc_split_combine_kernel).
+  int split;
+  int slice_stages;
+  float* partial;
   int direct_store;  // outputs cannot take the TMA store (base or row pitch off 16 bytes)
   // kTcPlain; kTcPair: out = silu(gate x) * (up x): an item is 128 rows, tile 0 works
   // on the gate matrix and tile 1 on the same rows of the up matrix;
@@ -93,9 +102,25 @@ struct alignas(64) TcDesc {
   int mode;
 };
 enum : int { kTcPlain = 0, kTcPair = 1, kTcResidual = 2 };
+// units of a projection: its items times its K-slices
 __host__ __device__ inline int tc_desc_items(const TcDesc& d) {
-  return d.mode == kTcPair ? (d.N + kTcRowsPerTile - 1) / kTcRowsPerTile
-                           : (d.N + kTcItemRows - 1) / kTcItemRows;
+  return (d.mode == kTcPair ? (d.N + kTcRowsPerTile - 1) / kTcRowsPerTile
+                            : (d.N + kTcItemRows - 1) / kTcItemRows) * d.split;
+}
+// Unit `uu` of projection d: its item, its slice, the first group and the number of groups.
+struct TcUnit {
+  int j, slice, g_lo, groups;
+};
+__device__ __forceinline__ TcUnit tc_unit(const TcDesc& d, int uu) {
+  TcUnit u;
+  u.j = uu / d.split;
+  u.slice = uu - u.j * d.split;
+  const int G = d.K >> 7;
+  u.g_lo = 2 * u.slice * d.slice_stages;
+  int g_hi = u.g_lo + 2 * d.slice_stages;
+  if (g_hi > G) g_hi = G;
+  u.groups = g_hi - u.g_lo;
+  return u;
 }
 
 struct TcParams {
@@ -420,7 +445,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
         const int mid = (lo + hi + 1) >> 1;
         if (tbl[mid].cost_begin <= cost) lo = mid; else hi = mid - 1;
       }
-      const int per_item = ((tbl[lo].K >> 7) + 1) >> 1;
+      const int per_item = tbl[lo].slice_stages;
       return tbl[lo].item_begin + static_cast<int>((cost - tbl[lo].cost_begin + per_item - 1) / per_item);
     };
     it_lo = item_at(static_cast<long long>(blockIdx.x) * p.total_cost / gridDim.x);
@@ -450,7 +475,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
         const std::uint64_t policy = policy_evict_first();
         bool ok = true;
         const TcDesc* L = nullptr;
-        int G = 0, item_begin = 0;
+        int item_begin = 0;
         bool pair = false;
         int ps = 0;                  // stage to fill next
         std::uint32_t ps_phase = 0;  // phase its `full` barrier completes next
@@ -458,16 +483,16 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
         for (int item = it_lo; item < it_hi && ok && !*abort_flag; ++item) {
           if (wk.seek(item) || L == nullptr) {
             L = tbl + wk.d;
-            G = L->K >> 7;
             item_begin = L->item_begin;
             pair = L->mode == kTcPair;
           }
-          const int j = item - item_begin;
+          const TcUnit u = tc_unit(*L, item - item_begin);
+          const int j = u.j;
           // plain: tiles are consecutive 128-row blocks of one matrix; pair: the same
           // 128 rows of the gate (tile 0) and up (tile 1) matrices
           const int row0 = pair ? j * kTcRowsPerTile : j * kTcItemRows;
           const int tile_step = pair ? 0 : kTcRowsPerTile;
-          for (int c = 0; c < (G + 1) / 2; ++c) {
+          for (int c = u.g_lo >> 1; c < (u.g_lo + u.groups + 1) >> 1; ++c) {
             // second and later uses of a stage wait until its previous content is done with
             if (ps_round && !tc_wait(&sm->empty[ps], ps_phase ^ 1u, abort_flag)) {
               ok = false;
@@ -514,10 +539,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
         std::uint64_t* const a_full = &sm->a_full[t][buf];
         std::uint64_t* const mma_done = &sm->mma_done[t][buf];
         bool ok = true;
-        int G = 0;
         int s = 0;  // stage of the current group
         for (int item = it_lo; item < it_hi && ok && !*abort_flag; ++item) {
-          if (wk.seek(item) || G == 0) G = tbl[wk.d].K >> 7;
+          (void)wk.seek(item);
+          const int G = tc_unit(tbl[wk.d], item - tbl[wk.d].item_begin).groups;
           for (int g = 0; g < G; ++g, ++git) {
             if ((git & 1u) == buf) {
               const std::uint32_t b_addr = stage0 + s * kStageBytes + (g & 1) * 2 * kBoxBytes;
@@ -549,7 +574,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
             L = tbl + wk.d;
             LN = L->N;
             item_begin = L->item_begin;
-            direct = L->direct_store != 0;
+            // (also the outputs of a projection whose K is split: whichever unit ends last
+            // stores them)
+            direct = L->direct_store != 0 || L->split > 1;
             pair = L->mode == kTcPair;
           }
           if (direct) continue;  // the read-back threads store these rows themselves
@@ -598,11 +625,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
     const std::uint32_t lane_base = static_cast<std::uint32_t>((warp & 3) * 32) << 16;
     const std::uint32_t tile_base = tmem_base + tile * kColsPerTile + lane_base;
     bool alive = true;
-    int G = 0;
     int s = 0;                  // stage of the current group
     std::uint32_t s_phase = 0;  // phase of its `full` barrier
     for (int item = it_lo; item < it_hi && alive; ++item) {
-      if (wk.seek(item) || G == 0) G = tbl[wk.d].K >> 7;
+      (void)wk.seek(item);
+      const int G = tc_unit(tbl[wk.d], item - tbl[wk.d].item_begin).groups;
       for (int g = 0; g < G && alive; ++g, ++git) {
         const int half = g & 1;
         if (half == 0) {
@@ -664,7 +691,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
     int fs = 0;  // stage of the current group
     const TcDesc* L = nullptr;
     std::uint16_t* y = nullptr;
-    int LN = 0, LM = 0, G = 0, item_begin = 0, mode = kTcPlain;
+    int LN = 0, LM = 0, GK = 0, item_begin = 0, mode = kTcPlain, split = 1;
     bool direct = false;
     for (int item = it_lo; item < it_hi && alive; ++item) {
       if (wk.seek(item) || L == nullptr) {
@@ -672,12 +699,15 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
         y = L->y;
         LN = L->N;
         LM = L->M;
-        G = L->K >> 7;
+        GK = L->K >> 7;
         item_begin = L->item_begin;
-        direct = L->direct_store != 0;
+        split = L->split;
+        direct = L->direct_store != 0 || split > 1;
         mode = L->mode;
       }
-      const int j = item - item_begin;
+      const TcUnit u = tc_unit(*L, item - item_begin);
+      const int j = u.j;
+      const int G = u.groups;
       const bool pair = EXTRA && mode == kTcPair;
       const bool second = pair && tile == 1;         // this tile works on the up matrix
       const bool first_of_pair = pair && tile == 0;  // this tile works on the gate matrix
@@ -685,7 +715,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
       const int row0 = pair ? j * kTcRowsPerTile : j * kTcItemRows + tile * kTcRowsPerTile;
       const int row = row0 + lrow;
       const bool row_ok = row < LN;
-      const std::uint16_t* srow = S + static_cast<std::size_t>(row_ok ? row : 0) * G;
+      const std::uint16_t* srow = S + static_cast<std::size_t>(row_ok ? row : 0) * GK + u.g_lo;
       float acc[NTOK];
 #pragma unroll
       for (int n = 0; n < NTOK; ++n) acc[n] = 0.f;
@@ -764,6 +794,15 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
           const int n = 2 * word + copy;
           if (n < LM) atomicMax(&sm->row_max[n], bf16_key(copy ? (kv[0] >> 16) : (kv[0] & 0xFFFFu)));
         }
+      }
+      if (split > 1) {
+        // this unit's sums go to the item's scratch ([activation row][weight row]: a warp's
+        // store is 128 contiguous bytes); the follow-up kernel adds the slices up
+        float* part = L->partial +
+                      ((static_cast<std::size_t>(j) * split + u.slice) * kTcTiles + tile) * kTcRowsPerTile * NTOK + lrow;
+#pragma unroll
+        for (int n = 0; n < NTOK; ++n) __stcg(part + n * kTcRowsPerTile, acc[n]);
+        continue;
       }
       if (direct) {
         // outputs the TMA unit cannot address: plain stores, one row per thread
@@ -859,6 +898,42 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
   if (*abort_flag && tid == 0) atomicExch(p.status, CUDALM_B200_ERR_TIMEOUT);
   tc_fence_after();
   if (warp == 0) tmem_dealloc(tmem_base, 512);
+}
+
+// Outputs of the projections whose K was split: blockIdx.z is the projection, blockIdx.x
+// its 128-row tile, one thread per weight row, blockIdx.y strides over the activation
+// rows.  The slices are added in slice order, so the result does not depend on how the
+// units were spread over the CTAs.
+__global__ void __launch_bounds__(kTcRowsPerTile)
+tc_split_combine_kernel(const __grid_constant__ TcParams p, int ntok) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const TcDesc& L = (p.table ? p.table : p.inl)[blockIdx.z];
+  if (L.split <= 1) return;
+  const int t = blockIdx.x;
+  const int lrow = threadIdx.x;
+  const int row = t * kTcRowsPerTile + lrow;
+  if (row >= L.N) return;
+  const bool pair = L.mode == kTcPair;  // an item is one tile of rows: tile 0 gate, tile 1 up
+  const int j = pair ? t : t / kTcTiles, tile = pair ? 0 : t - j * kTcTiles;
+  const std::size_t slice_floats = static_cast<std::size_t>(kTcTiles) * kTcRowsPerTile * ntok;
+  const float* p0 = L.partial + (static_cast<std::size_t>(j) * L.split * kTcTiles + tile) * kTcRowsPerTile * ntok + lrow;
+  for (int n = blockIdx.y; n < L.M; n += gridDim.y) {
+    float a = 0.f;
+    for (int sl = 0; sl < L.split; ++sl) a += __ldcg(p0 + sl * slice_floats + n * kTcRowsPerTile);
+    const std::size_t at = static_cast<std::size_t>(n) * L.N + row;
+    std::uint16_t bits = float_to_bf16_bits(a);
+    if (pair) {
+      // CUDALM's rounding order: bf16 after each projection, after silu, after the product
+      float b = 0.f;
+      const float* p1 = p0 + static_cast<std::size_t>(kTcRowsPerTile) * ntok;
+      for (int sl = 0; sl < L.split; ++sl) b += __ldcg(p1 + sl * slice_floats + n * kTcRowsPerTile);
+      bits = float_to_bf16_bits(bf16_bits_to_float(silu_bits(bits)) * bf16_bits_to_float(float_to_bf16_bits(b)));
+    } else if (L.mode == kTcResidual) {
+      bits = add_bits(L.res[at], bits);
+    }
+    L.y[at] = bits;
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -1001,15 +1076,34 @@ bool tc_eligible(const cudalm_b200_linear& l) {
   return aligned_to(l.weight, 16) && aligned_to(l.x, 16);
 }
 
+// Scratch of the projections whose K is split (TcDesc::partial, ::tickets).
+struct TcScratchPlan {
+  size_t bytes = 0;  // the partial sums of every split projection
+  int tiles = 0;     // most 128-row tiles of any split projection: the combine kernel's grid.x
+};
+
 // Fills `out[count]` and the launch totals; UNSUPPORTED when a projection does
-// not meet the kernel's alignment rules.
+// not meet the kernel's alignment rules.  `pair`: the one projection is a gate/up pair
+// (the caller adds the second matrix).  With `scratch` non-null, a launch with few
+// 128-row tiles (at most one per SM: the length of one item's chain of groups, not the
+// bytes, then sets the time) has the K of its projections from K = 2048 on split into
+// slices of two stages (four groups), and `scratch` receives the size of the memory the
+// caller has to provide through tc_bind_scratch; with `scratch` null nothing is split.
+// Launches with more tiles are not split: measured on 96 items of 28 groups, the extra
+// traffic and the per-unit costs outweigh the shorter chains (29 -> 37 us).
 int tc_describe(const cudalm_b200_linear* ls, int count, TcDesc* out, int* items_out,
-                int* cost_out, int* ntok_out) {
+                int* cost_out, int* ntok_out, TcScratchPlan* scratch = nullptr, bool pair = false) {
   int items = 0, cost = 0, ntok = 0;
+  long long tiles = 0;
   for (int i = 0; i < count; ++i) {
     if (!tc_eligible(ls[i])) return CUDALM_B200_ERR_UNSUPPORTED;
     ntok = tc_ntok(ls[i].M) > ntok ? tc_ntok(ls[i].M) : ntok;
+    tiles += pair ? 2ll * ((ls[i].N + kTcRowsPerTile - 1) / kTcRowsPerTile)
+                  : static_cast<long long>(kTcTiles) * ((ls[i].N + kTcItemRows - 1) / kTcItemRows);
   }
+  const bool few_tiles = scratch != nullptr && tiles <= num_sms();
+  size_t partial_floats = 0;
+  int split_tiles = 0;
   for (int i = 0; i < count; ++i) {
     const cudalm_b200_linear& l = ls[i];
     TcDesc& d = out[i];
@@ -1021,22 +1115,116 @@ int tc_describe(const cudalm_b200_linear* ls, int count, TcDesc* out, int* items
     d.S = l.scales;
     d.S2 = nullptr;
     d.res = nullptr;
-    d.mode = kTcPlain;
+    d.mode = pair ? kTcPair : kTcPlain;
     d.y = l.y;
     d.N = l.N;
     d.K = l.K;
     d.M = l.M;
     d.item_begin = items;
     d.cost_begin = cost;
-    const int n_items = (l.N + kTcItemRows - 1) / kTcItemRows;
-    items += n_items;
-    cost += n_items * (((l.K >> 7) + 1) >> 1);
+    const int n_items = pair ? (l.N + kTcRowsPerTile - 1) / kTcRowsPerTile : (l.N + kTcItemRows - 1) / kTcItemRows;
+    const int stages = ((l.K >> 7) + 1) >> 1;
+    const int split = (few_tiles && stages >= 8) ? stages / 2 : 1;
+    d.slice_stages = (stages + split - 1) / split;
+    d.split = (stages + d.slice_stages - 1) / d.slice_stages;  // no empty slice
+    d.partial = nullptr;
+    if (d.split > 1) {
+      const int out_tiles = pair ? n_items : n_items * kTcTiles;
+      if (out_tiles > split_tiles) split_tiles = out_tiles;
+      partial_floats += static_cast<size_t>(n_items) * d.split * kTcItemRows * ntok;
+    }
+    items += n_items * d.split;
+    cost += n_items * d.split * d.slice_stages;
+  }
+  if (scratch) {
+    scratch->bytes = partial_floats * sizeof(float);
+    scratch->tiles = split_tiles;
   }
   *items_out = items;
   *cost_out = cost;
   *ntok_out = ntok;
   return CUDALM_B200_OK;
 }
+
+// Points the split projections of `tbl` into `mem` (TcScratchPlan::bytes, 256-byte aligned).
+void tc_bind_scratch(TcDesc* tbl, int count, int ntok, void* mem) {
+  float* partial = static_cast<float*>(mem);
+  for (int i = 0; i < count; ++i) {
+    TcDesc& d = tbl[i];
+    if (d.split <= 1) continue;
+    const int n_items = tc_desc_items(d) / d.split;
+    d.partial = partial;
+    partial += static_cast<size_t>(n_items) * d.split * kTcItemRows * ntok;
+  }
+}
+
+// The follow-up launch of a launch with split projections.
+int tc_launch_combine(const TcParams& p, int ntok, int tiles, cudaStream_t stream) {
+  if (tiles <= 0) return CUDALM_B200_OK;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(tiles), 16u, static_cast<unsigned>(p.n_desc));
+  cfg.blockDim = dim3(kTcRowsPerTile);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t le = cudaLaunchKernelEx(&cfg, tc_split_combine_kernel, p, ntok);
+  if (le != cudaSuccess) {
+    g_last_cuda_error = static_cast<int>(le);
+    (void)cudaGetLastError();
+    return CUDALM_B200_ERR_CUDA;
+  }
+  return check_launch();
+}
+
+// The library's own memory pool of a device for the stream-ordered scratch below (its
+// release threshold is unlimited, so that a decode loop's allocations are served from
+// memory the pool already holds; the device's default pool is left alone).
+cudaMemPool_t tc_scratch_pool() {
+  static std::mutex mu;
+  static std::vector<std::pair<int, cudaMemPool_t>> pools;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+  std::lock_guard<std::mutex> lk(mu);
+  for (const auto& e : pools)
+    if (e.first == dev) return e.second;
+  cudaMemPoolProps props = {};
+  props.allocType = cudaMemAllocationTypePinned;
+  props.handleTypes = cudaMemHandleTypeNone;
+  props.location.type = cudaMemLocationTypeDevice;
+  props.location.id = dev;
+  cudaMemPool_t pool = nullptr;
+  if (cudaMemPoolCreate(&pool, &props) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return nullptr;
+  }
+  unsigned long long keep = ~0ull;
+  (void)cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+  pools.emplace_back(dev, pool);
+  return pool;
+}
+
+// Stream-ordered scratch for one launch: allocated before it, freed after it.
+struct TcCallScratch {
+  void* mem = nullptr;
+  cudaStream_t stream = nullptr;
+  int acquire(const TcScratchPlan& plan, cudaStream_t st) {
+    stream = st;
+    if (plan.bytes == 0) return CUDALM_B200_OK;
+    cudaMemPool_t pool = tc_scratch_pool();
+    if (pool) {
+      CB200_CUDA_TRY(cudaMallocFromPoolAsync(&mem, plan.bytes, pool, st));
+    } else {
+      CB200_CUDA_TRY(cudaMallocAsync(&mem, plan.bytes, st));
+    }
+    return CUDALM_B200_OK;
+  }
+  ~TcCallScratch() {
+    if (mem) (void)cudaFreeAsync(mem, stream);
+  }
+};
 
 int tc_run_params(TcParams& p, int ntok, cudaStream_t stream, int* grid_out = nullptr, int max_grid = 0) {
   p.status = device_status_word();
@@ -1054,16 +1242,18 @@ int run_tc_extra(const cudalm_b200_linear& l, const std::uint8_t* weight2,
   TcParams p;
   std::memset(&p, 0, sizeof(p));
   int ntok = 0;
-  if (int rc = tc_describe(&l, 1, p.inl, &p.total_items, &p.total_cost, &ntok)) return rc;
+  TcScratchPlan plan;
+  if (weight2 && (!aligned_to(weight2, 16) || !scales2)) return CUDALM_B200_ERR_UNSUPPORTED;
+  if (int rc = tc_describe(&l, 1, p.inl, &p.total_items, &p.total_cost, &ntok, &plan, weight2 != nullptr))
+    return rc;
   TcDesc& d = p.inl[0];
   if (d.direct_store) return CUDALM_B200_ERR_UNSUPPORTED;
+  TcCallScratch scratch;
+  if (int rc = scratch.acquire(plan, stream)) return rc;
+  if (scratch.mem) tc_bind_scratch(p.inl, 1, ntok, scratch.mem);
   if (weight2) {
-    if (!aligned_to(weight2, 16) || !scales2) return CUDALM_B200_ERR_UNSUPPORTED;
     if (int rc = tc_encode(weight2, l.K / 8, l.N, 32, kTcRowsPerTile, 0, &d.tmap2)) return rc;
     d.S2 = scales2;
-    d.mode = kTcPair;
-    p.total_items = tc_desc_items(d);
-    p.total_cost = p.total_items * (((l.K >> 7) + 1) >> 1);
   } else if (residual) {
     if (!aligned_to(residual, 16)) return CUDALM_B200_ERR_UNSUPPORTED;
     if (int rc = tc_encode(residual, l.N, l.M, kTcRowsPerTile, ntok, 2, &d.rmap)) return rc;
@@ -1073,9 +1263,11 @@ int run_tc_extra(const cudalm_b200_linear& l, const std::uint8_t* weight2,
   p.n_desc = 1;
   p.status = device_status_word();
   if (!p.status) return CUDALM_B200_ERR_CUDA;
-  if (ntok == 16) return tc_launch<16, true>(p, stream);
-  if (ntok == 32) return tc_launch<32, true>(p, stream);
-  return tc_launch<64, true>(p, stream);
+  const int rc = ntok == 16   ? tc_launch<16, true>(p, stream)
+                 : ntok == 32 ? tc_launch<32, true>(p, stream)
+                              : tc_launch<64, true>(p, stream);
+  if (rc != CUDALM_B200_OK) return rc;
+  return tc_launch_combine(p, ntok, plan.tiles, stream);
 }
 
 // The vocabulary projection: one projection whose CTAs also collect the candidates of
@@ -1096,31 +1288,45 @@ int run_tc(const cudalm_b200_linear* ls, int count, cudaStream_t stream) {
   TcParams p;
   std::memset(&p, 0, sizeof(p));
   int ntok = 0;
-  if (int rc = tc_describe(ls, count, p.inl, &p.total_items, &p.total_cost, &ntok)) return rc;
+  TcScratchPlan plan;
+  if (int rc = tc_describe(ls, count, p.inl, &p.total_items, &p.total_cost, &ntok, &plan)) return rc;
+  TcCallScratch scratch;
+  if (int rc = scratch.acquire(plan, stream)) return rc;
+  if (scratch.mem) tc_bind_scratch(p.inl, count, ntok, scratch.mem);
   p.n_desc = count;
-  return tc_run_params(p, ntok, stream);
+  if (int rc = tc_run_params(p, ntok, stream)) return rc;
+  return tc_launch_combine(p, ntok, plan.tiles, stream);
 }
 
 // Any number of projections: the descriptor table lives on the device.
 struct TcGroup {
   TcDesc* table_dev = nullptr;
-  int count = 0, items = 0, cost = 0, ntok = 0;
+  void* scratch = nullptr;  // of the projections whose K is split; the group's for its lifetime
+  int count = 0, items = 0, cost = 0, ntok = 0, split_tiles = 0;
 };
 
 int tc_group_create(const cudalm_b200_linear* ls, int count, TcGroup** out) {
   std::vector<TcDesc> tbl(static_cast<size_t>(count));
   TcGroup* g = new TcGroup();
   g->count = count;
-  if (int rc = tc_describe(ls, count, tbl.data(), &g->items, &g->cost, &g->ntok)) {
+  TcScratchPlan plan;
+  if (int rc = tc_describe(ls, count, tbl.data(), &g->items, &g->cost, &g->ntok, &plan)) {
     delete g;
     return rc;
   }
-  cudaError_t e = cudaMalloc(&g->table_dev, sizeof(TcDesc) * tbl.size());
+  cudaError_t e = cudaSuccess;
+  if (plan.bytes) {
+    e = cudaMalloc(&g->scratch, plan.bytes);
+    if (e == cudaSuccess) tc_bind_scratch(tbl.data(), count, g->ntok, g->scratch);
+    g->split_tiles = plan.tiles;
+  }
+  if (e == cudaSuccess) e = cudaMalloc(&g->table_dev, sizeof(TcDesc) * tbl.size());
   if (e == cudaSuccess)
     e = cudaMemcpy(g->table_dev, tbl.data(), sizeof(TcDesc) * tbl.size(), cudaMemcpyHostToDevice);
   if (e != cudaSuccess) {
     g_last_cuda_error = static_cast<int>(e);
     if (g->table_dev) cudaFree(g->table_dev);
+    if (g->scratch) cudaFree(g->scratch);
     delete g;
     return CUDALM_B200_ERR_CUDA;
   }
@@ -1135,12 +1341,14 @@ int tc_group_run(const TcGroup* g, cudaStream_t stream) {
   p.n_desc = g->count;
   p.total_items = g->items;
   p.total_cost = g->cost;
-  return tc_run_params(p, g->ntok, stream);
+  if (int rc = tc_run_params(p, g->ntok, stream)) return rc;
+  return tc_launch_combine(p, g->ntok, g->split_tiles, stream);
 }
 
 void tc_group_destroy(TcGroup* g) {
   if (!g) return;
   cudaFree(g->table_dev);
+  if (g->scratch) cudaFree(g->scratch);
   delete g;
 }
 

@@ -78,7 +78,15 @@ CUDALM_B200_API int cudalm_b200_int4_gemv_bf16(const uint8_t* weight, const uint
  * Replaces cudalm::kernels::batch_int4_gemv_bf16
  * (CUDALM include/cudalm/kernels/batch_decode.h:61-63,
  *  src/kernels/batch_decode.cu:95-190,647-659): x is [B, K], y is [B, N].
- * Unlike CUDALM's, the weights are read once for all B rows. */
+ * Unlike CUDALM's, the weights are read once for all B rows.
+ * From 17 rows on (tensor-memory kernel), a call whose projections have few rows
+ * and K >= 2048 cuts K into slices that separate CTAs work on and adds them up in a
+ * fixed order in a second launch; the fp32 partial sums live in stream-ordered
+ * scratch from a memory pool the library owns (allocated and freed on `stream`, so
+ * the call stays asynchronous and can be captured in a CUDA graph).  The same holds
+ * for cudalm_b200_linear_multi, _gate_up_silu_bf16 and _linear_residual_bf16; a
+ * group allocates its scratch once in cudalm_b200_group_create, which is why a
+ * group must not run on two streams at the same time. */
 CUDALM_B200_API int cudalm_b200_batch_int4_gemv_bf16(const uint8_t* weight,
                                      const uint16_t* scales, const uint16_t* x,
                                      uint16_t* y, int N, int K, int B,

@@ -458,6 +458,40 @@ def test_tensor_memory_path_is_deterministic(eng, orc):
         assert np.array_equal(a, gpu_batch(eng, W, S, x))
 
 
+@pytest.mark.parametrize("N,K,M", [(1024, 3584, 32), (1024, 3584, 64), (520, 2048, 17), (2048, 4096, 40)])
+def test_split_k_projection_with_few_items(eng, orc, N, K, M):
+    """A projection with few 256-row items and a long K on the tensor-memory kernel: its K
+    is cut into slices that separate CTAs work on, and a follow-up kernel adds the slices
+    up in slice order.  Against the oracle and the streaming kernel; the same bits on every
+    run, from a single call and from a group (scratch of its own), and with the residual
+    added in the same pass, in place."""
+    import torch
+    W, S = raw_weights(N, K, 700 + N + M)
+    x = make_x(orc, (M, K), 701 + K, "outlier")
+    want = orc.batch_gemv_bf16(W, S, x, threads=8)
+    got = gpu_batch(eng, W, S, x)
+    check_close(orc, got, want, f"split K {N}x{K} M={M}")
+    prev = eng.set_tensor_path_min_rows(1 << 30)
+    try:
+        check_close(orc, got, gpu_batch(eng, W, S, x), f"split K vs streaming {N}x{K} M={M}")
+    finally:
+        eng.set_tensor_path_min_rows(prev)
+    for _ in range(3):
+        assert np.array_equal(got, gpu_batch(eng, W, S, x))
+    lin = eng.W4A16Linear(to_dev(W), to_dev(S, torch.float16))
+    dx = to_dev(x, torch.bfloat16)
+    y = torch.zeros((M, N), dtype=torch.bfloat16, device="cuda")
+    grp = eng.LinearGroup([(lin, dx, y)])
+    grp.run()
+    torch.cuda.synchronize()
+    assert np.array_equal(from_dev(y), got), "group and single call differ"
+    res = make_x(orc, (M, N), 702 + N, "normal")
+    dres = to_dev(res, torch.bfloat16)
+    out = eng.linear_residual_bf16(lin, dx, dres, y=dres)
+    torch.cuda.synchronize()
+    assert np.array_equal(from_dev(out), orc.add_bf16(res, got)), "residual of a split projection"
+
+
 def test_group_on_tensor_memory_path(eng, orc):
     import torch
     M = 32
