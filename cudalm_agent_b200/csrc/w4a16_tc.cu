@@ -131,6 +131,11 @@ struct TcParams {
   int total_items;
   int total_cost;
   int* status;
+  // Launches with a device table: per CTA {first unit, its projection}, gridDim.x + 1
+  // entries, cut on the host, so that a CTA finds its range with two loads; a search of
+  // the table from the kernel is a chain of dependent global loads (tens of them for the
+  // last CTAs of a launch of 48 projections: 12 us before the CTA could start).
+  const int2* cta_ranges;
   // Optional (vocabulary projection, one projection per launch; pick.slots non-null):
   // the CTAs keep per activation row the largest bf16-rounded output they have produced
   // and leave it in the table the token pick derives its bounds from (lm_head_pick.cuh).
@@ -437,7 +442,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
 
   // This CTA's contiguous range of items: an equal share of the stage loads.
   int it_lo, it_hi, d_first;
-  {
+  if (p.cta_ranges != nullptr) {
+    const int2 a = __ldg(p.cta_ranges + blockIdx.x), b = __ldg(p.cta_ranges + blockIdx.x + 1);
+    it_lo = a.x;
+    it_hi = b.x;
+    d_first = it_lo >= it_hi ? p.n_desc : a.y;
+  } else {
     auto item_at = [&](long long cost) -> int {
       if (cost >= p.total_cost) return p.total_items;
       int lo = 0, hi = p.n_desc - 1;
@@ -1301,6 +1311,8 @@ int run_tc(const cudalm_b200_linear* ls, int count, cudaStream_t stream) {
 // Any number of projections: the descriptor table lives on the device.
 struct TcGroup {
   TcDesc* table_dev = nullptr;
+  int2* ranges_dev = nullptr;  // per-CTA ranges for `grid` CTAs
+  int grid = 0;
   void* scratch = nullptr;  // of the projections whose K is split; the group's for its lifetime
   int count = 0, items = 0, cost = 0, ntok = 0, split_tiles = 0;
 };
@@ -1323,9 +1335,35 @@ int tc_group_create(const cudalm_b200_linear* ls, int count, TcGroup** out) {
   if (e == cudaSuccess) e = cudaMalloc(&g->table_dev, sizeof(TcDesc) * tbl.size());
   if (e == cudaSuccess)
     e = cudaMemcpy(g->table_dev, tbl.data(), sizeof(TcDesc) * tbl.size(), cudaMemcpyHostToDevice);
+  // the CTAs' ranges: equal shares of the stage loads, as the kernel cuts them itself
+  // for launches without a device table
+  g->grid = num_sms() < g->items ? num_sms() : g->items;
+  std::vector<int2> ranges(static_cast<size_t>(g->grid) + 1);
+  {
+    auto unit_at = [&](long long cost) -> int {
+      if (cost >= g->cost) return g->items;
+      int lo = 0, hi = count - 1;
+      while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (tbl[static_cast<size_t>(mid)].cost_begin <= cost) lo = mid; else hi = mid - 1;
+      }
+      const TcDesc& d = tbl[static_cast<size_t>(lo)];
+      return d.item_begin + static_cast<int>((cost - d.cost_begin + d.slice_stages - 1) / d.slice_stages);
+    };
+    int d = 0;
+    for (int b = 0; b <= g->grid; ++b) {
+      const int u = unit_at(static_cast<long long>(b) * g->cost / g->grid);
+      while (d + 1 < count && tbl[static_cast<size_t>(d) + 1].item_begin <= u) ++d;
+      ranges[static_cast<size_t>(b)] = make_int2(u, d);
+    }
+  }
+  if (e == cudaSuccess) e = cudaMalloc(&g->ranges_dev, sizeof(int2) * ranges.size());
+  if (e == cudaSuccess)
+    e = cudaMemcpy(g->ranges_dev, ranges.data(), sizeof(int2) * ranges.size(), cudaMemcpyHostToDevice);
   if (e != cudaSuccess) {
     g_last_cuda_error = static_cast<int>(e);
     if (g->table_dev) cudaFree(g->table_dev);
+    if (g->ranges_dev) cudaFree(g->ranges_dev);
     if (g->scratch) cudaFree(g->scratch);
     delete g;
     return CUDALM_B200_ERR_CUDA;
@@ -1341,13 +1379,15 @@ int tc_group_run(const TcGroup* g, cudaStream_t stream) {
   p.n_desc = g->count;
   p.total_items = g->items;
   p.total_cost = g->cost;
-  if (int rc = tc_run_params(p, g->ntok, stream)) return rc;
+  p.cta_ranges = g->ranges_dev;
+  if (int rc = tc_run_params(p, g->ntok, stream, nullptr, g->grid)) return rc;
   return tc_launch_combine(p, g->ntok, g->split_tiles, stream);
 }
 
 void tc_group_destroy(TcGroup* g) {
   if (!g) return;
   cudaFree(g->table_dev);
+  if (g->ranges_dev) cudaFree(g->ranges_dev);
   if (g->scratch) cudaFree(g->scratch);
   delete g;
 }
