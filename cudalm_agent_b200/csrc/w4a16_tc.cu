@@ -465,8 +465,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
     if (it_lo >= it_hi) d_first = p.n_desc;
   }
 
+  // Programmatic dependent launch: everything but the copy thread waits here for the
+  // preceding kernel; the copy thread first starts the weight copies of its first stages
+  // (weights are nobody's output) and waits before the first activation copy.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (warp != kTcProducerWarp) asm volatile("griddepcontrol.wait;" ::: "memory");
 
   std::uint32_t git = 0;  // groups so far (same count in every role)
   TcWalk wk;
@@ -490,6 +493,27 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
         int ps = 0;                  // stage to fill next
         std::uint32_t ps_phase = 0;  // phase its `full` barrier completes next
         bool ps_round = false;       // every stage has been used at least once
+        // activation copies held back until the preceding kernel has completed
+        const CUtensorMap* pend_map[kTcMaxStages];
+        int pend_c[kTcMaxStages];
+        int n_pend = 0;
+        bool waited = false;
+        auto activations = [&](int s, const CUtensorMap* xmap, int c) {
+          std::uint8_t* st = stages + s * kStageBytes;
+          // four boxes of 64 k each; k past K and rows past M arrive as zeros
+          for (int q = 0; q < 4; ++q) {
+            asm volatile(
+                "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+                " [%0], [%1, {%2, %3}], [%4];" ::"r"(smem_u32(st + kTcWeightBytes + q * kBoxBytes)),
+                "l"(xmap), "r"(c * 256 + q * 64), "r"(0), "r"(smem_u32(&sm->full[s]))
+                : "memory");
+          }
+        };
+        auto release_pending = [&]() {
+          asm volatile("griddepcontrol.wait;" ::: "memory");
+          for (int i = 0; i < n_pend; ++i) activations(i, pend_map[i], pend_c[i]);
+          waited = true;
+        };
         for (int item = it_lo; item < it_hi && ok && !*abort_flag; ++item) {
           if (wk.seek(item) || L == nullptr) {
             L = tbl + wk.d;
@@ -520,13 +544,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
                   "r"(smem_u32(&sm->full[s])), "l"(policy)
                   : "memory");
             }
-            // four boxes of 64 k each; k past K and rows past M arrive as zeros
-            for (int q = 0; q < 4; ++q) {
-              asm volatile(
-                  "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
-                  " [%0], [%1, {%2, %3}], [%4];" ::"r"(smem_u32(st + kTcWeightBytes + q * kBoxBytes)),
-                  "l"(&L->xmap), "r"(c * 256 + q * 64), "r"(0), "r"(smem_u32(&sm->full[s]))
-                  : "memory");
+            if (waited) {
+              activations(s, &L->xmap, c);
+            } else {
+              // (the first pass over the ring: stage s is the s-th one filled)
+              pend_map[n_pend] = &L->xmap;
+              pend_c[n_pend] = c;
+              if (++n_pend == kTcStages) release_pending();
             }
             if (++ps == kTcStages) {
               ps = 0;
@@ -535,6 +559,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) w4a16_tc_kernel(const __grid_co
             }
           }
         }
+        if (!waited) release_pending();
       }
     } else if (warp >= kTcMmaWarp && warp < kTcStoreWarp) {
       // ---------------- MMA issuer, one per buffer and tile ----------------
