@@ -751,9 +751,13 @@ def run_ours(args):
         slots[b]["xh"].copy_(x_dev)
     torch.cuda.synchronize()
 
+    waited = [0.0]
+
     def piped_step(i):
         sl = slots[i % 2]
+        w0 = time.perf_counter()
         sl["done"].synchronize()  # the outputs of the step that last used these buffers are on the host
+        waited[0] += time.perf_counter() - w0
         with torch.cuda.stream(sl["stream"]):
             sl["x"].copy_(sl["xh"], non_blocking=True)
             sl["groups"][i % copies].run()
@@ -770,6 +774,7 @@ def run_ours(args):
         e2e_steps = max(args.steps, int(0.25 / max(kernel_ms * 1e-3, 1e-6)))
     t0 = time.perf_counter()
     host_busy = 0.0
+    waited[0] = 0.0
     for i in range(e2e_steps):
         h0 = time.perf_counter()
         piped_step(i)
@@ -781,7 +786,8 @@ def run_ours(args):
     e2e_ms = max_over_ranks(torch, dist, e2e_local_ms) * args.steps / e2e_steps
     e2e_value = world * bytes_step * args.steps / (e2e_ms * 1e-3) / 1e9
     # where a step's time goes on the host: issuing it (copies + launch) or waiting for the GPU
-    e2e_host_issue_ms = max_over_ranks(torch, dist, host_busy * 1e3 / e2e_steps)
+    e2e_host_issue_ms = max_over_ranks(torch, dist, (host_busy - waited[0]) * 1e3 / e2e_steps)
+    e2e_host_wait_ms = max_over_ranks(torch, dist, waited[0] * 1e3 / e2e_steps)
     # the pipelined steps must have produced what the serial call produces
     last = e2e_steps - 1
     for b in range(2):
@@ -861,7 +867,10 @@ def run_ours(args):
                 "h2d_bytes_per_step": x_dev.numel() * 2, "d2h_bytes_per_step": y_dev.numel() * 2,
                 "ms_per_step": e2e_ms / args.steps,
                 "steps_timed": e2e_steps,
+                # the host's share of a step: issuing it (two copies and a launch through Python)
+                # and waiting for the step that last used the same buffers
                 "host_issue_ms_per_step": e2e_host_issue_ms,
+                "host_wait_ms_per_step": e2e_host_wait_ms,
                 "serial_value": serial_value, "serial_ms_per_step": serial_ms / args.steps,
                 "what": "per step: pinned-host activations copied in, one grouped launch, outputs "
                         "copied back to pinned host; two steps in flight on two streams (the host "
