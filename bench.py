@@ -49,7 +49,7 @@ METRIC = "w4a16_gemv_hbm_gbps_m1_projection_set"
 UNIT = "GB/s"
 # dram__bytes_read.sum + dram__bytes_write.sum of one grouped launch, from an ncu
 # capture of this command with --only set (None until a capture exists)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 241_729_536
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 242_111_232
 
 
 def set_bytes(M: int = 1) -> int:
