@@ -492,6 +492,29 @@ def test_split_k_projection_with_few_items(eng, orc, N, K, M):
     assert np.array_equal(from_dev(out), orc.add_bf16(res, got)), "residual of a split projection"
 
 
+def test_group_with_split_and_unsplit_projections(eng, orc):
+    """One launch of the tensor-memory kernel over few tiles in which some projections have
+    their K split (K >= 2048) and others not: every output equals the single call's."""
+    import torch
+    M = 32
+    shapes = [(1024, 3584), (512, 1024), (520, 2048), (264, 4096), (256, 128)]
+    items, singles = [], []
+    for i, (N, K) in enumerate(shapes):
+        W, S = raw_weights(N, K, 800 + i)
+        x = make_x(orc, (M, K), 810 + i, "outlier")
+        singles.append(gpu_batch(eng, W, S, x))
+        check_close(orc, singles[-1], orc.batch_gemv_bf16(W, S, x, threads=8), f"single {N}x{K}")
+        lin = eng.W4A16Linear(to_dev(W), to_dev(S, torch.float16))
+        items.append((lin, to_dev(x, torch.bfloat16), torch.zeros((M, N), dtype=torch.bfloat16, device="cuda")))
+    grp = eng.LinearGroup(items)
+    for _ in range(2):
+        grp.run()
+    torch.cuda.synchronize()
+    for (lin, _, y), want, (N, K) in zip(items, singles, shapes):
+        assert np.array_equal(from_dev(y), want), f"group differs from the single call at {N}x{K}"
+    assert eng.device_status() == 0
+
+
 def test_group_on_tensor_memory_path(eng, orc):
     import torch
     M = 32
