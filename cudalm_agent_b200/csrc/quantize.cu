@@ -53,8 +53,11 @@ __device__ __forceinline__ std::uint32_t quantize_eight(const uint4& v, unsigned
   std::uint32_t out = 0;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    float q = quant_round(w[i], scale32, inv);
-    q = fminf(fmaxf(q, -7.f), 7.f);
+    // No clamp: |w| <= amax and scale32 = fl(amax / 7) >= (amax / 7)(1 - 2^-24) (for a
+    // subnormal scale: within 2^-14 of it, the smallest bf16 being 2^-133), so the quotient
+    // stays below 7.5 and rounds into [-7, 7] by itself, as the quantizer's clip then
+    // never acts on finite inputs.
+    const float q = quant_round(w[i], scale32, inv);
     // q is an integer in [-7, 7]: adding 1.5 * 2^23 leaves it, in two's
     // complement, in the low mantissa bits
     out = insert_nibble(out, __float_as_uint(q + 12582912.0f), 4 * i);
