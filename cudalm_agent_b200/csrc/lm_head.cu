@@ -306,8 +306,9 @@ static int lm_head_topk_impl(const uint8_t* weight, const uint16_t* scales, cons
       t.M = rows;
       int grid = 0;
       if (int rc = run_linear_with_pick(l, t, st, &grid)) return rc;
-      int slices = (N + 4095) / 4096;
-      const int cap = (2 * num_sms() + rows - 1) / rows;
+      // (measured: 2048 logits per CTA and four CTAs per SM in all; 32 rows 74.6 -> 70.6 us)
+      int slices = (N + 2047) / 2048;
+      const int cap = (4 * num_sms() + rows - 1) / rows;
       if (slices > cap) slices = cap;
       if (slices < 1) slices = 1;
       if (int rc = launch_after(lm_head_scan_pick_kernel, dim3(slices, rows), dim3(kSelectThreads), st,
@@ -322,8 +323,8 @@ static int lm_head_topk_impl(const uint8_t* weight, const uint16_t* scales, cons
     zero_counts_kernel<<<1, 64, 0, st>>>(ws.counts, kMaxPassRows);
     if (int rc = check_launch()) return rc;
     if (int rc = run_linear_any(l, st)) return rc;
-    int slices = (N + 4095) / 4096;
-    const int cap = (2 * num_sms() + rows - 1) / rows;
+    int slices = (N + 2047) / 2048;
+    const int cap = (4 * num_sms() + rows - 1) / rows;
     if (slices > cap) slices = cap;
     if (slices < 1) slices = 1;
     if (int rc = launch_after(lm_head_scan_pick_kernel, dim3(slices, rows), dim3(kSelectThreads), st,
