@@ -83,3 +83,50 @@ def test_random_projection(eng, orc, N, K, M, kind, xkind, offset):
     diff = f != want_f
     assert diff.mean() <= 0.005, f"fused gate/up differs on {diff.sum()} of {diff.size}"
     assert eng.device_status() == 0
+
+
+def _pick_cases(n, seed):
+    rng = np.random.default_rng(seed)
+    out = []
+    for i in range(n):
+        N = int(rng.choice([rng.integers(8, 200), rng.integers(200, 5000), rng.integers(5000, 60000)]))
+        K = 128 * int(rng.integers(1, 17))
+        M = int(rng.choice([1, rng.integers(2, 9), rng.integers(9, 17), rng.integers(17, 41)]))
+        k = int(rng.choice([1, 8, 50, 64]))
+        out.append((N, K, M, k, i % 3 == 0))
+    return out
+
+
+@pytest.mark.parametrize("N,K,M,k,ties", _pick_cases(18, 78))
+def test_random_vocabulary_pick(eng, orc, N, K, M, k, ties):
+    """The token pick on random vocabularies: argmax and top-k follow the reference's
+    ordering rule on the device's logits (lists padded with -1 past the vocabulary), with
+    heavy ties (few distinct weight rows) in every third case, with and without a logits
+    buffer, and on consecutive calls (the workspace must come back clean)."""
+    import torch
+    W, S = raw_weights(N, K, 9100 + N + K, "small" if ties else "random")
+    if ties:
+        W[:] = W[np.arange(N) % 7]
+        S[:] = S[np.arange(N) % 7]
+    x = make_x(orc, (M, K), 9101 + M, "rmsnorm")
+    lin = eng.W4A16Linear(to_dev(W), to_dev(S, torch.float16))
+    dx = to_dev(x, torch.bfloat16)
+    head = eng.LmHead(lin, top_k=k, id_offset=17, max_rows=max(M, 1), keep_logits=True)
+    bare = eng.LmHead(lin, top_k=k, id_offset=17, max_rows=max(M, 1))
+    for _ in range(2):
+        argmax, idx, val = head.forward(dx)
+        a2, i2, v2 = bare.forward(dx)
+        torch.cuda.synchronize()
+        logits = from_dev(head.logits[:M])
+        check_close(orc, logits, orc.batch_gemv_bf16(W, S, x, threads=8), f"logits {N}x{K} M={M}")
+        gi, gv, ga = from_dev(idx), from_dev(val), from_dev(argmax)
+        for m in range(M):
+            wi, wv = orc.topk_bf16(logits[m], k)
+            n = len(wi)
+            assert np.array_equal(gi[m][:n] - 17, wi), (N, K, M, k, m)
+            assert np.array_equal(gv[m][:n], wv), (N, K, M, k, m)
+            assert np.all(gi[m][n:] == -1)
+            assert int(ga[m]) - 17 == orc.argmax_bf16(logits[m])
+        assert np.array_equal(from_dev(i2), gi) and np.array_equal(from_dev(v2), gv)
+        assert np.array_equal(from_dev(a2), ga)
+    assert eng.device_status() == 0
