@@ -130,3 +130,65 @@ def test_random_vocabulary_pick(eng, orc, N, K, M, k, ties):
         assert np.array_equal(from_dev(i2), gi) and np.array_equal(from_dev(v2), gv)
         assert np.array_equal(from_dev(a2), ga)
     assert eng.device_status() == 0
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_group(eng, orc, seed):
+    """Grouped launches over random sets of projections (2 to 60 of them, K from 128 to
+    4096, rows 1 to 64 per projection, the same or different row counts inside a group):
+    every output against the oracle, the same bits on a second run, and against the
+    projection's own call on the same kernel class (lean kernel off, so that a single call
+    of up to 16 rows streams as the group does): the same bits when the group's row counts
+    are equal, within one bf16 step on at most one value in a thousand otherwise."""
+    import torch
+    rng = np.random.default_rng(500 + seed)
+    count = int(rng.integers(2, 61))
+    big_m = seed % 4 == 3          # every fourth group: the tensor-memory kernel
+    same_m = seed % 2 == 0
+    m_all = int(rng.integers(17, 65)) if big_m else int(rng.integers(1, 17))
+    items, refs, raws = [], [], []
+    for i in range(count):
+        N = int(rng.choice([rng.integers(1, 40), rng.integers(40, 900), rng.integers(900, 4200)]))
+        K = 128 * int(rng.choice([rng.integers(1, 9), rng.integers(9, 33)]))
+        M = m_all if same_m else (int(rng.integers(17, 65)) if big_m else int(rng.integers(1, 17)))
+        W, S = raw_weights(N, K, 9200 + 100 * seed + i, KINDS[i % 3])
+        x = make_x(orc, (M, K), 9300 + 100 * seed + i, XKINDS[i % 4])
+        lin = eng.W4A16Linear(to_dev(W), to_dev(S, torch.float16))
+        y = torch.zeros((M, N), dtype=torch.bfloat16, device="cuda")
+        items.append((lin, to_dev(x, torch.bfloat16), y))
+        refs.append(orc.batch_gemv_bf16(W, S, x, threads=8))
+        raws.append((W, S, x))
+    grp = eng.LinearGroup(items)
+    grp.run()
+    torch.cuda.synchronize()
+    first = [from_dev(y) for _, _, y in items]
+    for i, (got, want) in enumerate(zip(first, refs)):
+        check_close(orc, got, want, f"group {seed} item {i} {items[i][0].N}x{items[i][0].K} M={items[i][1].shape[0]}")
+    grp.run()
+    torch.cuda.synchronize()
+    for a, (_, _, y) in zip(first, items):
+        assert np.array_equal(a, from_dev(y)), "second run differs"
+    prev = eng.set_direct_path_max_bytes(0)
+    try:
+        for i in range(0, count, max(1, count // 6)):
+            lin, dx, _ = items[i]
+            single = eng.batch_int4_gemv_bf16(lin.weight, lin.scale, dx)
+            torch.cuda.synchronize()
+            # (a projection whose K the tensor-memory kernel splits when it is launched
+            # alone sums in another order than inside a launch with many tiles)
+            if not big_m:
+                # The same kernel class, but a group with several row counts runs every
+                # projection with the column tiles of its largest one: measured, one or two
+                # values in 10,000 then sit on the neighbouring bf16 value.  Never more.
+                sg = from_dev(single)
+                d = np.abs(sg.astype(np.int32) - first[i].astype(np.int32))
+                assert d.max() <= 1 and (d > 0).mean() <= 1e-3, \
+                    f"item {i} differs from its own call: {(d > 0).sum()} of {d.size}, max step {d.max()}"
+                if same_m:
+                    assert d.max() == 0, f"item {i}: equal row counts, yet other bits than its own call"
+            else:
+                check_close(orc, from_dev(single), first[i], f"item {i} against its own call")
+    finally:
+        eng.set_direct_path_max_bytes(prev)
+    grp.close()
+    assert eng.device_status() == 0
