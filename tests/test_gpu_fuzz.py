@@ -177,9 +177,12 @@ def test_random_group(eng, orc, seed):
             # (a projection whose K the tensor-memory kernel splits when it is launched
             # alone sums in another order than inside a launch with many tiles)
             if not big_m:
-                # The same kernel class, but a group with several row counts runs every
-                # projection with the column tiles of its largest one: measured, one or two
-                # values in 10,000 then sit on the neighbouring bf16 value.  Never more.
+                # A group that no single launch takes (its longest K with its largest row
+                # count does not fit the rings) runs its projections one by one, where the
+                # small ones take the lean kernel, whose sums are grouped otherwise:
+                # measured, one or two values in 10,000 then sit on the neighbouring bf16
+                # value.  Never more.  (Row counts alone change nothing: 1, 3, 8, 9 and 16
+                # rows of one projection give the same bits row for row.)
                 sg = from_dev(single)
                 d = np.abs(sg.astype(np.int32) - first[i].astype(np.int32))
                 assert d.max() <= 1 and (d > 0).mean() <= 1e-3, \
