@@ -195,3 +195,34 @@ def test_random_group(eng, orc, seed):
         eng.set_direct_path_max_bytes(prev)
     grp.close()
     assert eng.device_status() == 0
+
+
+@pytest.mark.parametrize("N,K", [(4015, 1024), (3546, 2048), (100, 384)])
+def test_a_row_does_not_depend_on_its_batch(eng, orc, N, K):
+    """CUDALM's batch test holds every row of a batched call to the single call's result
+    (tests/cuda/test_qwen35_batch_kernels.cpp:88-134).  Here a row's bits are the same
+    whether it is projected alone or with 2, 7, 8 or 15 others, on the streaming kernel and
+    (up to 8 rows) on the lean kernel; with 17 rows and more the tensor-memory kernel, whose
+    sums are grouped otherwise, gives the same bits for 17, 40 and 64 rows."""
+    import torch
+    W, S = raw_weights(N, K, 9400 + N)
+    x = make_x(orc, (64, K), 9401 + K, "outlier")
+    dW, dS = to_dev(W), to_dev(S, torch.float16)
+
+    def rows(M):
+        dx = to_dev(x[:M], torch.bfloat16)
+        y = eng.batch_int4_gemv_bf16(dW, dS, dx) if M > 1 else eng.int4_gemv_bf16(dW, dS, dx[0]).view(1, N)
+        torch.cuda.synchronize()
+        return from_dev(y)
+
+    for lean in (0, 1 << 40):
+        prev = eng.set_direct_path_max_bytes(lean)
+        try:
+            base = rows(16 if lean == 0 else 8)
+            for M in ((1, 3, 8, 9) if lean == 0 else (1, 3, 7)):
+                assert np.array_equal(rows(M), base[:M]), f"{M} rows, lean kernel {'on' if lean else 'off'}"
+        finally:
+            eng.set_direct_path_max_bytes(prev)
+    base = rows(64)
+    for M in (17, 40):
+        assert np.array_equal(rows(M), base[:M]), f"{M} rows on the tensor-memory kernel"
